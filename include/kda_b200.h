@@ -1,0 +1,145 @@
+/*
+ * kda_b200 — C ABI of the B200 (sm_100a) Kimi Delta Attention kernels.
+ *
+ * One shared library (libkda_b200.so), extern "C", plain pointers and sizes only.  Every entry point
+ *   - returns 0 on success, a negative KDA_E* code for an argument error (nothing was launched), or a
+ *     positive cudaError_t value if a CUDA call failed;
+ *   - launches on the stream it is given (a cudaStream_t passed as void*), never synchronises and,
+ *     unless its comment says otherwise, never allocates: all outputs and scratch memory belong to
+ *     the caller;
+ *   - may be called from any host thread.
+ *
+ * The operator these entry points implement is the one published as `chunk_kda` / `fused_recurrent_kda`
+ * in flash-linear-attention 0.5.1 (third-party; the NVlabs/kda repository has no native interface for
+ * this path, so the citations below name the Python operator each entry point stands behind):
+ *
+ *     S_t = (I - beta_t k_t k_t^T) Diag(exp g_t) S_{t-1} + beta_t k_t v_t^T,      o_t = scale * S_t^T q_t
+ *
+ * Tensor layout: tokens are flattened, a tensor "[tokens, H, D]" is row-major with D contiguous;
+ * sequence n owns tokens cu_seqlens[n] .. cu_seqlens[n+1]-1.  States are [N, H, K, V] fp32, V contiguous.
+ */
+#ifndef KDA_B200_H_
+#define KDA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default) /* the entry points below are the library's only exports */
+#endif
+
+#define KDA_B200_ABI_VERSION 1
+#define KDA_CHUNK 64 /* tokens per chunk of the chunked kernels */
+
+/* io_dtype of q, k, v, o and of their gradients */
+#define KDA_BF16 0
+#define KDA_FP32 1
+
+/* argument errors */
+#define KDA_OK 0
+#define KDA_E_NULL (-1)        /* a required pointer is NULL */
+#define KDA_E_SHAPE (-2)       /* unsupported or inconsistent sizes */
+#define KDA_E_DTYPE (-3)       /* unsupported io_dtype for this entry point */
+#define KDA_E_ALIGN (-4)       /* a pointer is not 16-byte aligned */
+#define KDA_E_WORKSPACE (-5)   /* workspace too small */
+#define KDA_E_DEVICE (-6)      /* the current device is not sm_100 */
+#define KDA_E_LIMIT (-7)       /* size beyond a documented fixed maximum */
+
+int kda_b200_abi_version(void);
+/* Text for a return code of this library (negative: argument error; positive: cudaGetErrorString). */
+const char* kda_b200_strerror(int code);
+
+/* ------------------------------------------------------------------------------------------------
+ * Token-recurrent forward: decode (one token per sequence) and exact fp32 scans of any length.
+ * Stands behind fused_recurrent_kda (fla/ops/kda/fused_recurrent.py:329-452) and its in-place
+ * lower level fused_recurrent_kda_fwd (fla/ops/kda/fused_recurrent.py:229-325).
+ * The state is kept in fp32 registers, decayed, delta-updated, then read out, token by token.
+ * ------------------------------------------------------------------------------------------------ */
+typedef struct kda_recurrent_args {
+  const void* q;               /* [tokens, H, K] io_dtype */
+  const void* k;               /* [tokens, H, K] io_dtype */
+  const void* v;               /* [tokens, H, V] io_dtype */
+  const float* g;              /* [tokens, H, K] fp32 log-decay (<= 0) */
+  const float* beta;           /* [tokens, H]    fp32 */
+  const float* h0;             /* [slots, H, K, V] fp32 initial states, or NULL for zeros */
+  float* ht;                   /* [slots, H, K, V] fp32 final states, or NULL; may equal h0 (in place) */
+  void* o;                     /* [tokens, H, V] io_dtype */
+  const int32_t* cu_seqlens;   /* device [N+1] or NULL (then every sequence has T tokens) */
+  const int32_t* state_indices;/* device [N] or NULL: sequence n reads/writes state slot state_indices[n] */
+  int64_t tokens;              /* total tokens */
+  int32_t N;                   /* sequences */
+  int32_t T;                   /* tokens per sequence when cu_seqlens is NULL */
+  int32_t H, K, V;             /* K in {32,64,128,256}; V a multiple of 32 */
+  int32_t io_dtype;            /* KDA_BF16 or KDA_FP32 */
+  int32_t use_qk_l2norm;       /* x * rsqrt(sum x^2 + 1e-6) on q and k rows inside the kernel */
+  float scale;
+} kda_recurrent_args;
+
+int kda_recurrent_fwd(const kda_recurrent_args* args, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Chunked forward / backward (chunk = 64 tokens), bf16 tensor-core path, K = V = 128.
+ * Stand behind chunk_kda and its autograd function (fla/ops/kda/chunk.py:167-411, :22-162).
+ *
+ * The caller passes one scratch buffer ("workspace") of at least kda_chunk_workspace_bytes(...).
+ * When save_for_backward != 0 the forward leaves in it what kda_chunk_bwd needs; the caller keeps the
+ * buffer alive and unmodified until the backward call and passes the same pointer.
+ * cu_seqlens is always required (for equal lengths pass 0, T, 2T, ...); chunks restart at every
+ * sequence start and the last chunk of a sequence may be partial.
+ * ------------------------------------------------------------------------------------------------ */
+typedef struct kda_chunk_args {
+  /* forward inputs */
+  const void* q;               /* [tokens, H, K] bf16 */
+  const void* k;               /* [tokens, H, K] bf16 */
+  const void* v;               /* [tokens, H, V] bf16 */
+  const float* g;              /* [tokens, H, K] fp32 log-decay */
+  const float* beta;           /* [tokens, H]    fp32 */
+  const float* h0;             /* [N, H, K, V] fp32 or NULL */
+  const int32_t* cu_seqlens;   /* device [N+1] int32 */
+  /* forward outputs */
+  void* o;                     /* [tokens, H, V] bf16 */
+  float* ht;                   /* [N, H, K, V] fp32 or NULL */
+  /* backward inputs (kda_chunk_bwd only) */
+  const void* d_o;             /* [tokens, H, V] bf16 */
+  const float* d_ht;           /* [N, H, K, V] fp32 or NULL */
+  /* backward outputs (kda_chunk_bwd only) */
+  void* dq;                    /* [tokens, H, K] bf16 */
+  void* dk;                    /* [tokens, H, K] bf16 */
+  void* dv;                    /* [tokens, H, V] bf16 */
+  float* dg;                   /* [tokens, H, K] fp32 */
+  float* dbeta;                /* [tokens, H]    fp32 */
+  float* dh0;                  /* [N, H, K, V] fp32 or NULL */
+  /* scratch */
+  void* workspace;             /* >= kda_chunk_workspace_bytes(..), 256-byte aligned */
+  size_t workspace_bytes;
+  void* bwd_workspace;         /* kda_chunk_bwd only: >= kda_chunk_bwd_workspace_bytes(..), 256-byte aligned */
+  size_t bwd_workspace_bytes;
+  /* sizes */
+  int64_t tokens;
+  int32_t N, H, K, V;
+  int32_t io_dtype;            /* KDA_BF16 */
+  int32_t use_qk_l2norm;
+  int32_t save_for_backward;
+  float scale;
+} kda_chunk_args;
+
+/* Upper bound on the number of chunks: every sequence adds at most one partial chunk. */
+int64_t kda_chunk_max_chunks(int64_t tokens, int32_t N);
+/* Bytes of scratch kda_chunk_fwd needs (more when it must keep what the backward reads). */
+size_t kda_chunk_workspace_bytes(int64_t tokens, int32_t N, int32_t H, int32_t K, int32_t V, int32_t save_for_backward);
+/* Bytes of the backward's own scratch (args->bwd_workspace); it need not outlive the backward call. */
+size_t kda_chunk_bwd_workspace_bytes(int64_t tokens, int32_t N, int32_t H, int32_t K, int32_t V);
+
+int kda_chunk_fwd(const kda_chunk_args* args, void* stream);
+int kda_chunk_bwd(const kda_chunk_args* args, void* stream);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#ifdef __cplusplus
+}
+#endif
+#endif /* KDA_B200_H_ */

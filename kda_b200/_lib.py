@@ -1,0 +1,89 @@
+"""ctypes binding of libkda_b200.so (the C ABI declared in include/kda_b200.h).
+
+There is no fallback: if the shared library is missing or does not load, importing an operator raises."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(PKG, "libkda_b200.so")
+
+KDA_BF16, KDA_FP32 = 0, 1
+ABI_VERSION = 1
+
+
+class RecurrentArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("g", C.c_void_p), ("beta", C.c_void_p),
+        ("h0", C.c_void_p), ("ht", C.c_void_p), ("o", C.c_void_p), ("cu_seqlens", C.c_void_p),
+        ("state_indices", C.c_void_p),
+        ("tokens", C.c_int64), ("N", C.c_int32), ("T", C.c_int32), ("H", C.c_int32), ("K", C.c_int32),
+        ("V", C.c_int32), ("io_dtype", C.c_int32), ("use_qk_l2norm", C.c_int32), ("scale", C.c_float),
+    ]
+
+
+class ChunkArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("g", C.c_void_p), ("beta", C.c_void_p),
+        ("h0", C.c_void_p), ("cu_seqlens", C.c_void_p),
+        ("o", C.c_void_p), ("ht", C.c_void_p),
+        ("d_o", C.c_void_p), ("d_ht", C.c_void_p),
+        ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p), ("dg", C.c_void_p), ("dbeta", C.c_void_p),
+        ("dh0", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("bwd_workspace", C.c_void_p), ("bwd_workspace_bytes", C.c_size_t),
+        ("tokens", C.c_int64), ("N", C.c_int32), ("H", C.c_int32), ("K", C.c_int32), ("V", C.c_int32),
+        ("io_dtype", C.c_int32), ("use_qk_l2norm", C.c_int32), ("save_for_backward", C.c_int32),
+        ("scale", C.c_float),
+    ]
+
+
+EXPORTS = (
+    "kda_b200_abi_version", "kda_b200_strerror", "kda_recurrent_fwd",
+    "kda_chunk_max_chunks", "kda_chunk_workspace_bytes", "kda_chunk_bwd_workspace_bytes",
+    "kda_chunk_fwd", "kda_chunk_bwd",
+)
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Loads the library once; raises RuntimeError with a build hint if it is absent."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m kda_b200.build` (nvcc, sm_100a). "
+            "kda_b200 has no CPU or PyTorch fallback.")
+    lib = C.CDLL(LIB_PATH)
+    lib.kda_b200_abi_version.restype = C.c_int
+    lib.kda_b200_strerror.restype = C.c_char_p
+    lib.kda_b200_strerror.argtypes = [C.c_int]
+    lib.kda_recurrent_fwd.restype = C.c_int
+    lib.kda_recurrent_fwd.argtypes = [C.POINTER(RecurrentArgs), C.c_void_p]
+    lib.kda_chunk_max_chunks.restype = C.c_int64
+    lib.kda_chunk_max_chunks.argtypes = [C.c_int64, C.c_int32]
+    lib.kda_chunk_workspace_bytes.restype = C.c_size_t
+    lib.kda_chunk_workspace_bytes.argtypes = [C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32]
+    lib.kda_chunk_bwd_workspace_bytes.restype = C.c_size_t
+    lib.kda_chunk_bwd_workspace_bytes.argtypes = [C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32]
+    for name in ("kda_chunk_fwd", "kda_chunk_bwd"):
+        fn = getattr(lib, name)
+        fn.restype = C.c_int
+        fn.argtypes = [C.POINTER(ChunkArgs), C.c_void_p]
+    if lib.kda_b200_abi_version() != ABI_VERSION:
+        raise RuntimeError("libkda_b200.so was built from a different ABI version; rebuild it")
+    _lib = lib
+    return lib
+
+
+class KdaError(RuntimeError):
+    pass
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        msg = load().kda_b200_strerror(code).decode()
+        raise KdaError(f"{what} failed with code {code}: {msg}")

@@ -1,0 +1,86 @@
+// Shared definitions of the chunked KDA kernels: workspace carving and per-(chunk, head) tile formats.
+//
+// Every intermediate that travels between kernels is a per-(chunk, head) TILE that is contiguous in
+// global memory and already holds the XOR-swizzled image the consumer wants in shared memory, so a
+// consumer fetches a tile with one 1-D bulk (TMA) copy and reads it with ldmatrix without bank
+// conflicts.  Tile index = chunk * H + head.  Formats (bf16 unless noted):
+//   W, QG, KG : [64 tokens][128 k]   256-byte rows      w = Tm (beta k Gam), qg = scale q Gam, kg = k exp(G_last - G)
+//   AQK, TI   : [64 t][64 j]         128-byte rows      Aqk (lower incl. diagonal), Tm = (I + Akk)^-1
+//   UT        : [128 v][64 t]        128-byte rows      u^T,  u = Tm (beta v)
+//   GL        : fp32 [128]                              Gam_last = exp(G_last)
+//   HS, DH    : [128 v][128 k]       256-byte rows      transposed state at chunk start / its gradient at chunk end
+//   VNEWT, DVNEWT : [128 v][64 t]    128-byte rows      v_new^T and its gradient
+#pragma once
+
+#include "kda_common.cuh"
+
+namespace kda {
+
+constexpr int KD = 128;   // key head dim served by the chunked kernels
+constexpr int VD = 128;   // value head dim
+
+constexpr size_t TILE_TK = size_t(C) * KD * 2;    // 16 KiB
+constexpr size_t TILE_TT = size_t(C) * C * 2;     //  8 KiB
+constexpr size_t TILE_VT = size_t(VD) * C * 2;    // 16 KiB
+constexpr size_t TILE_VK = size_t(VD) * KD * 2;   // 32 KiB
+constexpr size_t TILE_GL = size_t(KD) * 4;        // 512 B
+
+struct ChunkWs {
+  int* seq_chunk_off;   // [N+1] first chunk of each sequence; [N] = total chunks
+  int* chunk_seq;       // [max_chunks] sequence of each chunk
+  unsigned* status;     // [4] device status word(s): nonzero = a bounded wait gave up
+  unsigned char *W, *UT, *KG, *QG, *AQK, *GL;          // always
+  unsigned char *TI, *HS, *VNEWT;                      // save_for_backward only
+  unsigned char *DH, *DVNEWT;                          // backward scratch
+  size_t fwd_bytes, bwd_bytes;
+};
+
+inline size_t align_up(size_t x, size_t a = 256) { return (x + a - 1) / a * a; }
+
+// Lays the workspace out.  base may be NULL (sizes only).  bwd_base: separate backward scratch.
+inline ChunkWs carve_ws(unsigned char* base, unsigned char* bwd_base, int64_t tokens, int N, int H, bool save) {
+  ChunkWs w{};
+  const size_t NTmax = static_cast<size_t>(tokens / C + N);
+  const size_t tiles = NTmax * static_cast<size_t>(H);
+  size_t off = 0;
+  auto take = [&](size_t bytes) { unsigned char* p = base ? base + off : nullptr; off += align_up(bytes); return p; };
+  w.seq_chunk_off = reinterpret_cast<int*>(take(sizeof(int) * (static_cast<size_t>(N) + 1)));
+  w.chunk_seq = reinterpret_cast<int*>(take(sizeof(int) * (NTmax + 1)));
+  w.status = reinterpret_cast<unsigned*>(take(16));
+  w.W = take(tiles * TILE_TK);
+  w.UT = take(tiles * TILE_VT);
+  w.KG = take(tiles * TILE_TK);
+  w.QG = take(tiles * TILE_TK);
+  w.AQK = take(tiles * TILE_TT);
+  w.GL = take(tiles * TILE_GL);
+  if (save) {
+    w.TI = take(tiles * TILE_TT);
+    w.HS = take(tiles * TILE_VK);
+    w.VNEWT = take(tiles * TILE_VT);
+  }
+  w.fwd_bytes = off;
+  size_t boff = 0;
+  auto takeb = [&](size_t bytes) { unsigned char* p = bwd_base ? bwd_base + boff : nullptr; boff += align_up(bytes); return p; };
+  w.DH = takeb(tiles * TILE_VK);
+  w.DVNEWT = takeb(tiles * TILE_VT);
+  w.bwd_bytes = boff;
+  return w;
+}
+
+// Chunk geometry read from the tables: which sequence, first token, valid rows.
+struct ChunkInfo {
+  int seq;
+  long long tok0;
+  int len;
+};
+__device__ __forceinline__ ChunkInfo chunk_info(const int* seq_chunk_off, const int* chunk_seq, const int* cu, int c) {
+  ChunkInfo ci;
+  ci.seq = chunk_seq[c];
+  const int cis = c - seq_chunk_off[ci.seq];
+  ci.tok0 = static_cast<long long>(cu[ci.seq]) + static_cast<long long>(cis) * C;
+  const long long rem = static_cast<long long>(cu[ci.seq + 1]) - ci.tok0;
+  ci.len = rem < C ? static_cast<int>(rem) : C;
+  return ci;
+}
+
+}  // namespace kda

@@ -1,0 +1,781 @@
+// Chunked KDA forward for sm_100a: chunk tables, per-chunk preparation, and the state scan.
+//
+//  kda_chunk_tables_kernel   cu_seqlens -> (first chunk of each sequence, sequence of each chunk); device only,
+//                            so that variable-length calls need no device->host copy.
+//  kda_chunk_prepare_kernel  one CTA per (chunk, head): everything that does not depend on the state:
+//                            G = cumsum(g), Aqk, Akk, Tm = (I+Akk)^-1, w, u, qg, kg  -> tiles in the workspace.
+//  kda_chunk_scan_kernel     one CTA per (sequence, head): walks the chunks in order with the fp32 state in
+//                            registers (transposed, one warp per 16 value columns, all 128 key columns),
+//                            operand tiles streamed through a 3-stage TMA bulk-copy pipeline issued by
+//                            one lane.   v_new = u - w h;  o = qg h + Aqk v_new;  h = Diag(Gam_last) h + kg^T v_new.
+#include <mutex>
+
+#include "kda_chunk.cuh"
+
+namespace kda {
+
+// =================================================================================================
+// chunk tables
+// =================================================================================================
+__global__ void __launch_bounds__(1024) kda_chunk_tables_kernel(const int* __restrict__ cu, int N, int* __restrict__ seq_chunk_off,
+                                                                int* __restrict__ chunk_seq, unsigned* __restrict__ status) {
+  __shared__ int part[1024];
+  const int tid = threadIdx.x;
+  const int per = (N + 1023) / 1024;
+  const int n0 = min(N, tid * per), n1 = min(N, n0 + per);
+  int sum = 0;
+  for (int n = n0; n < n1; ++n) {
+    const int len = cu[n + 1] - cu[n];
+    sum += (len > 0) ? (len + C - 1) / C : 0;
+  }
+  part[tid] = sum;
+  __syncthreads();
+  for (int off = 1; off < 1024; off <<= 1) {   // inclusive Hillis-Steele scan
+    int x = (tid >= off) ? part[tid - off] : 0;
+    __syncthreads();
+    part[tid] += x;
+    __syncthreads();
+  }
+  int run = part[tid] - sum;   // exclusive prefix
+  for (int n = n0; n < n1; ++n) {
+    const int len = cu[n + 1] - cu[n];
+    const int nc = (len > 0) ? (len + C - 1) / C : 0;
+    seq_chunk_off[n] = run;
+    for (int c = 0; c < nc; ++c) chunk_seq[run + c] = n;
+    run += nc;
+  }
+  if (tid == 1023) seq_chunk_off[N] = part[1023];
+  if (tid < 4) status[tid] = 0u;
+}
+
+// =================================================================================================
+// per-chunk preparation
+// =================================================================================================
+constexpr int QS = 136;   // bf16 elements per padded row of the q/k/v tiles (272 B: ldmatrix rows hit distinct banks)
+constexpr int GS = 136;   // floats per padded row of G
+constexpr int AS = 68;    // floats per padded row of the 64x64 matrices
+
+struct PrepSmem {
+  __nv_bfloat16 q[C * QS];
+  __nv_bfloat16 k[C * QS];
+  __nv_bfloat16 v[C * QS];
+  float G[C * GS];        // log2-domain inclusive cumsum of g
+  float Akk[C * AS];      // beta_t <k_t D, k_j>, then overwritten by Tm = (I + Akk)^-1
+  float Aqk[C * AS];      // scale <q_t D, k_j>
+  float X[32 * 33];       // scratch of the block-merge products
+  float beta[C];
+};
+
+struct PrepParams {
+  const __nv_bfloat16 *q, *k, *v;
+  const float *g, *beta;
+  const int* cu;
+  const int *seq_chunk_off, *chunk_seq;
+  unsigned char *W, *UT, *KG, *QG, *AQK, *GL, *TI;   // TI may be NULL
+  int N, H;
+  int use_l2norm;
+  float scale;
+};
+
+__global__ void __launch_bounds__(256, 1) kda_chunk_prepare_kernel(const PrepParams p) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  PrepSmem& s = *reinterpret_cast<PrepSmem*>(smem_raw);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gid = lane >> 2, tig = lane & 3;
+  const int c = blockIdx.x, h = blockIdx.y;
+  if (c >= p.seq_chunk_off[p.N]) return;
+  const ChunkInfo ci = chunk_info(p.seq_chunk_off, p.chunk_seq, p.cu, c);
+  const int len = ci.len;
+  const size_t tile = static_cast<size_t>(c) * p.H + h;
+
+  // ---- P1: stage q, k, v, g, beta; rows >= len are zero-filled -----------------------------------
+  {
+    for (int i = tid; i < C * 16; i += 256) {
+      const int r = i >> 4, pc = i & 15;
+      const bool ok = r < len;
+      const size_t row = (static_cast<size_t>(ci.tok0 + (ok ? r : 0)) * p.H + h) * KD + pc * 8;
+      cp_async16(&s.q[r * QS + pc * 8], p.q + row, ok);
+      cp_async16(&s.k[r * QS + pc * 8], p.k + row, ok);
+      cp_async16(&s.v[r * QS + pc * 8], p.v + row, ok);
+    }
+    for (int i = tid; i < C * 32; i += 256) {
+      const int r = i >> 5, pc = i & 31;
+      const bool ok = r < len;
+      const size_t row = (static_cast<size_t>(ci.tok0 + (ok ? r : 0)) * p.H + h) * KD + pc * 4;
+      cp_async16(&s.G[r * GS + pc * 4], p.g + row, ok);
+    }
+    cp_async_commit();
+    if (tid < C) s.beta[tid] = (tid < len) ? __ldg(p.beta + static_cast<size_t>(ci.tok0 + tid) * p.H + h) : 0.f;
+    for (int i = tid; i < C * AS; i += 256) {
+      s.Akk[i] = 0.f;
+      s.Aqk[i] = 0.f;
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+  }
+
+  // ---- P1b: optional L2 normalisation of q and k rows (result rounded to bf16, as the unfused op does)
+  if (p.use_l2norm) {
+    for (int r = warp; r < C; r += 8) {
+      uint2 qr = *reinterpret_cast<uint2*>(&s.q[r * QS + lane * 4]);
+      uint2 kr = *reinterpret_cast<uint2*>(&s.k[r * QS + lane * 4]);
+      float2 q0 = unpack_bf16(qr.x), q1 = unpack_bf16(qr.y), k0 = unpack_bf16(kr.x), k1 = unpack_bf16(kr.y);
+      float sq = warp_sum(q0.x * q0.x + q0.y * q0.y + q1.x * q1.x + q1.y * q1.y);
+      float sk = warp_sum(k0.x * k0.x + k0.y * k0.y + k1.x * k1.x + k1.y * k1.y);
+      const float rq = rsqrtf(sq + L2NORM_EPS), rk = rsqrtf(sk + L2NORM_EPS);
+      qr.x = pack_bf16(q0.x * rq, q0.y * rq); qr.y = pack_bf16(q1.x * rq, q1.y * rq);
+      kr.x = pack_bf16(k0.x * rk, k0.y * rk); kr.y = pack_bf16(k1.x * rk, k1.y * rk);
+      *reinterpret_cast<uint2*>(&s.q[r * QS + lane * 4]) = qr;
+      *reinterpret_cast<uint2*>(&s.k[r * QS + lane * 4]) = kr;
+    }
+  }
+
+  // ---- P2: G = cumsum(g) * log2(e), one column per thread -----------------------------------------
+  if (tid < KD) {
+    float run = 0.f;
+#pragma unroll 8
+    for (int t = 0; t < C; ++t) {
+      run += s.G[t * GS + tid];
+      s.G[t * GS + tid] = run * LOG2E;
+    }
+  }
+  __syncthreads();
+
+  // ---- P3a: diagonal 16x16 blocks, pairwise decay exp2(G_t - G_j) (never a factorisation: range-safe)
+  // A warp takes rows {warp, 15-warp} of each block (equal work); lanes own 4 key columns each.
+  for (int b = 0; b < 4; ++b) {
+#pragma unroll 1
+    for (int rr = 0; rr < 2; ++rr) {
+      const int t = 16 * b + (rr ? 15 - warp : warp);
+      const float4 Gt = *reinterpret_cast<const float4*>(&s.G[t * GS + lane * 4]);
+      const uint2 qr = *reinterpret_cast<const uint2*>(&s.q[t * QS + lane * 4]);
+      const uint2 kr = *reinterpret_cast<const uint2*>(&s.k[t * QS + lane * 4]);
+      const float2 q0 = unpack_bf16(qr.x), q1 = unpack_bf16(qr.y), k0 = unpack_bf16(kr.x), k1 = unpack_bf16(kr.y);
+      const float bt = s.beta[t];
+#pragma unroll 2
+      for (int j = 16 * b; j <= t; ++j) {
+        const float4 Gj = *reinterpret_cast<const float4*>(&s.G[j * GS + lane * 4]);
+        const uint2 jr = *reinterpret_cast<const uint2*>(&s.k[j * QS + lane * 4]);
+        const float2 j0 = unpack_bf16(jr.x), j1 = unpack_bf16(jr.y);
+        const float d0 = j0.x * ex2(Gt.x - Gj.x), d1 = j0.y * ex2(Gt.y - Gj.y);
+        const float d2 = j1.x * ex2(Gt.z - Gj.z), d3 = j1.y * ex2(Gt.w - Gj.w);
+        const float pq = q0.x * d0 + q0.y * d1 + q1.x * d2 + q1.y * d3;
+        const float pk = k0.x * d0 + k0.y * d1 + k1.x * d2 + k1.y * d3;
+        // lanes 0..15 end with sum(pq), lanes 16..31 with sum(pk)
+        const bool hi = lane & 16;
+        float x = (hi ? pk : pq) + __shfl_xor_sync(0xffffffffu, hi ? pq : pk, 16);
+        x += __shfl_xor_sync(0xffffffffu, x, 8);
+        x += __shfl_xor_sync(0xffffffffu, x, 4);
+        x += __shfl_xor_sync(0xffffffffu, x, 2);
+        x += __shfl_xor_sync(0xffffffffu, x, 1);
+        if (lane == 0) s.Aqk[t * AS + j] = p.scale * x;
+        if (lane == 16 && j < t) s.Akk[t * AS + j] = bt * x;
+      }
+    }
+  }
+
+  // ---- P3b: off-diagonal 16x16 blocks on tensor cores.  For row block I the decay is factored around
+  // the block's first row r0 = 16 I:  exp2(G_t - G_r0) * exp2(G_r0 - G_j), both factors <= 1 for j < r0 <= t.
+  for (int u = warp; u < 12; u += 8) {
+    const int I = (u < 2) ? 1 : (u < 6 ? 2 : 3);
+    const int nt = (u < 2) ? u : (u < 6 ? u - 2 : u - 6);
+    const int r0 = 16 * I, ta = r0 + gid, tb = ta + 8, j = nt * 8 + gid;
+    float cq[4] = {0.f, 0.f, 0.f, 0.f}, ck[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 2
+    for (int ks = 0; ks < 8; ++ks) {
+      const int k0 = ks * 16 + tig * 2, k1 = k0 + 8;
+      const float2 R0 = *reinterpret_cast<const float2*>(&s.G[r0 * GS + k0]);
+      const float2 R1 = *reinterpret_cast<const float2*>(&s.G[r0 * GS + k1]);
+      const float2 Ga0 = *reinterpret_cast<const float2*>(&s.G[ta * GS + k0]);
+      const float2 Ga1 = *reinterpret_cast<const float2*>(&s.G[ta * GS + k1]);
+      const float2 Gb0 = *reinterpret_cast<const float2*>(&s.G[tb * GS + k0]);
+      const float2 Gb1 = *reinterpret_cast<const float2*>(&s.G[tb * GS + k1]);
+      const float2 Gj0 = *reinterpret_cast<const float2*>(&s.G[j * GS + k0]);
+      const float2 Gj1 = *reinterpret_cast<const float2*>(&s.G[j * GS + k1]);
+      const float ea0x = ex2(Ga0.x - R0.x), ea0y = ex2(Ga0.y - R0.y), ea1x = ex2(Ga1.x - R1.x), ea1y = ex2(Ga1.y - R1.y);
+      const float eb0x = ex2(Gb0.x - R0.x), eb0y = ex2(Gb0.y - R0.y), eb1x = ex2(Gb1.x - R1.x), eb1y = ex2(Gb1.y - R1.y);
+      const float2 qa0 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.q[ta * QS + k0]));
+      const float2 qa1 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.q[ta * QS + k1]));
+      const float2 qb0 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.q[tb * QS + k0]));
+      const float2 qb1 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.q[tb * QS + k1]));
+      const float2 ka0 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.k[ta * QS + k0]));
+      const float2 ka1 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.k[ta * QS + k1]));
+      const float2 kb0 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.k[tb * QS + k0]));
+      const float2 kb1 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.k[tb * QS + k1]));
+      const float2 kj0 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.k[j * QS + k0]));
+      const float2 kj1 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.k[j * QS + k1]));
+      uint32_t aq[4], ak[4];
+      aq[0] = pack_bf16(qa0.x * ea0x, qa0.y * ea0y); aq[1] = pack_bf16(qb0.x * eb0x, qb0.y * eb0y);
+      aq[2] = pack_bf16(qa1.x * ea1x, qa1.y * ea1y); aq[3] = pack_bf16(qb1.x * eb1x, qb1.y * eb1y);
+      ak[0] = pack_bf16(ka0.x * ea0x, ka0.y * ea0y); ak[1] = pack_bf16(kb0.x * eb0x, kb0.y * eb0y);
+      ak[2] = pack_bf16(ka1.x * ea1x, ka1.y * ea1y); ak[3] = pack_bf16(kb1.x * eb1x, kb1.y * eb1y);
+      const uint32_t b0 = pack_bf16(kj0.x * ex2(R0.x - Gj0.x), kj0.y * ex2(R0.y - Gj0.y));
+      const uint32_t b1 = pack_bf16(kj1.x * ex2(R1.x - Gj1.x), kj1.y * ex2(R1.y - Gj1.y));
+      mma16816(cq, aq, b0, b1);
+      mma16816(ck, ak, b0, b1);
+    }
+    const int col = nt * 8 + tig * 2;
+    const float ba = s.beta[ta], bb = s.beta[tb];
+    s.Aqk[ta * AS + col] = p.scale * cq[0]; s.Aqk[ta * AS + col + 1] = p.scale * cq[1];
+    s.Aqk[tb * AS + col] = p.scale * cq[2]; s.Aqk[tb * AS + col + 1] = p.scale * cq[3];
+    s.Akk[ta * AS + col] = ba * ck[0]; s.Akk[ta * AS + col + 1] = ba * ck[1];
+    s.Akk[tb * AS + col] = bb * ck[2]; s.Akk[tb * AS + col + 1] = bb * ck[3];
+  }
+  __syncthreads();
+
+  // ---- P4: Tm = (I + Akk)^-1, fp32.  16x16 diagonal blocks by forward substitution (one column per
+  // thread, in registers), then two levels of block merges  T21 = -T22 A21 T11.
+  {
+    float x[16];
+    if (tid < 64) {
+      const int b = tid >> 4, cc = tid & 15;
+      const float* A = &s.Akk[(16 * b) * AS + 16 * b];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        float acc = (i == cc) ? 1.f : 0.f;
+#pragma unroll
+        for (int m = 0; m < i; ++m) acc -= A[i * AS + m] * x[m];
+        x[i] = acc;
+      }
+    }
+    __syncthreads();
+    if (tid < 64) {
+      const int b = tid >> 4, cc = tid & 15;
+      float* A = &s.Akk[(16 * b) * AS + 16 * b];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) A[i * AS + cc] = x[i];
+    }
+    __syncthreads();
+    // level 1: pairs (rows 16..31 | cols 0..15) and (rows 48..63 | cols 32..47)
+    {
+      const int pr = tid >> 7, e = tid & 127;            // 2 pairs x 128 threads, 2 outputs each
+      const int base = 32 * pr;
+      float* A21 = &s.Akk[(base + 16) * AS + base];
+      const float* T11 = &s.Akk[base * AS + base];
+      const float* T22 = &s.Akk[(base + 16) * AS + base + 16];
+      float* X = &s.X[pr * 16 * 17];
+      float r[2];
+#pragma unroll
+      for (int o = 0; o < 2; ++o) {
+        const int idx = e * 2 + o, i = idx >> 4, jj = idx & 15;
+        float acc = 0.f;
+#pragma unroll
+        for (int m = 0; m < 16; ++m) acc += A21[i * AS + m] * T11[m * AS + jj];
+        r[o] = acc;
+      }
+#pragma unroll
+      for (int o = 0; o < 2; ++o) {
+        const int idx = e * 2 + o;
+        X[(idx >> 4) * 17 + (idx & 15)] = r[o];
+      }
+      __syncthreads();
+#pragma unroll
+      for (int o = 0; o < 2; ++o) {
+        const int idx = e * 2 + o, i = idx >> 4, jj = idx & 15;
+        float acc = 0.f;
+#pragma unroll
+        for (int m = 0; m < 16; ++m) acc += T22[i * AS + m] * X[m * 17 + jj];
+        r[o] = -acc;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int o = 0; o < 2; ++o) {
+        const int idx = e * 2 + o;
+        A21[(idx >> 4) * AS + (idx & 15)] = r[o];
+      }
+      __syncthreads();
+    }
+    // level 2: rows 32..63 | cols 0..31
+    {
+      float* A21 = &s.Akk[32 * AS];
+      const float* T11 = &s.Akk[0];
+      const float* T22 = &s.Akk[32 * AS + 32];
+      float r[4];
+#pragma unroll
+      for (int o = 0; o < 4; ++o) {
+        const int idx = tid * 4 + o, i = idx >> 5, jj = idx & 31;
+        float acc = 0.f;
+#pragma unroll 8
+        for (int m = 0; m < 32; ++m) acc += A21[i * AS + m] * T11[m * AS + jj];
+        r[o] = acc;
+      }
+#pragma unroll
+      for (int o = 0; o < 4; ++o) {
+        const int idx = tid * 4 + o;
+        s.X[(idx >> 5) * 33 + (idx & 31)] = r[o];
+      }
+      __syncthreads();
+#pragma unroll
+      for (int o = 0; o < 4; ++o) {
+        const int idx = tid * 4 + o, i = idx >> 5, jj = idx & 31;
+        float acc = 0.f;
+#pragma unroll 8
+        for (int m = 0; m < 32; ++m) acc += T22[i * AS + m] * s.X[m * 33 + jj];
+        r[o] = -acc;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int o = 0; o < 4; ++o) {
+        const int idx = tid * 4 + o;
+        A21[(idx >> 5) * AS + (idx & 31)] = r[o];
+      }
+      __syncthreads();
+    }
+  }
+
+  // ---- P5a: elementwise tiles straight to global in their swizzled images: QG, KG, AQK, TI, GL ---------
+  {
+    unsigned char* gQG = p.QG + tile * TILE_TK;
+    unsigned char* gKG = p.KG + tile * TILE_TK;
+    for (int i = tid; i < C * 16; i += 256) {
+      const int r = i >> 4, pc = i & 15;
+      const uint4 qr = *reinterpret_cast<const uint4*>(&s.q[r * QS + pc * 8]);
+      const uint4 kr = *reinterpret_cast<const uint4*>(&s.k[r * QS + pc * 8]);
+      const float4 Ga = *reinterpret_cast<const float4*>(&s.G[r * GS + pc * 8]);
+      const float4 Gb = *reinterpret_cast<const float4*>(&s.G[r * GS + pc * 8 + 4]);
+      const float4 La = *reinterpret_cast<const float4*>(&s.G[(C - 1) * GS + pc * 8]);
+      const float4 Lb = *reinterpret_cast<const float4*>(&s.G[(C - 1) * GS + pc * 8 + 4]);
+      const float g8[8] = {Ga.x, Ga.y, Ga.z, Ga.w, Gb.x, Gb.y, Gb.z, Gb.w};
+      const float l8[8] = {La.x, La.y, La.z, La.w, Lb.x, Lb.y, Lb.z, Lb.w};
+      const uint32_t qw[4] = {qr.x, qr.y, qr.z, qr.w}, kw[4] = {kr.x, kr.y, kr.z, kr.w};
+      uint32_t oq[4], ok[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 qq = unpack_bf16(qw[e]), kk = unpack_bf16(kw[e]);
+        const float e0 = ex2(g8[2 * e]), e1 = ex2(g8[2 * e + 1]);
+        oq[e] = pack_bf16(p.scale * qq.x * e0, p.scale * qq.y * e1);
+        ok[e] = pack_bf16(kk.x * ex2(l8[2 * e] - g8[2 * e]), kk.y * ex2(l8[2 * e + 1] - g8[2 * e + 1]));
+      }
+      const uint32_t off = swz<256>(r, pc * 8);
+      *reinterpret_cast<uint4*>(gQG + off) = make_uint4(oq[0], oq[1], oq[2], oq[3]);
+      *reinterpret_cast<uint4*>(gKG + off) = make_uint4(ok[0], ok[1], ok[2], ok[3]);
+    }
+    unsigned char* gA = p.AQK + tile * TILE_TT;
+    unsigned char* gT = p.TI ? p.TI + tile * TILE_TT : nullptr;
+    for (int i = tid; i < C * 8; i += 256) {
+      const int r = i >> 3, pc = i & 7;
+      const float4 a0 = *reinterpret_cast<const float4*>(&s.Aqk[r * AS + pc * 8]);
+      const float4 a1 = *reinterpret_cast<const float4*>(&s.Aqk[r * AS + pc * 8 + 4]);
+      const uint32_t off = swz<128>(r, pc * 8);
+      *reinterpret_cast<uint4*>(gA + off) =
+          make_uint4(pack_bf16(a0.x, a0.y), pack_bf16(a0.z, a0.w), pack_bf16(a1.x, a1.y), pack_bf16(a1.z, a1.w));
+      if (gT) {
+        const float4 t0 = *reinterpret_cast<const float4*>(&s.Akk[r * AS + pc * 8]);
+        const float4 t1 = *reinterpret_cast<const float4*>(&s.Akk[r * AS + pc * 8 + 4]);
+        *reinterpret_cast<uint4*>(gT + off) =
+            make_uint4(pack_bf16(t0.x, t0.y), pack_bf16(t0.z, t0.w), pack_bf16(t1.x, t1.y), pack_bf16(t1.z, t1.w));
+      }
+    }
+    if (tid < KD) reinterpret_cast<float*>(p.GL + tile * TILE_GL)[tid] = ex2(s.G[(C - 1) * GS + tid]);
+  }
+  __syncthreads();   // every read of s.q is done: its buffer becomes k * Gam
+
+  // ---- P5b: kGam = k * exp2(G) (bf16) into the q buffer ---------------------------------------------
+  for (int i = tid; i < C * 16; i += 256) {
+    const int r = i >> 4, pc = i & 15;
+    const uint4 kr = *reinterpret_cast<const uint4*>(&s.k[r * QS + pc * 8]);
+    const float4 Ga = *reinterpret_cast<const float4*>(&s.G[r * GS + pc * 8]);
+    const float4 Gb = *reinterpret_cast<const float4*>(&s.G[r * GS + pc * 8 + 4]);
+    const float2 k0 = unpack_bf16(kr.x), k1 = unpack_bf16(kr.y), k2 = unpack_bf16(kr.z), k3 = unpack_bf16(kr.w);
+    *reinterpret_cast<uint4*>(&s.q[r * QS + pc * 8]) =
+        make_uint4(pack_bf16(k0.x * ex2(Ga.x), k0.y * ex2(Ga.y)), pack_bf16(k1.x * ex2(Ga.z), k1.y * ex2(Ga.w)),
+                   pack_bf16(k2.x * ex2(Gb.x), k2.y * ex2(Gb.y)), pack_bf16(k3.x * ex2(Gb.z), k3.y * ex2(Gb.w)));
+  }
+  __syncthreads();
+
+  // ---- P5c: u = (Tm beta) v,  w = (Tm beta) kGam on tensor cores.  Warp = (row tile mt, column half nh).
+  {
+    const int mt = warp & 3, nh = warp >> 2;
+    uint32_t a[4][4];
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+      const int ra = mt * 16 + gid, rb = ra + 8, c0 = ks * 16 + tig * 2, c1 = c0 + 8;
+      const float2 b0 = *reinterpret_cast<const float2*>(&s.beta[c0]);
+      const float2 b1 = *reinterpret_cast<const float2*>(&s.beta[c1]);
+      const float2 t00 = *reinterpret_cast<const float2*>(&s.Akk[ra * AS + c0]);
+      const float2 t10 = *reinterpret_cast<const float2*>(&s.Akk[rb * AS + c0]);
+      const float2 t01 = *reinterpret_cast<const float2*>(&s.Akk[ra * AS + c1]);
+      const float2 t11 = *reinterpret_cast<const float2*>(&s.Akk[rb * AS + c1]);
+      a[ks][0] = pack_bf16(t00.x * b0.x, t00.y * b0.y);
+      a[ks][1] = pack_bf16(t10.x * b0.x, t10.y * b0.y);
+      a[ks][2] = pack_bf16(t01.x * b1.x, t01.y * b1.y);
+      a[ks][3] = pack_bf16(t11.x * b1.x, t11.y * b1.y);
+    }
+    unsigned char* gW = p.W + tile * TILE_TK;
+    unsigned char* gUT = p.UT + tile * TILE_VT;
+#pragma unroll 1
+    for (int which = 0; which < 2; ++which) {
+      const __nv_bfloat16* Bs = which ? s.q : s.v;   // kGam or v, [token j][column]
+      float acc[8][4];
+#pragma unroll
+      for (int n = 0; n < 8; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) {
+#pragma unroll
+        for (int np = 0; np < 4; ++np) {
+          const int krow = ks * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+          const int ncol = nh * 64 + np * 16 + ((lane >> 4) << 3);
+          uint32_t b[4];
+          ldsm_x4_t(b, smem_u32(&Bs[krow * QS + ncol]));
+          mma16816(acc[2 * np], a[ks], b[0], b[1]);
+          mma16816(acc[2 * np + 1], a[ks], b[2], b[3]);
+        }
+      }
+      const int ta = mt * 16 + gid, tb = ta + 8;
+#pragma unroll
+      for (int n = 0; n < 8; ++n) {
+        const int col = nh * 64 + n * 8 + tig * 2;
+        if (which) {   // W tile [t][k]
+          *reinterpret_cast<uint32_t*>(gW + swz<256>(ta, col)) = pack_bf16(acc[n][0], acc[n][1]);
+          *reinterpret_cast<uint32_t*>(gW + swz<256>(tb, col)) = pack_bf16(acc[n][2], acc[n][3]);
+        } else {       // UT tile [v][t]
+          *reinterpret_cast<__nv_bfloat16*>(gUT + swz<128>(col, ta)) = __float2bfloat16_rn(acc[n][0]);
+          *reinterpret_cast<__nv_bfloat16*>(gUT + swz<128>(col + 1, ta)) = __float2bfloat16_rn(acc[n][1]);
+          *reinterpret_cast<__nv_bfloat16*>(gUT + swz<128>(col, tb)) = __float2bfloat16_rn(acc[n][2]);
+          *reinterpret_cast<__nv_bfloat16*>(gUT + swz<128>(col + 1, tb)) = __float2bfloat16_rn(acc[n][3]);
+        }
+      }
+    }
+  }
+}
+
+// =================================================================================================
+// state scan (forward)
+// =================================================================================================
+constexpr int SCAN_STAGES = 3;
+constexpr int SCAN_CWARPS = 8;                       // compute warps: 16 value columns each
+constexpr int SCAN_THREADS = SCAN_CWARPS * 32;
+
+struct ScanStage {
+  unsigned char W[TILE_TK], QG[TILE_TK], KG[TILE_TK], AQK[TILE_TT], UT[TILE_VT];
+  float GL[KD];
+};
+constexpr unsigned SCAN_STAGE_TX = 3 * TILE_TK + TILE_TT + TILE_VT + TILE_GL;
+
+struct ScanSmem {
+  ScanStage st[SCAN_STAGES];
+  uint64_t full[SCAN_STAGES], empty[SCAN_STAGES];
+};
+
+struct ScanParams {
+  const int* cu;
+  const int *seq_chunk_off, *chunk_seq;
+  const unsigned char *W, *UT, *KG, *QG, *AQK, *GL;
+  unsigned char *HS, *VNEWT;    // NULL unless saving for backward
+  const float* h0;
+  float* ht;
+  __nv_bfloat16* o;
+  unsigned* status;
+  int N, H;
+};
+
+__global__ void __launch_bounds__(SCAN_THREADS, 1) kda_chunk_scan_kernel(const ScanParams p) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  ScanSmem& s = *reinterpret_cast<ScanSmem*>(smem_raw);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gid = lane >> 2, tig = lane & 3;
+  const int seq = blockIdx.x / p.H, h = blockIdx.x % p.H;
+  const int c_begin = p.seq_chunk_off[seq], c_end = p.seq_chunk_off[seq + 1];
+  const int nchunks = c_end - c_begin;
+
+  if (tid == 0) {
+    for (int i = 0; i < SCAN_STAGES; ++i) {
+      mbar_init(&s.full[i], 1);
+      mbar_init(&s.empty[i], SCAN_CWARPS);
+    }
+    fence_mbar_init();
+  }
+  __syncthreads();
+
+  // Warp 0's lane 0 doubles as the producer: it streams the tiles of chunk i+2 while chunk i is computed.
+  auto issue = [&](int i) -> bool {
+    const int stg = i % SCAN_STAGES;
+    if (i >= SCAN_STAGES) {
+      if (!mbar_wait(&s.empty[stg], ((i / SCAN_STAGES) & 1) ^ 1)) return false;
+    }
+    const size_t tile = static_cast<size_t>(c_begin + i) * p.H + h;
+    ScanStage& d = s.st[stg];
+    mbar_expect_tx(&s.full[stg], SCAN_STAGE_TX);
+    bulk_g2s(d.W, p.W + tile * TILE_TK, TILE_TK, &s.full[stg]);
+    bulk_g2s(d.QG, p.QG + tile * TILE_TK, TILE_TK, &s.full[stg]);
+    bulk_g2s(d.KG, p.KG + tile * TILE_TK, TILE_TK, &s.full[stg]);
+    bulk_g2s(d.AQK, p.AQK + tile * TILE_TT, TILE_TT, &s.full[stg]);
+    bulk_g2s(d.UT, p.UT + tile * TILE_VT, TILE_VT, &s.full[stg]);
+    bulk_g2s(d.GL, p.GL + tile * TILE_GL, TILE_GL, &s.full[stg]);
+    return true;
+  };
+  if (tid == 0) {
+    for (int i = 0; i < SCAN_STAGES - 1 && i < nchunks; ++i) issue(i);
+  }
+
+  // --------------------------------- compute warps ------------------------------------------------
+  const int v0 = warp * 16;
+  float hT[16][4];   // transposed state: rows v0+gid (+8), columns nt*8 + 2 tig (+1)
+  {
+    const size_t sb = (static_cast<size_t>(seq) * p.H + h) * KD * VD;
+#pragma unroll
+    for (int nt = 0; nt < 16; ++nt) {
+      const int kk = nt * 8 + tig * 2;
+      if (p.h0) {
+        hT[nt][0] = __ldg(p.h0 + sb + static_cast<size_t>(kk) * VD + v0 + gid);
+        hT[nt][1] = __ldg(p.h0 + sb + static_cast<size_t>(kk + 1) * VD + v0 + gid);
+        hT[nt][2] = __ldg(p.h0 + sb + static_cast<size_t>(kk) * VD + v0 + gid + 8);
+        hT[nt][3] = __ldg(p.h0 + sb + static_cast<size_t>(kk + 1) * VD + v0 + gid + 8);
+      } else {
+        hT[nt][0] = hT[nt][1] = hT[nt][2] = hT[nt][3] = 0.f;
+      }
+    }
+  }
+
+  bool failed = false;
+  for (int i = 0; i < nchunks; ++i) {
+    const int stg = i % SCAN_STAGES;
+    const int c = c_begin + i;
+    if (tid == 0 && i + SCAN_STAGES - 1 < nchunks) {
+      if (!issue(i + SCAN_STAGES - 1)) atomicOr(p.status, 1u);   // consumers then time out on `full` and leave too
+    }
+    __syncwarp();
+    if (!mbar_wait(&s.full[stg], (i / SCAN_STAGES) & 1)) {
+      failed = true;
+      break;
+    }
+    const ScanStage& d = s.st[stg];
+    const ChunkInfo ci = chunk_info(p.seq_chunk_off, p.chunk_seq, p.cu, c);
+    const size_t tile = static_cast<size_t>(c) * p.H + h;
+
+    // bf16 copy of the state as A fragments (and the saved chunk-start state)
+    uint32_t hA[8][4];
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      hA[ks][0] = pack_bf16(hT[2 * ks][0], hT[2 * ks][1]);
+      hA[ks][1] = pack_bf16(hT[2 * ks][2], hT[2 * ks][3]);
+      hA[ks][2] = pack_bf16(hT[2 * ks + 1][0], hT[2 * ks + 1][1]);
+      hA[ks][3] = pack_bf16(hT[2 * ks + 1][2], hT[2 * ks + 1][3]);
+    }
+    if (p.HS) {
+      unsigned char* g = p.HS + tile * TILE_VK;
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        const int kk = ks * 16 + tig * 2;
+        *reinterpret_cast<uint32_t*>(g + swz<256>(v0 + gid, kk)) = hA[ks][0];
+        *reinterpret_cast<uint32_t*>(g + swz<256>(v0 + gid + 8, kk)) = hA[ks][1];
+        *reinterpret_cast<uint32_t*>(g + swz<256>(v0 + gid, kk + 8)) = hA[ks][2];
+        *reinterpret_cast<uint32_t*>(g + swz<256>(v0 + gid + 8, kk + 8)) = hA[ks][3];
+      }
+    }
+
+    // v_new^T = u^T - h^T w^T        (rows: value columns of this warp; columns: tokens)
+    float vn[8][4];
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+      const int t = nt * 8 + tig * 2;
+      const float2 ua = unpack_bf16(*reinterpret_cast<const uint32_t*>(d.UT + swz<128>(v0 + gid, t)));
+      const float2 ub = unpack_bf16(*reinterpret_cast<const uint32_t*>(d.UT + swz<128>(v0 + gid + 8, t)));
+      vn[nt][0] = ua.x; vn[nt][1] = ua.y; vn[nt][2] = ub.x; vn[nt][3] = ub.y;
+    }
+    float oT[8][4];
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) oT[nt][0] = oT[nt][1] = oT[nt][2] = oT[nt][3] = 0.f;
+    const uint32_t wbase = smem_u32(d.W), qbase = smem_u32(d.QG);
+    const int brow = (lane & 7) + ((lane >> 4) << 3), bcol = ((lane >> 3) & 1) << 3;   // non-transposed B tiles
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      uint32_t hneg[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) hneg[e] = hA[ks][e] ^ 0x80008000u;
+#pragma unroll
+      for (int np = 0; np < 4; ++np) {
+        uint32_t b[4];
+        ldsm_x4(b, wbase + swz<256>(np * 16 + brow, ks * 16 + bcol));
+        mma16816(vn[2 * np], hneg, b[0], b[1]);
+        mma16816(vn[2 * np + 1], hneg, b[2], b[3]);
+        ldsm_x4(b, qbase + swz<256>(np * 16 + brow, ks * 16 + bcol));
+        mma16816(oT[2 * np], hA[ks], b[0], b[1]);
+        mma16816(oT[2 * np + 1], hA[ks], b[2], b[3]);
+      }
+    }
+    // v_new as A fragments (and the saved copy)
+    uint32_t vA[4][4];
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+      vA[ks][0] = pack_bf16(vn[2 * ks][0], vn[2 * ks][1]);
+      vA[ks][1] = pack_bf16(vn[2 * ks][2], vn[2 * ks][3]);
+      vA[ks][2] = pack_bf16(vn[2 * ks + 1][0], vn[2 * ks + 1][1]);
+      vA[ks][3] = pack_bf16(vn[2 * ks + 1][2], vn[2 * ks + 1][3]);
+    }
+    if (p.VNEWT) {
+      unsigned char* g = p.VNEWT + tile * TILE_VT;
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) {
+        const int t = ks * 16 + tig * 2;
+        *reinterpret_cast<uint32_t*>(g + swz<128>(v0 + gid, t)) = vA[ks][0];
+        *reinterpret_cast<uint32_t*>(g + swz<128>(v0 + gid + 8, t)) = vA[ks][1];
+        *reinterpret_cast<uint32_t*>(g + swz<128>(v0 + gid, t + 8)) = vA[ks][2];
+        *reinterpret_cast<uint32_t*>(g + swz<128>(v0 + gid + 8, t + 8)) = vA[ks][3];
+      }
+    }
+    // o^T += v_new^T Aqk^T
+    const uint32_t abase = smem_u32(d.AQK);
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+#pragma unroll
+      for (int np = 0; np < 4; ++np) {
+        uint32_t b[4];
+        ldsm_x4(b, abase + swz<128>(np * 16 + brow, ks * 16 + bcol));
+        mma16816(oT[2 * np], vA[ks], b[0], b[1]);
+        mma16816(oT[2 * np + 1], vA[ks], b[2], b[3]);
+      }
+    }
+    // h^T = h^T Diag(Gam_last) + v_new^T kg
+#pragma unroll
+    for (int nt = 0; nt < 16; ++nt) {
+      const float2 gl = *reinterpret_cast<const float2*>(&d.GL[nt * 8 + tig * 2]);
+      hT[nt][0] *= gl.x; hT[nt][1] *= gl.y; hT[nt][2] *= gl.x; hT[nt][3] *= gl.y;
+    }
+    const uint32_t kbase = smem_u32(d.KG);
+    const int trow = (lane & 7) + (((lane >> 3) & 1) << 3), tcol = (lane >> 4) << 3;   // transposed B tiles
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+#pragma unroll
+      for (int np = 0; np < 8; ++np) {
+        uint32_t b[4];
+        ldsm_x4_t(b, kbase + swz<256>(ks * 16 + trow, np * 16 + tcol));
+        mma16816(hT[2 * np], vA[ks], b[0], b[1]);
+        mma16816(hT[2 * np + 1], vA[ks], b[2], b[3]);
+      }
+    }
+    // o: stage this warp's [64 t][16 v] slab in its own (now dead) rows of the UT tile, then 16-byte stores
+    {
+      __syncwarp();
+      __nv_bfloat16* slab = reinterpret_cast<__nv_bfloat16*>(const_cast<unsigned char*>(d.UT) + static_cast<size_t>(v0) * (C * 2));
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        const int t = nt * 8 + tig * 2;
+        slab[t * 16 + gid] = __float2bfloat16_rn(oT[nt][0]);
+        slab[(t + 1) * 16 + gid] = __float2bfloat16_rn(oT[nt][1]);
+        slab[t * 16 + gid + 8] = __float2bfloat16_rn(oT[nt][2]);
+        slab[(t + 1) * 16 + gid + 8] = __float2bfloat16_rn(oT[nt][3]);
+      }
+      __syncwarp();
+#pragma unroll
+      for (int it = 0; it < 4; ++it) {
+        const int pc = lane + 32 * it, t = pc >> 1, half = pc & 1;
+        if (t < ci.len) {
+          const uint4 val = *reinterpret_cast<const uint4*>(&slab[t * 16 + half * 8]);
+          *reinterpret_cast<uint4*>(p.o + (static_cast<size_t>(ci.tok0 + t) * p.H + h) * VD + v0 + half * 8) = val;
+        }
+      }
+      __syncwarp();
+    }
+    fence_proxy_async();   // this warp's generic-proxy writes to the stage precede the next bulk copy into it
+    if (lane == 0) mbar_arrive(&s.empty[stg]);
+  }
+  if (failed && lane == 0) atomicOr(p.status, 2u);
+
+  if (p.ht && !failed) {
+    const size_t sb = (static_cast<size_t>(seq) * p.H + h) * KD * VD;
+#pragma unroll
+    for (int nt = 0; nt < 16; ++nt) {
+      const int kk = nt * 8 + tig * 2;
+      p.ht[sb + static_cast<size_t>(kk) * VD + v0 + gid] = hT[nt][0];
+      p.ht[sb + static_cast<size_t>(kk + 1) * VD + v0 + gid] = hT[nt][1];
+      p.ht[sb + static_cast<size_t>(kk) * VD + v0 + gid + 8] = hT[nt][2];
+      p.ht[sb + static_cast<size_t>(kk + 1) * VD + v0 + gid + 8] = hT[nt][3];
+    }
+  }
+}
+
+static std::once_flag g_attr_once;
+static cudaError_t g_attr_err = cudaSuccess;
+
+static cudaError_t set_attrs() {
+  std::call_once(g_attr_once, [] {
+    cudaError_t e = cudaFuncSetAttribute(kda_chunk_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(sizeof(PrepSmem)));
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(kda_chunk_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(sizeof(ScanSmem)));
+    g_attr_err = e;
+  });
+  return g_attr_err;
+}
+
+int validate_chunk_args(const kda_chunk_args& a, bool backward) {
+  if (a.tokens < 0 || a.N < 0 || a.H <= 0) return KDA_E_SHAPE;
+  if (a.K != KD || a.V != VD) return KDA_E_SHAPE;
+  if (a.io_dtype != KDA_BF16) return KDA_E_DTYPE;
+  if (a.tokens / C + a.N > 0x3fffffffLL) return KDA_E_SHAPE;
+  if (a.tokens == 0 || a.N == 0) return KDA_OK;
+  if (!a.q || !a.k || !a.v || !a.g || !a.beta || !a.cu_seqlens || !a.o || !a.workspace) return KDA_E_NULL;
+  uintptr_t bits = reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.k) | reinterpret_cast<uintptr_t>(a.v) |
+                   reinterpret_cast<uintptr_t>(a.g) | reinterpret_cast<uintptr_t>(a.o) | reinterpret_cast<uintptr_t>(a.h0) |
+                   reinterpret_cast<uintptr_t>(a.ht);
+  if (backward) {
+    if (!a.d_o || !a.dq || !a.dk || !a.dv || !a.dg || !a.dbeta || !a.bwd_workspace) return KDA_E_NULL;
+    bits |= reinterpret_cast<uintptr_t>(a.d_o) | reinterpret_cast<uintptr_t>(a.dq) | reinterpret_cast<uintptr_t>(a.dk) |
+            reinterpret_cast<uintptr_t>(a.dv) | reinterpret_cast<uintptr_t>(a.dg) | reinterpret_cast<uintptr_t>(a.d_ht) |
+            reinterpret_cast<uintptr_t>(a.dh0) | (reinterpret_cast<uintptr_t>(a.bwd_workspace) & 255u);
+  }
+  if (bits & 15u) return KDA_E_ALIGN;
+  if (reinterpret_cast<uintptr_t>(a.workspace) & 255u) return KDA_E_ALIGN;
+  return KDA_OK;
+}
+
+}  // namespace kda
+
+extern "C" int64_t kda_chunk_max_chunks(int64_t tokens, int32_t N) { return tokens / kda::C + N; }
+
+extern "C" size_t kda_chunk_workspace_bytes(int64_t tokens, int32_t N, int32_t H, int32_t K, int32_t V, int32_t save) {
+  (void)K; (void)V;
+  return kda::carve_ws(nullptr, nullptr, tokens, N, H, save != 0).fwd_bytes;
+}
+
+extern "C" size_t kda_chunk_bwd_workspace_bytes(int64_t tokens, int32_t N, int32_t H, int32_t K, int32_t V) {
+  (void)K; (void)V;
+  return kda::carve_ws(nullptr, nullptr, tokens, N, H, true).bwd_bytes;
+}
+
+extern "C" int kda_chunk_fwd(const kda_chunk_args* args, void* stream) {
+  using namespace kda;
+  if (!args) return KDA_E_NULL;
+  const kda_chunk_args& a = *args;
+  int rc = validate_chunk_args(a, false);
+  if (rc != KDA_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (a.N == 0) return KDA_OK;
+  if (a.tokens == 0) {
+    if (a.ht && a.ht != a.h0) {
+      const size_t bytes = static_cast<size_t>(a.N) * a.H * KD * VD * sizeof(float);
+      return static_cast<int>(a.h0 ? cudaMemcpyAsync(a.ht, a.h0, bytes, cudaMemcpyDeviceToDevice, st)
+                                   : cudaMemsetAsync(a.ht, 0, bytes, st));
+    }
+    return KDA_OK;
+  }
+  const bool save = a.save_for_backward != 0;
+  ChunkWs w = carve_ws(static_cast<unsigned char*>(a.workspace), nullptr, a.tokens, a.N, a.H, save);
+  if (a.workspace_bytes < w.fwd_bytes) return KDA_E_WORKSPACE;
+  cudaError_t e = set_attrs();
+  if (e != cudaSuccess) return static_cast<int>(e);
+  const int NTmax = static_cast<int>(a.tokens / C + a.N);
+
+  kda_chunk_tables_kernel<<<1, 1024, 0, st>>>(a.cu_seqlens, a.N, w.seq_chunk_off, w.chunk_seq, w.status);
+  if ((e = cudaGetLastError()) != cudaSuccess) return static_cast<int>(e);
+
+  PrepParams pp{};
+  pp.q = static_cast<const __nv_bfloat16*>(a.q);
+  pp.k = static_cast<const __nv_bfloat16*>(a.k);
+  pp.v = static_cast<const __nv_bfloat16*>(a.v);
+  pp.g = a.g; pp.beta = a.beta; pp.cu = a.cu_seqlens;
+  pp.seq_chunk_off = w.seq_chunk_off; pp.chunk_seq = w.chunk_seq;
+  pp.W = w.W; pp.UT = w.UT; pp.KG = w.KG; pp.QG = w.QG; pp.AQK = w.AQK; pp.GL = w.GL; pp.TI = save ? w.TI : nullptr;
+  pp.N = a.N; pp.H = a.H; pp.use_l2norm = a.use_qk_l2norm; pp.scale = a.scale;
+  kda_chunk_prepare_kernel<<<dim3(NTmax, a.H), 256, sizeof(PrepSmem), st>>>(pp);
+  if ((e = cudaGetLastError()) != cudaSuccess) return static_cast<int>(e);
+
+  ScanParams sp{};
+  sp.cu = a.cu_seqlens; sp.seq_chunk_off = w.seq_chunk_off; sp.chunk_seq = w.chunk_seq;
+  sp.W = w.W; sp.UT = w.UT; sp.KG = w.KG; sp.QG = w.QG; sp.AQK = w.AQK; sp.GL = w.GL;
+  sp.HS = save ? w.HS : nullptr; sp.VNEWT = save ? w.VNEWT : nullptr;
+  sp.h0 = a.h0; sp.ht = a.ht; sp.o = static_cast<__nv_bfloat16*>(a.o); sp.status = w.status;
+  sp.N = a.N; sp.H = a.H;
+  kda_chunk_scan_kernel<<<a.N * a.H, SCAN_THREADS, sizeof(ScanSmem), st>>>(sp);
+  return static_cast<int>(cudaGetLastError());
+}

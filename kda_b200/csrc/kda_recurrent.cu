@@ -1,0 +1,207 @@
+// Token-recurrent KDA forward: decode (one token per sequence, HBM-bound) and exact fp32 scans.
+//
+// One warp owns one (sequence, head, V-slice) and keeps its [K x VS] slice of the fp32 state in
+// registers for the whole call.  Lanes are arranged as RG row groups x CL column lanes; a lane holds
+// rows rg, rg+RG, ... and four consecutive V columns, so every state load/store is a 128-bit access
+// and a warp-wide access covers RG rows x (VS*4) contiguous bytes.  Both reductions over K (S^T k for the
+// delta rule, S^T q for the read-out) are register sums followed by log2(RG) shuffles: no shared-memory
+// reduction, no block barrier, warps are independent.
+// Per token (order as in fla/ops/kda/fused_recurrent.py:146-192): S *= exp(g); v' = beta (v - S^T k);
+// S += k v'^T; o = scale S^T q.
+#include "kda_common.cuh"
+
+namespace kda {
+
+template <typename IO> struct IoTraits;
+template <> struct IoTraits<float> {
+  static __device__ __forceinline__ float ld(const float* p) { return __ldg(p); }
+  static __device__ __forceinline__ void st4(float* p, float4 x) { *reinterpret_cast<float4*>(p) = x; }
+  static __device__ __forceinline__ float4 ld4(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
+};
+template <> struct IoTraits<__nv_bfloat16> {
+  static __device__ __forceinline__ float ld(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+  static __device__ __forceinline__ void st4(__nv_bfloat16* p, float4 x) {
+    uint2 u = make_uint2(pack_bf16(x.x, x.y), pack_bf16(x.z, x.w));
+    *reinterpret_cast<uint2*>(p) = u;
+  }
+  static __device__ __forceinline__ float4 ld4(const __nv_bfloat16* p) {
+    uint2 u = __ldg(reinterpret_cast<const uint2*>(p));
+    float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y);
+    return make_float4(a.x, a.y, b.x, b.y);
+  }
+};
+
+constexpr int REC_WARPS = 4;
+
+template <typename IO, int K, int VS>
+__global__ void __launch_bounds__(REC_WARPS * 32) kda_recurrent_kernel(const kda_recurrent_args a) {
+  constexpr int CL = VS / 4;      // lanes across the V slice (4 columns each)
+  constexpr int RG = 32 / CL;     // row groups
+  constexpr int R = K / RG;       // state rows per lane
+  constexpr int E = K / 32;       // q/k/g elements staged per lane
+  static_assert(K % RG == 0 && K % 32 == 0, "unsupported K");
+
+  __shared__ float s_k[REC_WARPS][K], s_q[REC_WARPS][K], s_eg[REC_WARPS][K];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nvs = a.V / VS;
+  const long long wid = static_cast<long long>(blockIdx.x) * REC_WARPS + warp;
+  const long long total = static_cast<long long>(a.N) * a.H * nvs;
+  if (wid >= total) return;   // whole warps leave; only __syncwarp is used below
+  const int vs = static_cast<int>(wid % nvs);
+  const int h = static_cast<int>((wid / nvs) % a.H);
+  const int n = static_cast<int>(wid / (static_cast<long long>(nvs) * a.H));
+  const int cg = lane % CL, rg = lane / CL;
+  const int col = vs * VS + cg * 4;
+
+  long long bos, eos;
+  if (a.cu_seqlens) {
+    bos = a.cu_seqlens[n];
+    eos = a.cu_seqlens[n + 1];
+  } else {
+    bos = static_cast<long long>(n) * a.T;
+    eos = bos + a.T;
+  }
+  const long long slot = a.state_indices ? a.state_indices[n] : n;
+  const size_t sbase = (static_cast<size_t>(slot) * a.H + h) * K * a.V + col;
+
+  float4 S[R];
+  if (a.h0) {
+#pragma unroll
+    for (int i = 0; i < R; ++i)
+      S[i] = __ldcs(reinterpret_cast<const float4*>(a.h0 + sbase + static_cast<size_t>(rg + RG * i) * a.V));
+  } else {
+#pragma unroll
+    for (int i = 0; i < R; ++i) S[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+
+  const IO* qp = static_cast<const IO*>(a.q);
+  const IO* kp = static_cast<const IO*>(a.k);
+  const IO* vp = static_cast<const IO*>(a.v);
+  IO* op = static_cast<IO*>(a.o);
+
+  for (long long t = bos; t < eos; ++t) {
+    const size_t rowk = (static_cast<size_t>(t) * a.H + h) * K + lane * E;
+    float qf[E], kf[E], gf[E];
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      qf[e] = IoTraits<IO>::ld(qp + rowk + e);
+      kf[e] = IoTraits<IO>::ld(kp + rowk + e);
+      gf[e] = __ldg(a.g + rowk + e);
+    }
+    float qs = a.scale;
+    if (a.use_qk_l2norm) {
+      float sq = 0.f, sk = 0.f;
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        sq += qf[e] * qf[e];
+        sk += kf[e] * kf[e];
+      }
+      sq = warp_sum(sq);
+      sk = warp_sum(sk);
+      qs *= rsqrtf(sq + L2NORM_EPS);
+      const float ks = rsqrtf(sk + L2NORM_EPS);
+#pragma unroll
+      for (int e = 0; e < E; ++e) kf[e] *= ks;
+    }
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      s_k[warp][lane * E + e] = kf[e];
+      s_q[warp][lane * E + e] = qf[e] * qs;
+      s_eg[warp][lane * E + e] = expf(gf[e]);
+    }
+    const float beta = __ldg(a.beta + static_cast<size_t>(t) * a.H + h);
+    const float4 vt = IoTraits<IO>::ld4(vp + (static_cast<size_t>(t) * a.H + h) * a.V + col);
+    __syncwarp();
+
+    float4 hk = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      const int r = rg + RG * i;
+      const float eg = s_eg[warp][r], kk = s_k[warp][r];
+      S[i].x *= eg; S[i].y *= eg; S[i].z *= eg; S[i].w *= eg;
+      hk.x += kk * S[i].x; hk.y += kk * S[i].y; hk.z += kk * S[i].z; hk.w += kk * S[i].w;
+    }
+#pragma unroll
+    for (int off = CL; off < 32; off <<= 1) {
+      hk.x += __shfl_xor_sync(0xffffffffu, hk.x, off);
+      hk.y += __shfl_xor_sync(0xffffffffu, hk.y, off);
+      hk.z += __shfl_xor_sync(0xffffffffu, hk.z, off);
+      hk.w += __shfl_xor_sync(0xffffffffu, hk.w, off);
+    }
+    const float4 dv = make_float4(beta * (vt.x - hk.x), beta * (vt.y - hk.y), beta * (vt.z - hk.z), beta * (vt.w - hk.w));
+    float4 oa = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      const int r = rg + RG * i;
+      const float kk = s_k[warp][r], qq = s_q[warp][r];
+      S[i].x += kk * dv.x; S[i].y += kk * dv.y; S[i].z += kk * dv.z; S[i].w += kk * dv.w;
+      oa.x += qq * S[i].x; oa.y += qq * S[i].y; oa.z += qq * S[i].z; oa.w += qq * S[i].w;
+    }
+#pragma unroll
+    for (int off = CL; off < 32; off <<= 1) {
+      oa.x += __shfl_xor_sync(0xffffffffu, oa.x, off);
+      oa.y += __shfl_xor_sync(0xffffffffu, oa.y, off);
+      oa.z += __shfl_xor_sync(0xffffffffu, oa.z, off);
+      oa.w += __shfl_xor_sync(0xffffffffu, oa.w, off);
+    }
+    if (rg == 0) IoTraits<IO>::st4(op + (static_cast<size_t>(t) * a.H + h) * a.V + col, oa);
+    __syncwarp();
+  }
+
+  if (a.ht) {
+#pragma unroll
+    for (int i = 0; i < R; ++i)
+      __stcs(reinterpret_cast<float4*>(a.ht + sbase + static_cast<size_t>(rg + RG * i) * a.V), S[i]);
+  }
+}
+
+template <typename IO, int K, int VS>
+static int launch_rec(const kda_recurrent_args& a, cudaStream_t st) {
+  const long long total = static_cast<long long>(a.N) * a.H * (a.V / VS);
+  const long long blocks = (total + REC_WARPS - 1) / REC_WARPS;
+  if (blocks <= 0) return KDA_OK;
+  if (blocks > 0x7fffffffLL) return KDA_E_SHAPE;
+  kda_recurrent_kernel<IO, K, VS><<<static_cast<unsigned>(blocks), REC_WARPS * 32, 0, st>>>(a);
+  return static_cast<int>(cudaGetLastError());
+}
+
+template <typename IO>
+static int dispatch_rec(const kda_recurrent_args& a, cudaStream_t st) {
+  switch (a.K) {
+    case 32: return launch_rec<IO, 32, 32>(a, st);
+    case 64: return launch_rec<IO, 64, 32>(a, st);
+    case 128: return launch_rec<IO, 128, 32>(a, st);
+    case 256: return (a.V % 32 == 0) ? launch_rec<IO, 256, 16>(a, st) : KDA_E_SHAPE;
+    default: return KDA_E_SHAPE;
+  }
+}
+
+}  // namespace kda
+
+extern "C" int kda_recurrent_fwd(const kda_recurrent_args* args, void* stream) {
+  if (!args) return KDA_E_NULL;
+  const kda_recurrent_args& a = *args;
+  if (a.N < 0 || a.H <= 0 || a.V <= 0 || a.V % 32 != 0 || a.tokens < 0) return KDA_E_SHAPE;
+  if (a.N == 0 || a.tokens == 0) {
+    // nothing to scan; with distinct h0/ht buffers the final state is the initial one
+    if (a.N > 0 && a.ht && a.ht != a.h0) {
+      const size_t bytes = static_cast<size_t>(a.N) * a.H * a.K * a.V * sizeof(float);
+      cudaError_t e = a.h0 ? cudaMemcpyAsync(a.ht, a.h0, bytes, cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream))
+                           : cudaMemsetAsync(a.ht, 0, bytes, static_cast<cudaStream_t>(stream));
+      return static_cast<int>(e);
+    }
+    return KDA_OK;
+  }
+  if (!a.q || !a.k || !a.v || !a.g || !a.beta || !a.o) return KDA_E_NULL;
+  if (!a.cu_seqlens && static_cast<int64_t>(a.N) * a.T != a.tokens) return KDA_E_SHAPE;
+  const uintptr_t bits = reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.k) |
+                         reinterpret_cast<uintptr_t>(a.v) | reinterpret_cast<uintptr_t>(a.g) |
+                         reinterpret_cast<uintptr_t>(a.o) | reinterpret_cast<uintptr_t>(a.h0) |
+                         reinterpret_cast<uintptr_t>(a.ht);
+  if (bits & 15u) return KDA_E_ALIGN;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (a.io_dtype == KDA_BF16) return kda::dispatch_rec<__nv_bfloat16>(a, st);
+  if (a.io_dtype == KDA_FP32) return kda::dispatch_rec<float>(a, st);
+  return KDA_E_DTYPE;
+}

@@ -1,0 +1,264 @@
+"""Operator front end: `chunk_kda` (prefill / training, autograd) and `fused_recurrent_kda` (decode).
+
+Signatures, argument meaning and error behaviour mirror flash-linear-attention 0.5.1
+(`fla/ops/kda/chunk.py:167-411`, `fla/ops/kda/fused_recurrent.py:229-452`); everything below the
+Python signature runs in hand-written sm_100a CUDA kernels reached through the C ABI of
+`include/kda_b200.h`.  PyTorch only owns device memory and streams here.  There is no fallback:
+CPU tensors, a missing shared library or an unsupported option raise.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import torch
+
+from . import _lib
+
+_DT = {torch.bfloat16: _lib.KDA_BF16, torch.float32: _lib.KDA_FP32}
+CHUNK = 64
+
+
+def _ptr(t):
+    return C.c_void_p(t.data_ptr()) if t is not None else C.c_void_p(0)
+
+
+def _stream(device) -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _unsupported(name, value, default):
+    if value is not default and value != default:
+        raise NotImplementedError(f"kda_b200: `{name}` is not supported by this implementation")
+
+
+def _check_common(q, k, v, g, beta, initial_state, cu_seqlens):
+    if not q.is_cuda:
+        raise RuntimeError("kda_b200 runs on CUDA (sm_100a) tensors only; there is no CPU path")
+    B, T, H, K = q.shape
+    assert q.shape == k.shape, f"q and k must have the same shape, got q={q.shape} vs k={k.shape}"
+    HV, V = v.shape[2], v.shape[3]
+    if HV != H:
+        raise NotImplementedError("kda_b200: grouped value heads (HV > H) are not supported")
+    assert K <= 256, f"Currently we only support key headdim <=256 for KDA, got {K}."
+    assert g.shape == (B, T, HV, K), f"g must have shape [B, T, HV, K]={[B, T, HV, K]}, got {list(g.shape)}"
+    assert beta.shape == (B, T, HV), f"beta must have shape [B, T, HV]={[B, T, HV]}, got {list(beta.shape)}"
+    if cu_seqlens is not None:
+        if B != 1:
+            raise ValueError(
+                f"The batch size is expected to be 1 rather than {q.shape[0]} when using `cu_seqlens`."
+                f"Please flatten variable-length inputs before processing.")
+        if initial_state is not None and initial_state.shape[0] != len(cu_seqlens) - 1:
+            raise ValueError(
+                f"The number of initial states is expected to be equal to the number of input sequences, "
+                f"i.e., {len(cu_seqlens) - 1} rather than {initial_state.shape[0]}.")
+    if initial_state is not None:
+        assert initial_state.dtype == torch.float32, "initial_state must be in float32."
+    if q.dtype not in _DT or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise NotImplementedError(f"kda_b200: q, k, v must share dtype bfloat16 or float32, got {q.dtype}")
+    return B, T, H, K, V
+
+
+_cu_cache: dict = {}
+
+
+def _fixed_cu_seqlens(B: int, T: int, device) -> torch.Tensor:
+    key = (B, T, str(device))
+    cu = _cu_cache.get(key)
+    if cu is None:
+        cu = torch.arange(0, (B + 1) * T, T, dtype=torch.int32, device=device) if T > 0 else \
+            torch.zeros(B + 1, dtype=torch.int32, device=device)
+        if len(_cu_cache) > 64:
+            _cu_cache.clear()
+        _cu_cache[key] = cu
+    return cu
+
+
+def _as_i32(cu: torch.Tensor, device) -> torch.Tensor:
+    if cu.dtype != torch.int32 or cu.device != device:
+        cu = cu.to(device=device, dtype=torch.int32)
+    return cu.contiguous()
+
+
+# =================================================================================================
+# decode / token-recurrent forward
+# =================================================================================================
+
+def fused_recurrent_kda_fwd(q, k, v, g, beta, scale, initial_state=None, inplace_final_state=False,
+                            output_final_state=True, use_qk_l2norm_in_kernel=False, cu_seqlens=None,
+                            ssm_state_indices=None):
+    """Lower-level entry (fla/ops/kda/fused_recurrent.py:229-325).  With `inplace_final_state` the
+    kernel writes the final state over `initial_state` (optionally through `ssm_state_indices`, one
+    state slot per sequence) and returns that tensor."""
+    B, T, H, K, V = _check_common(q, k, v, g, beta, None, cu_seqlens)
+    dev = q.device
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    g = g.contiguous().float()
+    beta = beta.contiguous().float()
+    N = B if cu_seqlens is None else len(cu_seqlens) - 1
+    cu = _as_i32(cu_seqlens, dev) if cu_seqlens is not None else None
+    h0 = initial_state.contiguous() if initial_state is not None else None
+    if inplace_final_state:
+        if h0 is None or h0.data_ptr() != initial_state.data_ptr():
+            raise ValueError("inplace_final_state needs a contiguous fp32 initial_state")
+        ht = h0
+    elif output_final_state:
+        ht = torch.empty(N, H, K, V, dtype=torch.float32, device=dev)
+    else:
+        ht = None
+    idx = None
+    if ssm_state_indices is not None:
+        if not inplace_final_state:
+            raise ValueError("ssm_state_indices requires inplace_final_state=True")
+        idx = ssm_state_indices.to(device=dev, dtype=torch.int32).contiguous()
+    o = torch.empty_like(v)
+    args = _lib.RecurrentArgs(
+        q=_ptr(q), k=_ptr(k), v=_ptr(v), g=_ptr(g), beta=_ptr(beta), h0=_ptr(h0), ht=_ptr(ht), o=_ptr(o),
+        cu_seqlens=_ptr(cu), state_indices=_ptr(idx), tokens=B * T, N=N, T=T, H=H, K=K, V=V,
+        io_dtype=_DT[q.dtype], use_qk_l2norm=int(bool(use_qk_l2norm_in_kernel)), scale=float(scale))
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().kda_recurrent_fwd(C.byref(args), _stream(dev)), "kda_recurrent_fwd")
+    return o, ht
+
+
+@torch.no_grad()
+def fused_recurrent_kda(q, k, v, g, beta, A_log=None, dt_bias=None, scale=None, initial_state=None,
+                        output_final_state=False, use_qk_l2norm_in_kernel=False, use_gate_in_kernel=False,
+                        use_beta_sigmoid_in_kernel=False, lower_bound=None, cu_seqlens=None,
+                        transpose_state_layout=False, **kwargs):
+    """Drop-in for fla.ops.kda.fused_recurrent_kda (fla/ops/kda/fused_recurrent.py:329-452): forward only.
+    q,k [B,T,H,K]; v [B,T,H,V]; g [B,T,H,K] log-decay; beta [B,T,H]; initial_state [N,H,K,V] fp32.
+    Returns (o, final_state or None)."""
+    _unsupported("use_gate_in_kernel", use_gate_in_kernel, False)
+    _unsupported("use_beta_sigmoid_in_kernel", use_beta_sigmoid_in_kernel, False)
+    _unsupported("transpose_state_layout", transpose_state_layout, False)
+    _unsupported("lower_bound", lower_bound, None)
+    if A_log is not None or dt_bias is not None:
+        raise NotImplementedError("kda_b200: the fused gate activation (A_log, dt_bias) is not supported")
+    if "use_qk_l2norm" in kwargs:
+        use_qk_l2norm_in_kernel = kwargs.pop("use_qk_l2norm")
+    _check_common(q, k, v, g, beta, initial_state, cu_seqlens)
+    if scale is None:
+        scale = k.shape[-1] ** -0.5
+    return fused_recurrent_kda_fwd(q, k, v, g, beta, scale, initial_state, False, output_final_state,
+                                   use_qk_l2norm_in_kernel, cu_seqlens)
+
+
+# =================================================================================================
+# chunked forward / backward
+# =================================================================================================
+
+def _chunk_args(q, k, v, g, beta, h0, cu, o, ht, ws, N, H, K, V, tokens, l2, save, scale, **extra):
+    a = _lib.ChunkArgs(
+        q=_ptr(q), k=_ptr(k), v=_ptr(v), g=_ptr(g), beta=_ptr(beta), h0=_ptr(h0), cu_seqlens=_ptr(cu),
+        o=_ptr(o), ht=_ptr(ht), workspace=_ptr(ws), workspace_bytes=ws.numel() if ws is not None else 0,
+        tokens=tokens, N=N, H=H, K=K, V=V, io_dtype=_lib.KDA_BF16, use_qk_l2norm=int(l2),
+        save_for_backward=int(save), scale=float(scale))
+    for name, t in extra.items():
+        if name == "bwd_ws":
+            a.bwd_workspace = _ptr(t)
+            a.bwd_workspace_bytes = t.numel()
+        else:
+            setattr(a, name, _ptr(t))
+    return a
+
+
+class ChunkKDAFunction(torch.autograd.Function):
+    """bf16 chunked path.  Saved for backward: the inputs plus one workspace buffer in which the forward
+    kernels left the per-chunk tiles the backward kernels read (fla/ops/kda/chunk.py:22-162 keeps the
+    inputs and recomputes; with 180 GB of HBM the tiles are kept instead)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, g, beta, scale, initial_state, output_final_state, use_l2norm, cu_seqlens):
+        B, T, H, K = q.shape
+        V = v.shape[-1]
+        dev = q.device
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        g32 = g.contiguous().float()
+        beta32 = beta.contiguous().float()
+        h0 = initial_state.contiguous() if initial_state is not None else None
+        if cu_seqlens is None:
+            N, cu = B, _fixed_cu_seqlens(B, T, dev)
+        else:
+            cu = _as_i32(cu_seqlens, dev)
+            N = cu.numel() - 1
+        tokens = B * T
+        need_grad = any(ctx.needs_input_grad)
+        lib = _lib.load()
+        ws = torch.empty(lib.kda_chunk_workspace_bytes(tokens, N, H, K, V, int(need_grad)), dtype=torch.uint8, device=dev)
+        o = torch.empty_like(v)
+        ht = torch.empty(N, H, K, V, dtype=torch.float32, device=dev) if output_final_state else None
+        args = _chunk_args(q, k, v, g32, beta32, h0, cu, o, ht, ws, N, H, K, V, tokens, use_l2norm, need_grad, scale)
+        with torch.cuda.device(dev):
+            _lib.check(lib.kda_chunk_fwd(C.byref(args), _stream(dev)), "kda_chunk_fwd")
+        if need_grad:
+            ctx.save_for_backward(q, k, v, g32, beta32, h0, cu, ws)
+            ctx.meta = (N, H, K, V, tokens, use_l2norm, scale, g.dtype, beta.dtype, initial_state is not None)
+        return o, ht
+
+    @staticmethod
+    def backward(ctx, do, dht):
+        q, k, v, g32, beta32, h0, cu, ws = ctx.saved_tensors
+        N, H, K, V, tokens, use_l2norm, scale, g_dtype, beta_dtype, has_h0 = ctx.meta
+        dev = q.device
+        lib = _lib.load()
+        do = do.contiguous()
+        dht = dht.contiguous().float() if dht is not None else None
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        dg = torch.empty_like(g32)
+        dbeta = torch.empty_like(beta32)
+        dh0 = torch.empty(N, H, K, V, dtype=torch.float32, device=dev) if has_h0 else None
+        bws = torch.empty(lib.kda_chunk_bwd_workspace_bytes(tokens, N, H, K, V), dtype=torch.uint8, device=dev)
+        args = _chunk_args(q, k, v, g32, beta32, h0, cu, None, None, ws, N, H, K, V, tokens, use_l2norm, True, scale,
+                           d_o=do, d_ht=dht, dq=dq, dk=dk, dv=dv, dg=dg, dbeta=dbeta, dh0=dh0, bwd_ws=bws)
+        with torch.cuda.device(dev):
+            _lib.check(lib.kda_chunk_bwd(C.byref(args), _stream(dev)), "kda_chunk_bwd")
+        return dq, dk, dv, dg.to(g_dtype), dbeta.to(beta_dtype), None, dh0, None, None, None
+
+
+@torch.compiler.disable
+def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False,
+              use_qk_l2norm_in_kernel=False, use_gate_in_kernel=False, use_beta_sigmoid_in_kernel=False,
+              cu_seqlens=None, cu_seqlens_cpu=None, safe_gate=False, lower_bound=None, disable_recompute=False,
+              return_intermediate_states=False, cp_context=None, transpose_state_layout=False, **kwargs):
+    """Drop-in for fla.ops.kda.chunk_kda (fla/ops/kda/chunk.py:167-411).
+
+    q, k [B,T,H,K]; v [B,T,H,V]; g [B,T,H,K] log-space decay (already activated); beta [B,T,H]
+    (already sigmoid-ed); initial_state [N,H,K,V] fp32; cu_seqlens [N+1] with B == 1.
+    Returns (o, final_state or None); differentiable w.r.t. q, k, v, g, beta, initial_state.
+
+    bf16 inputs with K = V = 128 take the chunked tensor-core kernels.  float32 inputs take the exact
+    token-recurrent fp32 kernel (forward only).  `safe_gate` and `disable_recompute` only select
+    faster variants upstream and are accepted as no-ops; options that change results raise.
+    """
+    _unsupported("use_gate_in_kernel", use_gate_in_kernel, False)
+    _unsupported("use_beta_sigmoid_in_kernel", use_beta_sigmoid_in_kernel, False)
+    _unsupported("return_intermediate_states", return_intermediate_states, False)
+    _unsupported("transpose_state_layout", transpose_state_layout, False)
+    _unsupported("cp_context", cp_context, None)
+    _unsupported("lower_bound", lower_bound, None)
+    if "use_qk_l2norm" in kwargs:
+        use_qk_l2norm_in_kernel = kwargs.pop("use_qk_l2norm")
+    chunk_size = kwargs.pop("chunk_size", 64)
+    if chunk_size not in (32, 64):
+        raise ValueError(f"`chunk_size` must be either 32 or 64 for KDA, got {chunk_size}.")
+    if chunk_size != CHUNK:
+        raise NotImplementedError("kda_b200: only chunk_size=64 is implemented")
+    if kwargs.get("A_log") is not None or kwargs.get("dt_bias") is not None:
+        raise NotImplementedError("kda_b200: the fused gate activation (A_log, dt_bias) is not supported")
+    B, T, H, K, V = _check_common(q, k, v, g, beta, initial_state, cu_seqlens)
+    if scale is None:
+        scale = K ** -0.5
+    if q.dtype == torch.float32:
+        if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (q, k, v, g, beta, initial_state)):
+            raise NotImplementedError("kda_b200: the float32 path is forward-only; use bfloat16 inputs for training")
+        return fused_recurrent_kda_fwd(q, k, v, g, beta, scale, initial_state, False, output_final_state,
+                                       use_qk_l2norm_in_kernel, cu_seqlens)
+    if K != 128 or V != 128:
+        raise NotImplementedError(f"kda_b200: the bf16 chunked kernels are built for K = V = 128, got K={K}, V={V}")
+    return ChunkKDAFunction.apply(q, k, v, g, beta, float(scale), initial_state, bool(output_final_state),
+                                  bool(use_qk_l2norm_in_kernel), cu_seqlens)
+
+
+def default_scale(K: int) -> float:
+    return 1.0 / math.sqrt(K)

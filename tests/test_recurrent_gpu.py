@@ -1,0 +1,94 @@
+"""GPU parity of the token-recurrent kernel (decode and exact fp32 scans) against the float64 oracle."""
+import numpy as np
+import pytest
+import torch
+
+from kda_b200.inputs import make_inputs, make_workload
+from oracle.kda_oracle import cosine, max_norm_err, recurrent_kda
+
+pytestmark = pytest.mark.gpu
+
+
+def _cuda(d):
+    return {n: (t.cuda() if isinstance(t, torch.Tensor) else t) for n, t in d.items()}
+
+
+def test_fp32_small_workload_matches_oracle_and_golden(golden_dir):
+    """The CPU-runnable workload (B=1 T=256 H=2 K=V=64 fp32): 1e-4 max-normalised vs the fp64 oracle."""
+    import os
+    from kda_b200 import chunk_kda
+    d = make_workload("fwd_fp32_small", seed=0)
+    ref_o, ref_h = recurrent_kda(d["q"], d["k"], d["v"], d["g"], d["beta"], output_final_state=True)
+    c = _cuda(d)
+    o, ht = chunk_kda(c["q"], c["k"], c["v"], c["g"], c["beta"], output_final_state=True)
+    assert o.dtype == torch.float32 and ht.dtype == torch.float32
+    assert max_norm_err(o, ref_o) <= 1e-4
+    assert max_norm_err(ht, ref_h) <= 1e-4
+    z = np.load(os.path.join(golden_dir, "kda_cfg0.npz"))
+    assert max_norm_err(o, torch.from_numpy(z["o"])) <= 1e-4
+    assert max_norm_err(ht, torch.from_numpy(z["ht"])) <= 1e-4
+
+
+@pytest.mark.parametrize("K,V", [(32, 32), (64, 64), (128, 128), (256, 64)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_recurrent_shapes(K, V, dtype):
+    from kda_b200 import fused_recurrent_kda
+    d = make_inputs(2, 37, 3, K, V, dtype, seed=K + V, h0_std=0.3)
+    ref_o, ref_h = recurrent_kda(d["q"], d["k"], d["v"], d["g"], d["beta"], initial_state=d["h0"], output_final_state=True)
+    c = _cuda(d)
+    o, ht = fused_recurrent_kda(c["q"], c["k"], c["v"], c["g"], c["beta"], initial_state=c["h0"], output_final_state=True)
+    tol = 1e-4 if dtype == torch.float32 else 2e-2     # bf16 output rounding only; the state stays fp32
+    assert max_norm_err(o, ref_o) <= tol
+    assert max_norm_err(ht, ref_h) <= 1e-4
+    assert cosine(o, ref_o) >= 0.9999
+
+
+def test_recurrent_varlen_l2norm_scale():
+    from kda_b200 import fused_recurrent_kda
+    lens = [5, 64, 1, 70, 3]
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int64)
+    d = make_inputs(1, sum(lens), 2, 64, 32, torch.float32, seed=11, h0_std=0.3, n_states=len(lens))
+    q, k = d["q"] * 3.0, d["k"] * 0.7
+    ref_o, ref_h = recurrent_kda(q, k, d["v"], d["g"], d["beta"], scale=0.5, initial_state=d["h0"],
+                                 output_final_state=True, cu_seqlens=cu, use_qk_l2norm=True)
+    c = _cuda(d)
+    o, ht = fused_recurrent_kda(q.cuda(), k.cuda(), c["v"], c["g"], c["beta"], scale=0.5, initial_state=c["h0"],
+                                output_final_state=True, cu_seqlens=cu.cuda(), use_qk_l2norm_in_kernel=True)
+    assert max_norm_err(o, ref_o) <= 1e-4
+    assert max_norm_err(ht, ref_h) <= 1e-4
+
+
+def test_decode_inplace_steps_match_scan():
+    """Three single-token in-place steps (with a state-slot table) equal one 3-token scan."""
+    from kda_b200 import fused_recurrent_kda, fused_recurrent_kda_fwd
+    d = _cuda(make_inputs(4, 3, 2, 128, 128, torch.bfloat16, seed=5, h0_std=0.02))
+    scale = 128 ** -0.5
+    o_ref, h_ref = fused_recurrent_kda(d["q"], d["k"], d["v"], d["g"], d["beta"], initial_state=d["h0"],
+                                       output_final_state=True)
+    pool = torch.zeros(6, 2, 128, 128, device="cuda")
+    slots = torch.tensor([4, 0, 5, 2], device="cuda", dtype=torch.int32)
+    pool[slots.long()] = d["h0"]
+    outs = []
+    for t in range(3):
+        o_t, _ = fused_recurrent_kda_fwd(d["q"][:, t:t + 1], d["k"][:, t:t + 1], d["v"][:, t:t + 1], d["g"][:, t:t + 1],
+                                         d["beta"][:, t:t + 1], scale, initial_state=pool, inplace_final_state=True,
+                                         ssm_state_indices=slots)
+        outs.append(o_t)
+    assert torch.equal(torch.cat(outs, 1), o_ref)
+    assert torch.equal(pool[slots.long()], h_ref)
+    assert torch.count_nonzero(pool[1]) == 0 and torch.count_nonzero(pool[3]) == 0
+
+
+def test_empty_and_errors():
+    from kda_b200 import chunk_kda, fused_recurrent_kda
+    d = _cuda(make_inputs(1, 8, 2, 64, 64, torch.float32, seed=1, h0_std=0.1))
+    with pytest.raises(ValueError):
+        fused_recurrent_kda(d["q"].repeat(2, 1, 1, 1), d["k"].repeat(2, 1, 1, 1), d["v"].repeat(2, 1, 1, 1),
+                            d["g"].repeat(2, 1, 1, 1), d["beta"].repeat(2, 1, 1), cu_seqlens=torch.tensor([0, 8]).cuda())
+    with pytest.raises(NotImplementedError):
+        chunk_kda(d["q"], d["k"], d["v"], d["g"], d["beta"], use_gate_in_kernel=True)
+    with pytest.raises(RuntimeError):
+        chunk_kda(d["q"].cpu(), d["k"].cpu(), d["v"].cpu(), d["g"].cpu(), d["beta"].cpu())
+    e = _cuda(make_inputs(2, 0, 2, 64, 64, torch.float32, seed=1, h0_std=0.1))
+    o, ht = fused_recurrent_kda(e["q"], e["k"], e["v"], e["g"], e["beta"], initial_state=e["h0"], output_final_state=True)
+    assert o.shape == (2, 0, 2, 64) and torch.equal(ht, e["h0"])
