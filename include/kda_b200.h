@@ -131,7 +131,7 @@ int64_t kda_chunk_max_chunks(int64_t tokens, int32_t N);
 /* Bytes of scratch kda_chunk_fwd needs (more when it must keep what the backward reads). */
 size_t kda_chunk_workspace_bytes(int64_t tokens, int32_t N, int32_t H, int32_t K, int32_t V, int32_t save_for_backward);
 /* Bytes of the backward's own scratch (args->bwd_workspace); it need not outlive the backward call. */
-size_t kda_chunk_bwd_workspace_bytes(int64_t tokens, int32_t N, int32_t H, int32_t K, int32_t V);
+size_t kda_chunk_bwd_workspace_bytes(int64_t tokens, int32_t N, int32_t H, int32_t K, int32_t V, int32_t use_qk_l2norm);
 
 int kda_chunk_fwd(const kda_chunk_args* args, void* stream);
 int kda_chunk_bwd(const kda_chunk_args* args, void* stream);

@@ -68,7 +68,7 @@ def load() -> C.CDLL:
     lib.kda_chunk_workspace_bytes.restype = C.c_size_t
     lib.kda_chunk_workspace_bytes.argtypes = [C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32]
     lib.kda_chunk_bwd_workspace_bytes.restype = C.c_size_t
-    lib.kda_chunk_bwd_workspace_bytes.argtypes = [C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32]
+    lib.kda_chunk_bwd_workspace_bytes.argtypes = [C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32]
     for name in ("kda_chunk_fwd", "kda_chunk_bwd"):
         fn = getattr(lib, name)
         fn.restype = C.c_int

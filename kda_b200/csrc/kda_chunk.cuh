@@ -5,7 +5,7 @@
 // consumer fetches a tile with one 1-D bulk (TMA) copy and reads it with ldmatrix without bank
 // conflicts.  Tile index = chunk * H + head.  Formats (bf16 unless noted):
 //   W, QG, KG : [64 tokens][128 k]   256-byte rows      w = Tm (beta k Gam), qg = scale q Gam, kg = k exp(G_last - G)
-//   AQK, TI   : [64 t][64 j]         128-byte rows      Aqk (lower incl. diagonal), Tm = (I + Akk)^-1
+//   AQK, TI, RKK : [64 t][64 j]      128-byte rows      Aqk (lower incl. diagonal), Tm = (I + Akk)^-1, raw <k_t D, k_j>
 //   UT        : [128 v][64 t]        128-byte rows      u^T,  u = Tm (beta v)
 //   GL        : fp32 [128]                              Gam_last = exp(G_last)
 //   HS, DH    : [128 v][128 k]       256-byte rows      transposed state at chunk start / its gradient at chunk end
@@ -30,15 +30,21 @@ struct ChunkWs {
   int* chunk_seq;       // [max_chunks] sequence of each chunk
   unsigned* status;     // [4] device status word(s): nonzero = a bounded wait gave up
   unsigned char *W, *UT, *KG, *QG, *AQK, *GL;          // always
-  unsigned char *TI, *HS, *VNEWT;                      // save_for_backward only
-  unsigned char *DH, *DVNEWT;                          // backward scratch
+  unsigned char *TI, *RKK, *HS, *VNEWT;                // save_for_backward only
+  unsigned char *DH, *DVNEWT;                          // backward scratch (bf16 tiles)
+  float *DQA, *DKP, *DKN;                              // fp32 [tile][64][128] partial dq, dk(+), dk(-)
+  float *DAD;                                          // fp32 [tile][2][4][16][16] diagonal blocks of dAqk, beta*dAkk
+  float *DGL;                                          // fp32 [tile][128] extra gradient of G at the chunk's last row
+  __nv_bfloat16 *QN, *KN;                              // [tokens][H][128] normalised q, k (use_qk_l2norm only)
+  float *RSTD;                                         // [2][tokens][H]
   size_t fwd_bytes, bwd_bytes;
 };
 
 inline size_t align_up(size_t x, size_t a = 256) { return (x + a - 1) / a * a; }
 
 // Lays the workspace out.  base may be NULL (sizes only).  bwd_base: separate backward scratch.
-inline ChunkWs carve_ws(unsigned char* base, unsigned char* bwd_base, int64_t tokens, int N, int H, bool save) {
+inline ChunkWs carve_ws(unsigned char* base, unsigned char* bwd_base, int64_t tokens, int N, int H, bool save,
+                        bool l2norm = true) {
   ChunkWs w{};
   const size_t NTmax = static_cast<size_t>(tokens / C + N);
   const size_t tiles = NTmax * static_cast<size_t>(H);
@@ -55,6 +61,7 @@ inline ChunkWs carve_ws(unsigned char* base, unsigned char* bwd_base, int64_t to
   w.GL = take(tiles * TILE_GL);
   if (save) {
     w.TI = take(tiles * TILE_TT);
+    w.RKK = take(tiles * TILE_TT);
     w.HS = take(tiles * TILE_VK);
     w.VNEWT = take(tiles * TILE_VT);
   }
@@ -63,6 +70,16 @@ inline ChunkWs carve_ws(unsigned char* base, unsigned char* bwd_base, int64_t to
   auto takeb = [&](size_t bytes) { unsigned char* p = bwd_base ? bwd_base + boff : nullptr; boff += align_up(bytes); return p; };
   w.DH = takeb(tiles * TILE_VK);
   w.DVNEWT = takeb(tiles * TILE_VT);
+  w.DQA = reinterpret_cast<float*>(takeb(tiles * C * KD * 4));
+  w.DKP = reinterpret_cast<float*>(takeb(tiles * C * KD * 4));
+  w.DKN = reinterpret_cast<float*>(takeb(tiles * C * KD * 4));
+  w.DAD = reinterpret_cast<float*>(takeb(tiles * 2 * 4 * 256 * 4));
+  w.DGL = reinterpret_cast<float*>(takeb(tiles * KD * 4));
+  if (l2norm) {
+    w.QN = reinterpret_cast<__nv_bfloat16*>(takeb(static_cast<size_t>(tokens) * H * KD * 2));
+    w.KN = reinterpret_cast<__nv_bfloat16*>(takeb(static_cast<size_t>(tokens) * H * KD * 2));
+    w.RSTD = reinterpret_cast<float*>(takeb(static_cast<size_t>(tokens) * H * 2 * 4));
+  }
   w.bwd_bytes = boff;
   return w;
 }

@@ -71,7 +71,7 @@ struct PrepParams {
   const float *g, *beta;
   const int* cu;
   const int *seq_chunk_off, *chunk_seq;
-  unsigned char *W, *UT, *KG, *QG, *AQK, *GL, *TI;   // TI may be NULL
+  unsigned char *W, *UT, *KG, *QG, *AQK, *GL, *TI, *RKK;   // TI, RKK may be NULL
   int N, H;
   int use_l2norm;
   float scale;
@@ -150,7 +150,6 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_prepare_kernel(const PrepPar
       const uint2 qr = *reinterpret_cast<const uint2*>(&s.q[t * QS + lane * 4]);
       const uint2 kr = *reinterpret_cast<const uint2*>(&s.k[t * QS + lane * 4]);
       const float2 q0 = unpack_bf16(qr.x), q1 = unpack_bf16(qr.y), k0 = unpack_bf16(kr.x), k1 = unpack_bf16(kr.y);
-      const float bt = s.beta[t];
 #pragma unroll 2
       for (int j = 16 * b; j <= t; ++j) {
         const float4 Gj = *reinterpret_cast<const float4*>(&s.G[j * GS + lane * 4]);
@@ -168,7 +167,7 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_prepare_kernel(const PrepPar
         x += __shfl_xor_sync(0xffffffffu, x, 2);
         x += __shfl_xor_sync(0xffffffffu, x, 1);
         if (lane == 0) s.Aqk[t * AS + j] = p.scale * x;
-        if (lane == 16 && j < t) s.Akk[t * AS + j] = bt * x;
+        if (lane == 16 && j < t) s.Akk[t * AS + j] = x;   // raw <k_t D, k_j>; beta_t is applied below
       }
     }
   }
@@ -214,11 +213,28 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_prepare_kernel(const PrepPar
       mma16816(ck, ak, b0, b1);
     }
     const int col = nt * 8 + tig * 2;
-    const float ba = s.beta[ta], bb = s.beta[tb];
     s.Aqk[ta * AS + col] = p.scale * cq[0]; s.Aqk[ta * AS + col + 1] = p.scale * cq[1];
     s.Aqk[tb * AS + col] = p.scale * cq[2]; s.Aqk[tb * AS + col + 1] = p.scale * cq[3];
-    s.Akk[ta * AS + col] = ba * ck[0]; s.Akk[ta * AS + col + 1] = ba * ck[1];
-    s.Akk[tb * AS + col] = bb * ck[2]; s.Akk[tb * AS + col + 1] = bb * ck[3];
+    s.Akk[ta * AS + col] = ck[0]; s.Akk[ta * AS + col + 1] = ck[1];
+    s.Akk[tb * AS + col] = ck[2]; s.Akk[tb * AS + col + 1] = ck[3];
+  }
+  __syncthreads();
+
+  // ---- P3c: keep the raw k-k products for the backward (dbeta), then Akk = beta_t * raw ----------------
+  {
+    unsigned char* gR = p.RKK ? p.RKK + tile * TILE_TT : nullptr;
+    for (int i = tid; i < C * 8; i += 256) {
+      const int r = i >> 3, pc = i & 7;
+      float4 a0 = *reinterpret_cast<const float4*>(&s.Akk[r * AS + pc * 8]);
+      float4 a1 = *reinterpret_cast<const float4*>(&s.Akk[r * AS + pc * 8 + 4]);
+      if (gR)
+        *reinterpret_cast<uint4*>(gR + swz<128>(r, pc * 8)) =
+            make_uint4(pack_bf16(a0.x, a0.y), pack_bf16(a0.z, a0.w), pack_bf16(a1.x, a1.y), pack_bf16(a1.z, a1.w));
+      const float b = s.beta[r];
+      a0.x *= b; a0.y *= b; a0.z *= b; a0.w *= b; a1.x *= b; a1.y *= b; a1.z *= b; a1.w *= b;
+      *reinterpret_cast<float4*>(&s.Akk[r * AS + pc * 8]) = a0;
+      *reinterpret_cast<float4*>(&s.Akk[r * AS + pc * 8 + 4]) = a1;
+    }
   }
   __syncthreads();
 
@@ -698,13 +714,15 @@ static cudaError_t set_attrs() {
   return g_attr_err;
 }
 
+int validate_chunk_args(const kda_chunk_args& a, bool backward);
 int validate_chunk_args(const kda_chunk_args& a, bool backward) {
   if (a.tokens < 0 || a.N < 0 || a.H <= 0) return KDA_E_SHAPE;
   if (a.K != KD || a.V != VD) return KDA_E_SHAPE;
   if (a.io_dtype != KDA_BF16) return KDA_E_DTYPE;
   if (a.tokens / C + a.N > 0x3fffffffLL) return KDA_E_SHAPE;
   if (a.tokens == 0 || a.N == 0) return KDA_OK;
-  if (!a.q || !a.k || !a.v || !a.g || !a.beta || !a.cu_seqlens || !a.o || !a.workspace) return KDA_E_NULL;
+  if (!a.q || !a.k || !a.v || !a.g || !a.beta || !a.cu_seqlens || !a.workspace) return KDA_E_NULL;
+  if (!backward && !a.o) return KDA_E_NULL;
   uintptr_t bits = reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.k) | reinterpret_cast<uintptr_t>(a.v) |
                    reinterpret_cast<uintptr_t>(a.g) | reinterpret_cast<uintptr_t>(a.o) | reinterpret_cast<uintptr_t>(a.h0) |
                    reinterpret_cast<uintptr_t>(a.ht);
@@ -726,11 +744,6 @@ extern "C" int64_t kda_chunk_max_chunks(int64_t tokens, int32_t N) { return toke
 extern "C" size_t kda_chunk_workspace_bytes(int64_t tokens, int32_t N, int32_t H, int32_t K, int32_t V, int32_t save) {
   (void)K; (void)V;
   return kda::carve_ws(nullptr, nullptr, tokens, N, H, save != 0).fwd_bytes;
-}
-
-extern "C" size_t kda_chunk_bwd_workspace_bytes(int64_t tokens, int32_t N, int32_t H, int32_t K, int32_t V) {
-  (void)K; (void)V;
-  return kda::carve_ws(nullptr, nullptr, tokens, N, H, true).bwd_bytes;
 }
 
 extern "C" int kda_chunk_fwd(const kda_chunk_args* args, void* stream) {
@@ -765,7 +778,7 @@ extern "C" int kda_chunk_fwd(const kda_chunk_args* args, void* stream) {
   pp.v = static_cast<const __nv_bfloat16*>(a.v);
   pp.g = a.g; pp.beta = a.beta; pp.cu = a.cu_seqlens;
   pp.seq_chunk_off = w.seq_chunk_off; pp.chunk_seq = w.chunk_seq;
-  pp.W = w.W; pp.UT = w.UT; pp.KG = w.KG; pp.QG = w.QG; pp.AQK = w.AQK; pp.GL = w.GL; pp.TI = save ? w.TI : nullptr;
+  pp.W = w.W; pp.UT = w.UT; pp.KG = w.KG; pp.QG = w.QG; pp.AQK = w.AQK; pp.GL = w.GL; pp.TI = save ? w.TI : nullptr; pp.RKK = save ? w.RKK : nullptr;
   pp.N = a.N; pp.H = a.H; pp.use_l2norm = a.use_qk_l2norm; pp.scale = a.scale;
   kda_chunk_prepare_kernel<<<dim3(NTmax, a.H), 256, sizeof(PrepSmem), st>>>(pp);
   if ((e = cudaGetLastError()) != cudaSuccess) return static_cast<int>(e);

@@ -208,7 +208,7 @@ class ChunkKDAFunction(torch.autograd.Function):
         dg = torch.empty_like(g32)
         dbeta = torch.empty_like(beta32)
         dh0 = torch.empty(N, H, K, V, dtype=torch.float32, device=dev) if has_h0 else None
-        bws = torch.empty(lib.kda_chunk_bwd_workspace_bytes(tokens, N, H, K, V), dtype=torch.uint8, device=dev)
+        bws = torch.empty(lib.kda_chunk_bwd_workspace_bytes(tokens, N, H, K, V, int(use_l2norm)), dtype=torch.uint8, device=dev)
         args = _chunk_args(q, k, v, g32, beta32, h0, cu, None, None, ws, N, H, K, V, tokens, use_l2norm, True, scale,
                            d_o=do, d_ht=dht, dq=dq, dk=dk, dv=dv, dg=dg, dbeta=dbeta, dh0=dh0, bwd_ws=bws)
         with torch.cuda.device(dev):

@@ -37,7 +37,7 @@ def test_workspace_sizes_are_monotone(lib):
     c = lib.kda_chunk_workspace_bytes(8192, 1, 2, 128, 128, 1)
     assert 0 < a < b < c
     assert lib.kda_chunk_max_chunks(130, 2) == 4
-    assert lib.kda_chunk_bwd_workspace_bytes(4096, 1, 2, 128, 128) > 0
+    assert lib.kda_chunk_bwd_workspace_bytes(4096, 1, 2, 128, 128, 0) > 0
 
 
 def test_argument_errors_without_gpu(lib):
