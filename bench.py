@@ -1,0 +1,355 @@
+#!/usr/bin/env python
+"""Benchmark of the KDA hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+Default workload `train_bf16`: bf16 chunk_kda forward+backward, B=8 T=8192 H=32 d_k=d_v=128, chunk 64,
+seeded synthetic inputs (kda_b200/inputs.py).  One step = one forward+backward over that batch.
+With N > 1 (launched by torchrun, one rank per GPU) every rank runs its own batch of the same shape
+(independent (batch, head) shards, no collective on the data path): weak scaling, value = all ranks'
+tokens / max-over-ranks time.
+
+Prints ONE JSON line: metric/value (inputs resident in HBM), `e2e` (same step through the public
+operator with pinned HOST buffers: host->device copies of every input and device->host copies of
+every output inside the timed region), `roofline` of the dominant kernel (per-kernel times from CUDA
+events recorded by the library around each kernel during the timed steps), `cpu_baseline` (the
+float32 token-recurrent PyTorch restatement on the host cores, bounded sample), clocks, launches.
+
+`--impl reference` times that CPU restatement alone, on all host threads (the NVlabs/kda repository
+has no implementation of this operator).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+from kda_b200.inputs import (WORKLOADS, decode_bytes_per_seq_head, flops_per_token_head, make_inputs,  # noqa: E402
+                             make_workload, min_hbm_bytes_per_token_head)
+
+METRIC = "KDA fwd+bwd tokens/s (H=32,d=128,bf16)"
+
+# Algorithmic work of each kernel per (token, head): C=64, K=V=128; GEMM = 2mnk, triangular products
+# counted full, the 64x64 inverse as (2/3) C^2 per token; bytes = the tensors the kernel must read and
+# write at the operator boundary plus the tiles it exchanges with the neighbouring kernels.
+K_, V_, C_ = 128, 128, 64
+_IN = 2 * K_ + 2 * K_ + 2 * V_ + 4 * K_ + 4                      # q,k,v bf16 + g fp32 + beta
+_TK, _TT, _VK = 2 * K_, 2 * C_, 2 * K_ * V_ / C_                 # bytes per token of a [64x128], [64x64], [128x128] bf16 tile
+KERNEL_WORK = {
+    # name: (flops, bytes) per (token, head)
+    "prepare": (2 * C_ * (3 * K_ + V_) + (2.0 / 3.0) * C_ * C_, _IN + 4 * _TK + _TT + 2 * _TT + 8),
+    "scan": (6 * K_ * V_ + 2 * C_ * V_, 4 * _TK + _TT + 8 + 2 * V_ + _VK + _TK),
+    "bwd_scan": (6 * K_ * V_ + 2 * C_ * V_, 3 * _TK + _TT + 8 + 2 * V_ + _VK + _TK),
+    "bwd_main": (6 * K_ * V_ + 12 * C_ * K_ + 6 * C_ * V_ + 4 * C_ * C_,
+                 _IN + 2 * V_ + 2 * _TT + 2 * _VK + 2 * _TK + 2 * V_ + 4 + 3 * 4 * K_ + 128 + 8),
+    "bwd_finish": (8 * C_ * K_ / 4.0, 2 * K_ * 2 + 4 * K_ + 3 * 4 * K_ + 128 + 8 + 2 * 2 * K_ + 4 * K_),
+}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(hbm=p["hbm_gbs"], tf_burst=p["bf16_tflops"], tf_sust=p.get("bf16_tflops_sustained", p["bf16_tflops"]),
+                    src="measured")
+    return dict(hbm=6650.0, tf_burst=1590.0, tf_sust=1400.0, src="fallback")
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons of one GPU while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        self.proc.terminate()          # the exact child started above
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        load = [x for x in sm if x >= 0.5 * max(sm)] if sm else []
+        return dict(sm_mhz=(statistics.median(load) if load else None), sm_max_mhz=(max(mx) if mx else None),
+                    reasons=sorted(reasons), samples=len(sm))
+
+
+def cpu_baseline(threads: int, T: int = 1024, backward: bool = True):
+    """The oracle's recurrence in float32 on the host cores (fla/ops/kda/naive.py:12-66 restated in
+    oracle/kda_oracle.py), forward+backward by autograd, B=1 H=32 d=128.  Returns tokens/s."""
+    from oracle.kda_oracle import recurrent_kda
+    torch.set_num_threads(threads)
+    d = make_inputs(1, T, 32, 128, 128, torch.float32, seed=0, h0_std=0.02, backward=True)
+    leaves = [d[n].clone().requires_grad_(backward) for n in ("q", "k", "v", "g", "beta")]
+    h0 = d["h0"].clone().requires_grad_(backward)
+    t0 = time.perf_counter()
+    o, ht = recurrent_kda(*leaves, initial_state=h0, output_final_state=True, dtype=torch.float32)
+    if backward:
+        torch.autograd.grad([o, ht], leaves + [h0], [d["do"], d["dht"]])
+    dt = time.perf_counter() - t0
+    return T / dt, dt
+
+
+def run_reference(args, rank):
+    """Reference arm: the CPU restatement, all host threads, bounded sample per step."""
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    T = 512
+    for _ in range(max(0, min(args.warmup, 1))):
+        cpu_baseline(threads, T=128)
+    times = []
+    for _ in range(args.steps):
+        tps, dt = cpu_baseline(threads, T=T)
+        times.append(dt)
+    ms = 1e3 * sum(times) / len(times)
+    value = T / (ms / 1e3)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "train_bf16 (B=8 T=8192 H=32 K=V=128 fwd+bwd)",
+                   "sample": f"B=1 T={T} H=32 K=V=128 per step"},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port",
+                         "sample": f"token-recurrent float32 PyTorch forward+backward, B=1 T={T} H=32 K=V=128 per step"},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="train_bf16", choices=sorted(WORKLOADS))
+    ap.add_argument("--scale-down", type=int, default=1, help="divide the batch (smaller case for profiling)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; kda_b200 has no CPU path")
+    args.warmup = max(args.warmup, 3)
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    import torch.distributed as dist
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    from kda_b200 import _lib, chunk_kda, fused_recurrent_kda_fwd
+    w = WORKLOADS[args.workload]
+    peaks = load_peaks()
+    host = make_workload(args.workload, seed=rank, scale_down=args.scale_down)
+    cu_host = host.pop("cu_seqlens")
+    names = [n for n, t in host.items() if t is not None]
+    pinned = {n: host[n].pin_memory() for n in names}
+    devt = {n: pinned[n].to(dev, non_blocking=True) for n in names}
+    cu = cu_host.to(dev) if cu_host is not None else None
+    B, T, H = devt["q"].shape[:3]
+    tokens = B * T
+    torch.cuda.synchronize()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def maxms(ms):
+        if world > 1:
+            t = torch.tensor([ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+        return ms
+
+    launches_per_step = 0
+    if args.workload == "decode":
+        state = devt["h0"].clone()
+        scale = 128 ** -0.5
+
+        def step(x=devt):
+            return fused_recurrent_kda_fwd(x["q"], x["k"], x["v"], x["g"], x["beta"], scale, initial_state=state,
+                                           inplace_final_state=True)
+        launches_per_step = 1
+        grad_names = []
+    elif w.backward:
+        grad_names = ["q", "k", "v", "g", "beta"] + (["h0"] if "h0" in devt else [])
+
+        def step(x=devt):
+            leaves = [x[n].requires_grad_(True) for n in grad_names]
+            o, ht = chunk_kda(x["q"], x["k"], x["v"], x["g"], x["beta"], initial_state=x.get("h0"),
+                              output_final_state=True, cu_seqlens=cu)
+            grads = torch.autograd.grad([o, ht], leaves, [x["do"], x["dht"]])
+            return (o, ht) + tuple(grads)
+        launches_per_step = 6
+    else:
+        grad_names = []
+
+        def step(x=devt):
+            with torch.no_grad():
+                return chunk_kda(x["q"], x["k"], x["v"], x["g"], x["beta"], initial_state=x.get("h0"),
+                                 output_final_state=True, cu_seqlens=cu)
+        launches_per_step = 3
+
+    # ---------------- kernel-resident timing ----------------
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank if os.environ.get("CUDA_VISIBLE_DEVICES") is None else
+                           int(os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local_rank]))
+    if rank == 0:
+        sampler.start()
+    _lib.profile_enable(True)
+    _lib.profile_read(reset=True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms_total = maxms(e0.elapsed_time(e1))
+    stages = _lib.profile_read(reset=True)
+    _lib.profile_enable(False)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_step = ms_total / args.steps
+    value = world * tokens / (ms_step / 1e3)
+
+    # ---------------- end to end: pinned host buffers in, every output back out ----------------
+    e2e = None
+    if not args.no_e2e:
+        out_host = None
+
+        def e2e_step():
+            nonlocal out_host
+            x = {n: pinned[n].to(dev, non_blocking=True) for n in names}
+            outs = step(x)
+            outs = [t for t in outs if t is not None]
+            if out_host is None:
+                out_host = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True) for t in outs]
+            for hbuf, t in zip(out_host, outs):
+                hbuf.copy_(t, non_blocking=True)
+        e2e_step()
+        barrier()
+        n_e2e = max(1, min(args.steps, 5))
+        e0.record()
+        for _ in range(n_e2e):
+            e2e_step()
+        e1.record()
+        barrier()
+        ms_e2e = maxms(e0.elapsed_time(e1)) / n_e2e
+        h2d = sum(pinned[n].numel() * pinned[n].element_size() for n in names)
+        d2h = sum(t.numel() * t.element_size() for t in out_host)
+        e2e = {"value": world * tokens / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": n_e2e}
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    # ---------------- roofline of the dominant kernel ----------------
+    th = tokens * H
+    if args.workload == "decode":
+        byt = B * H * decode_bytes_per_seq_head()
+        ach = byt / (ms_step * 1e-3) / 1e9
+        roof = {"kernel": "kda_recurrent_kernel", "bound": "hbm", "achieved": ach, "peak": peaks["hbm"], "unit": "GB/s",
+                "frac": ach / peaks["hbm"], "traffic": None, "peak_source": peaks["src"]}
+        kernels = {}
+    else:
+        kernels = {s: {"ms_per_launch": (ms / n), "launches": n} for s, (ms, n) in stages.items() if n > 0}
+        dom = max((s for s in kernels if s in KERNEL_WORK), key=lambda s: kernels[s]["ms_per_launch"] * kernels[s]["launches"])
+        fl, by = KERNEL_WORK[dom]
+        sec = kernels[dom]["ms_per_launch"] * 1e-3
+        ridge = peaks["tf_sust"] * 1e12 / (peaks["hbm"] * 1e9)
+        if fl / by >= ridge:
+            ach = fl * th / sec / 1e12
+            roof = {"kernel": dom, "bound": "tensor", "achieved": ach, "peak": peaks["tf_sust"], "unit": "TFLOP/s",
+                    "frac": ach / peaks["tf_sust"]}
+        else:
+            ach = by * th / sec / 1e9
+            roof = {"kernel": dom, "bound": "hbm", "achieved": ach, "peak": peaks["hbm"], "unit": "GB/s",
+                    "frac": ach / peaks["hbm"]}
+        roof.update({"traffic": None, "peak_source": peaks["src"], "ms_per_launch": kernels[dom]["ms_per_launch"],
+                     "algorithmic_flops_per_launch": fl * th, "algorithmic_bytes_per_launch": by * th})
+    # whole-step roofline fractions (both bounds), for context
+    fl_step = flops_per_token_head(backward=w.backward) * th
+    by_step = min_hbm_bytes_per_token_head(backward=w.backward) * th
+    whole = {"tensor_frac_sustained": fl_step / (ms_step * 1e-3) / 1e12 / peaks["tf_sust"],
+             "hbm_frac_min_traffic": by_step / (ms_step * 1e-3) / 1e9 / peaks["hbm"]}
+
+    cpu = None
+    if not args.no_cpu_baseline:
+        threads = os.cpu_count() or 1
+        tps, dt = cpu_baseline(threads, T=512, backward=w.backward)
+        cpu = {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",
+               "sample": f"token-recurrent float32 PyTorch {'forward+backward' if w.backward else 'forward'}, "
+                         f"B=1 T=512 H=32 K=V=128, {dt:.1f} s"}
+
+    line = {
+        "metric": METRIC if args.workload == "train_bf16" else f"KDA {args.workload} tokens/s",
+        "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"{args.workload} (B={B} T={T} H={H} K=V=128, chunk 64"
+                               f"{', fwd+bwd' if w.backward else ''}{', packed varlen' if cu is not None else ''})",
+                   "per_gpu_batch": B, "l2": "inputs (>= 3 GB per step) far exceed the 126 MB L2; no flush needed",
+                   "seed": "rank"},
+        "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
+        "roofline": roof, "step_roofline": whole, "kernels": kernels, "cpu_baseline": cpu,
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

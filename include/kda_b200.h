@@ -136,6 +136,25 @@ size_t kda_chunk_bwd_workspace_bytes(int64_t tokens, int32_t N, int32_t H, int32
 int kda_chunk_fwd(const kda_chunk_args* args, void* stream);
 int kda_chunk_bwd(const kda_chunk_args* args, void* stream);
 
+/* ------------------------------------------------------------------------------------------------
+ * Per-kernel timing for benchmarks (no counterpart in the Python operator; fla times whole calls).
+ * While enabled, kda_chunk_fwd / kda_chunk_bwd record a CUDA event on the call's stream before their
+ * first kernel and after each kernel.  The events live in a fixed ring owned by the library (created
+ * on the first enable; this is the one place the library creates CUDA objects).  kda_b200_profile_read
+ * waits for the recorded events and returns, per stage, the summed milliseconds and the launch count
+ * since the last reset.  Stage ids below.  Not meant to be left on in production.
+ * ------------------------------------------------------------------------------------------------ */
+#define KDA_STAGE_TABLES 0
+#define KDA_STAGE_PREPARE 1
+#define KDA_STAGE_SCAN 2
+#define KDA_STAGE_BWD_SCAN 3
+#define KDA_STAGE_BWD_MAIN 4
+#define KDA_STAGE_BWD_FINISH 5
+#define KDA_STAGE_L2NORM 6
+#define KDA_NUM_STAGES 7
+int kda_b200_profile_enable(int on);
+int kda_b200_profile_read(float* stage_ms, int* stage_launches, int reset);
+
 #if defined(__GNUC__)
 #pragma GCC visibility pop
 #endif

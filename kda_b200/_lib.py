@@ -42,7 +42,7 @@ class ChunkArgs(C.Structure):
 EXPORTS = (
     "kda_b200_abi_version", "kda_b200_strerror", "kda_recurrent_fwd",
     "kda_chunk_max_chunks", "kda_chunk_workspace_bytes", "kda_chunk_bwd_workspace_bytes",
-    "kda_chunk_fwd", "kda_chunk_bwd",
+    "kda_chunk_fwd", "kda_chunk_bwd", "kda_b200_profile_enable", "kda_b200_profile_read",
 )
 
 _lib = None
@@ -73,6 +73,10 @@ def load() -> C.CDLL:
         fn = getattr(lib, name)
         fn.restype = C.c_int
         fn.argtypes = [C.POINTER(ChunkArgs), C.c_void_p]
+    lib.kda_b200_profile_enable.restype = C.c_int
+    lib.kda_b200_profile_enable.argtypes = [C.c_int]
+    lib.kda_b200_profile_read.restype = C.c_int
+    lib.kda_b200_profile_read.argtypes = [C.POINTER(C.c_float), C.POINTER(C.c_int), C.c_int]
     if lib.kda_b200_abi_version() != ABI_VERSION:
         raise RuntimeError("libkda_b200.so was built from a different ABI version; rebuild it")
     _lib = lib
@@ -87,3 +91,18 @@ def check(code: int, what: str) -> None:
     if code != 0:
         msg = load().kda_b200_strerror(code).decode()
         raise KdaError(f"{what} failed with code {code}: {msg}")
+
+
+STAGES = ("tables", "prepare", "scan", "bwd_scan", "bwd_main", "bwd_finish", "l2norm")
+
+
+def profile_enable(on: bool) -> None:
+    check(load().kda_b200_profile_enable(int(on)), "kda_b200_profile_enable")
+
+
+def profile_read(reset: bool = True) -> dict:
+    """{stage: (total_ms, launches)} of the chunk kernels since the last reset (waits for the events)."""
+    ms = (C.c_float * len(STAGES))()
+    n = (C.c_int * len(STAGES))()
+    check(load().kda_b200_profile_read(ms, n, int(reset)), "kda_b200_profile_read")
+    return {s: (float(ms[i]), int(n[i])) for i, s in enumerate(STAGES)}

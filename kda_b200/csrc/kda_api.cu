@@ -20,3 +20,87 @@ extern "C" const char* kda_b200_strerror(int code) {
   if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));
   return "unknown kda_b200 error code";
 }
+
+// ---- per-kernel timing ------------------------------------------------------------------------------
+#include <mutex>
+#include <vector>
+
+#include "kda_chunk.cuh"
+
+namespace kda {
+
+constexpr int PROF_RING = 256;          // calls kept between two reads
+constexpr int PROF_MARKS = 6;           // marks per call (a forward uses 3, a backward up to 5)
+
+struct ProfCall {
+  cudaEvent_t start;
+  cudaEvent_t mark[PROF_MARKS];
+  int stage[PROF_MARKS];
+  int nmarks;
+};
+
+static std::mutex g_prof_mu;
+static bool g_prof_on = false;
+static std::vector<ProfCall> g_prof_ring;
+static int g_prof_used = 0;
+
+ProfCall* prof_begin(cudaStream_t st) {
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  if (!g_prof_on || g_prof_used >= PROF_RING) return nullptr;
+  ProfCall* pc = &g_prof_ring[g_prof_used++];
+  pc->nmarks = 0;
+  cudaEventRecord(pc->start, st);
+  return pc;
+}
+
+void prof_mark(ProfCall* pc, int stage, cudaStream_t st) {
+  if (!pc || pc->nmarks >= PROF_MARKS) return;
+  pc->stage[pc->nmarks] = stage;
+  cudaEventRecord(pc->mark[pc->nmarks], st);
+  pc->nmarks++;
+}
+
+}  // namespace kda
+
+extern "C" int kda_b200_profile_enable(int on) {
+  using namespace kda;
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  if (on && g_prof_ring.empty()) {
+    g_prof_ring.resize(PROF_RING);
+    for (auto& pc : g_prof_ring) {
+      cudaError_t e = cudaEventCreate(&pc.start);
+      for (int i = 0; i < PROF_MARKS && e == cudaSuccess; ++i) e = cudaEventCreate(&pc.mark[i]);
+      if (e != cudaSuccess) {
+        g_prof_ring.clear();
+        return static_cast<int>(e);
+      }
+    }
+  }
+  g_prof_on = on != 0;
+  return KDA_OK;
+}
+
+extern "C" int kda_b200_profile_read(float* stage_ms, int* stage_launches, int reset) {
+  using namespace kda;
+  if (!stage_ms || !stage_launches) return KDA_E_NULL;
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  for (int i = 0; i < KDA_NUM_STAGES; ++i) {
+    stage_ms[i] = 0.f;
+    stage_launches[i] = 0;
+  }
+  for (int c = 0; c < g_prof_used; ++c) {
+    ProfCall& pc = g_prof_ring[c];
+    cudaEvent_t prev = pc.start;
+    for (int m = 0; m < pc.nmarks; ++m) {
+      cudaError_t e = cudaEventSynchronize(pc.mark[m]);
+      float ms = 0.f;
+      if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, prev, pc.mark[m]);
+      if (e != cudaSuccess) return static_cast<int>(e);
+      stage_ms[pc.stage[m]] += ms;
+      stage_launches[pc.stage[m]] += 1;
+      prev = pc.mark[m];
+    }
+  }
+  if (reset) g_prof_used = 0;
+  return KDA_OK;
+}

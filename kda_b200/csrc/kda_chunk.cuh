@@ -100,4 +100,9 @@ __device__ __forceinline__ ChunkInfo chunk_info(const int* seq_chunk_off, const 
   return ci;
 }
 
+// ---- optional per-kernel timing (host side, see kda_b200_profile_* in the public header) ------------
+struct ProfCall;                                  // one call's worth of events
+ProfCall* prof_begin(cudaStream_t st);            // NULL when profiling is off
+void prof_mark(ProfCall* pc, int stage, cudaStream_t st);   // records "stage finished"
+
 }  // namespace kda

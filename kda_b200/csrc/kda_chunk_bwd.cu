@@ -1023,9 +1023,11 @@ extern "C" int kda_chunk_bwd(const kda_chunk_args* args, void* stream) {
   const long long rows = static_cast<long long>(a.tokens) * a.H;
   const __nv_bfloat16* q = static_cast<const __nv_bfloat16*>(a.q);
   const __nv_bfloat16* k = static_cast<const __nv_bfloat16*>(a.k);
+  ProfCall* prof = prof_begin(st);
   if (l2) {
     kda_l2norm_fwd_kernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, st>>>(q, k, w.QN, w.KN, w.RSTD, rows);
     if ((e = cudaGetLastError()) != cudaSuccess) return static_cast<int>(e);
+    prof_mark(prof, KDA_STAGE_L2NORM, st);
     q = w.QN;
     k = w.KN;
   }
@@ -1038,6 +1040,7 @@ extern "C" int kda_chunk_bwd(const kda_chunk_args* args, void* stream) {
   rp.N = a.N; rp.H = a.H;
   kda_chunk_bwd_scan_kernel<<<a.N * a.H, RS_THREADS, sizeof(RScanSmem), st>>>(rp);
   if ((e = cudaGetLastError()) != cudaSuccess) return static_cast<int>(e);
+  prof_mark(prof, KDA_STAGE_BWD_SCAN, st);
 
   MainParams mp{};
   mp.q = q; mp.k = k; mp.v = static_cast<const __nv_bfloat16*>(a.v); mp.d_o = static_cast<const __nv_bfloat16*>(a.d_o);
@@ -1048,6 +1051,7 @@ extern "C" int kda_chunk_bwd(const kda_chunk_args* args, void* stream) {
   mp.N = a.N; mp.H = a.H; mp.scale = a.scale;
   kda_chunk_bwd_main_kernel<<<dim3(NTmax, a.H), 256, sizeof(MainSmem), st>>>(mp);
   if ((e = cudaGetLastError()) != cudaSuccess) return static_cast<int>(e);
+  prof_mark(prof, KDA_STAGE_BWD_MAIN, st);
 
   FinParams fp{};
   fp.q = q; fp.k = k; fp.g = a.g; fp.cu = a.cu_seqlens; fp.seq_chunk_off = w.seq_chunk_off; fp.chunk_seq = w.chunk_seq;
@@ -1056,10 +1060,12 @@ extern "C" int kda_chunk_bwd(const kda_chunk_args* args, void* stream) {
   fp.N = a.N; fp.H = a.H; fp.scale = a.scale;
   kda_chunk_bwd_finish_kernel<<<dim3(NTmax, a.H), 256, 0, st>>>(fp);
   if ((e = cudaGetLastError()) != cudaSuccess) return static_cast<int>(e);
+  prof_mark(prof, KDA_STAGE_BWD_FINISH, st);
 
   if (l2) {
     kda_l2norm_bwd_kernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, st>>>(w.QN, w.KN, w.RSTD, fp.dq, fp.dk, rows);
     if ((e = cudaGetLastError()) != cudaSuccess) return static_cast<int>(e);
+    prof_mark(prof, KDA_STAGE_L2NORM, st);
   }
   return KDA_OK;
 }

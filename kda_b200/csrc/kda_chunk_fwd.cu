@@ -769,8 +769,10 @@ extern "C" int kda_chunk_fwd(const kda_chunk_args* args, void* stream) {
   if (e != cudaSuccess) return static_cast<int>(e);
   const int NTmax = static_cast<int>(a.tokens / C + a.N);
 
+  ProfCall* prof = prof_begin(st);
   kda_chunk_tables_kernel<<<1, 1024, 0, st>>>(a.cu_seqlens, a.N, w.seq_chunk_off, w.chunk_seq, w.status);
   if ((e = cudaGetLastError()) != cudaSuccess) return static_cast<int>(e);
+  prof_mark(prof, KDA_STAGE_TABLES, st);
 
   PrepParams pp{};
   pp.q = static_cast<const __nv_bfloat16*>(a.q);
@@ -782,6 +784,7 @@ extern "C" int kda_chunk_fwd(const kda_chunk_args* args, void* stream) {
   pp.N = a.N; pp.H = a.H; pp.use_l2norm = a.use_qk_l2norm; pp.scale = a.scale;
   kda_chunk_prepare_kernel<<<dim3(NTmax, a.H), 256, sizeof(PrepSmem), st>>>(pp);
   if ((e = cudaGetLastError()) != cudaSuccess) return static_cast<int>(e);
+  prof_mark(prof, KDA_STAGE_PREPARE, st);
 
   ScanParams sp{};
   sp.cu = a.cu_seqlens; sp.seq_chunk_off = w.seq_chunk_off; sp.chunk_seq = w.chunk_seq;
@@ -790,5 +793,7 @@ extern "C" int kda_chunk_fwd(const kda_chunk_args* args, void* stream) {
   sp.h0 = a.h0; sp.ht = a.ht; sp.o = static_cast<__nv_bfloat16*>(a.o); sp.status = w.status;
   sp.N = a.N; sp.H = a.H;
   kda_chunk_scan_kernel<<<a.N * a.H, SCAN_THREADS, sizeof(ScanSmem), st>>>(sp);
-  return static_cast<int>(cudaGetLastError());
+  if ((e = cudaGetLastError()) != cudaSuccess) return static_cast<int>(e);
+  prof_mark(prof, KDA_STAGE_SCAN, st);
+  return KDA_OK;
 }
