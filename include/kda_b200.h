@@ -137,6 +137,32 @@ int kda_chunk_fwd(const kda_chunk_args* args, void* stream);
 int kda_chunk_bwd(const kda_chunk_args* args, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * Forward for callers that must not allocate.  It has no counterpart in the reference or in fla: their
+ * host functions always allocate their intermediates with torch.empty.
+ *
+ * Who needs it: a serving process that handed every free byte of HBM to its state / KV-cache pool at
+ * start-up, a host thread inside a region where the framework forbids allocator calls (an allocation
+ * there can fail, or can stall the whole device while the allocator synchronises), or a plain C caller
+ * that owns no device allocator at all.  Such a caller still passes its inputs and outputs (q, k, v, g,
+ * beta, h0, cu_seqlens, o, ht) but no workspace: args->workspace / workspace_bytes are ignored, and the
+ * per-chunk tiles go to a fixed KDA_NOALLOC_SCRATCH_BYTES array that lives in the library's device
+ * image (every GPU that loads the library holds those bytes until the process exits).
+ *
+ *  - forward only: args->save_for_backward must be 0 (KDA_E_SHAPE otherwise), since the next call
+ *    overwrites the array;
+ *  - the problem must fit: kda_chunk_workspace_bytes(tokens, N, H, K, V, 0) <= KDA_NOALLOC_SCRATCH_BYTES,
+ *    else KDA_E_LIMIT and nothing is launched (72.5 KiB per (chunk, head): e.g. 14 chunks of 32 heads);
+ *  - the first call on each device looks the array's device address up (with that device current) and
+ *    caches it; make that first call during start-up, before any stream capture begins;
+ *  - all calls on a device share the one array: two calls that overlap on the GPU (different streams)
+ *    race, so keep them on one stream or order them with events.  Nothing in the array has to start
+ *    at zero: each call rewrites the tables, the status word and every tile it reads.
+ *  - it calls no cudaMalloc / cudaFree and no allocating library routine.
+ * ------------------------------------------------------------------------------------------------ */
+#define KDA_NOALLOC_SCRATCH_BYTES (32u << 20)
+int kda_chunk_fwd_noalloc(const kda_chunk_args* args, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
  * Per-kernel timing for benchmarks (no counterpart in the Python operator; fla times whole calls).
  * While enabled, kda_chunk_fwd / kda_chunk_bwd record a CUDA event on the call's stream before their
  * first kernel and after each kernel.  The events live in a fixed ring owned by the library (created

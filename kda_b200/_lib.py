@@ -10,6 +10,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG, "libkda_b200.so")
 
 KDA_BF16, KDA_FP32 = 0, 1
+NOALLOC_SCRATCH_BYTES = 32 << 20
 ABI_VERSION = 1
 
 
@@ -42,7 +43,7 @@ class ChunkArgs(C.Structure):
 EXPORTS = (
     "kda_b200_abi_version", "kda_b200_strerror", "kda_recurrent_fwd",
     "kda_chunk_max_chunks", "kda_chunk_workspace_bytes", "kda_chunk_bwd_workspace_bytes",
-    "kda_chunk_fwd", "kda_chunk_bwd", "kda_b200_profile_enable", "kda_b200_profile_read",
+    "kda_chunk_fwd", "kda_chunk_bwd", "kda_chunk_fwd_noalloc", "kda_b200_profile_enable", "kda_b200_profile_read",
 )
 
 _lib = None
@@ -69,7 +70,7 @@ def load() -> C.CDLL:
     lib.kda_chunk_workspace_bytes.argtypes = [C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32]
     lib.kda_chunk_bwd_workspace_bytes.restype = C.c_size_t
     lib.kda_chunk_bwd_workspace_bytes.argtypes = [C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32]
-    for name in ("kda_chunk_fwd", "kda_chunk_bwd"):
+    for name in ("kda_chunk_fwd", "kda_chunk_bwd", "kda_chunk_fwd_noalloc"):
         fn = getattr(lib, name)
         fn.restype = C.c_int
         fn.argtypes = [C.POINTER(ChunkArgs), C.c_void_p]

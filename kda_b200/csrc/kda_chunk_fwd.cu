@@ -797,3 +797,51 @@ extern "C" int kda_chunk_fwd(const kda_chunk_args* args, void* stream) {
   prof_mark(prof, KDA_STAGE_SCAN, st);
   return KDA_OK;
 }
+
+// =================================================================================================
+// forward without any allocation: the workspace is a fixed array inside the library's device image
+// =================================================================================================
+// The name below is a device symbol.  In host code it is only a handle: its device address has to be
+// asked for with cudaGetSymbolAddress, once per device, with that device current.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[KDA_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_noalloc_mu;
+unsigned char* g_noalloc_addr[kMaxDevices] = {};   // device address of g_noalloc_scratch, per device ordinal
+}  // namespace
+
+// Forward-only variant of kda_chunk_fwd for callers that cannot allocate device memory (a server whose
+// memory pool is frozen after start-up, a thread inside a no-allocation region, a C caller without an
+// allocator).  Inputs and outputs are the caller's; the per-chunk tiles live in g_noalloc_scratch.
+// The first call on a device resolves the array's address (do it at start-up, before stream capture).
+// Calls that overlap on one GPU share the array and race; the array keeps the previous call's bytes,
+// which is harmless because every call rewrites all it reads.
+extern "C" int kda_chunk_fwd_noalloc(const kda_chunk_args* args, void* stream) {
+  if (!args) return KDA_E_NULL;
+  if (args->save_for_backward != 0) return KDA_E_SHAPE;
+  if (args->tokens < 0 || args->N < 0 || args->H <= 0) return KDA_E_SHAPE;
+  const size_t need = kda::carve_ws(nullptr, nullptr, args->tokens, args->N, args->H, false).fwd_bytes;
+  if (need > static_cast<size_t>(KDA_NOALLOC_SCRATCH_BYTES)) return KDA_E_LIMIT;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= kMaxDevices) return KDA_E_LIMIT;
+  unsigned char* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
+    if (!g_noalloc_addr[dev]) {
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+      if (e != cudaSuccess) return static_cast<int>(e);
+      g_noalloc_addr[dev] = static_cast<unsigned char*>(p);
+    }
+    scratch = g_noalloc_addr[dev];
+  }
+  kda_chunk_args a = *args;
+  a.workspace = scratch;
+  a.workspace_bytes = KDA_NOALLOC_SCRATCH_BYTES;
+  a.bwd_workspace = nullptr;
+  a.bwd_workspace_bytes = 0;
+  return kda_chunk_fwd(&a, stream);
+}
