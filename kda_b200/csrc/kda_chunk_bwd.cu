@@ -827,102 +827,101 @@ struct FinParams {
   float scale;
 };
 
-__global__ void __launch_bounds__(256) kda_chunk_bwd_finish_kernel(const FinParams p) {
+__global__ void __launch_bounds__(512, 1) kda_chunk_bwd_finish_kernel(const FinParams p) {
   __shared__ float2 sA[4][16][16];     // (dAqk, beta dAkk) diagonal blocks
-  __shared__ float carryG[KD], carryD[KD];
-  const int tid = threadIdx.x, kk = tid & 127, half = tid >> 7;
+  __shared__ float carryG[4][KD], carryD[4][KD];
+  const int tid = threadIdx.x, kk = tid & 127, b = tid >> 7;   // one thread per (key column, 16-row block)
   const int c = blockIdx.x, h = blockIdx.y;
   if (c >= p.seq_chunk_off[p.N]) return;
   const ChunkInfo ci = chunk_info(p.seq_chunk_off, p.chunk_seq, p.cu, c);
   const int len = ci.len;
   const size_t tile = static_cast<size_t>(c) * p.H + h;
-
-  {
-    const float* gD = p.DAD + tile * 2048;
-    for (int i = tid; i < 1024; i += 256) {
-      const int b = i >> 8, r = (i >> 4) & 15, cc = i & 15;
-      sA[b][r][cc] = make_float2(gD[i], gD[1024 + i]);
-    }
-  }
-  // log2-domain cumsum of g for this column; rows >= len contribute 0
-  float Gc[32];
-  {
-    float run = 0.f;
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      const int t = half * 32 + i;
-      const float gv = (t < len) ? __ldg(p.g + (static_cast<size_t>(ci.tok0 + t) * p.H + h) * KD + kk) : 0.f;
-      run += gv;
-      Gc[i] = run;
-    }
-    if (half == 0) carryG[kk] = run;
-  }
-  __syncthreads();
-  {
-    const float add = half ? carryG[kk] : 0.f;
-#pragma unroll
-    for (int i = 0; i < 32; ++i) Gc[i] = (Gc[i] + add) * LOG2E;
-  }
-
-  float dGv[32];
   const float* gq = p.DQA + tile * (C * KD);
   const float* gp = p.DKP + tile * (C * KD);
   const float* gn = p.DKN + tile * (C * KD);
+
+  // issue every global load of this thread up front (all independent)
+  float Gc[16], qv[16], kv[16], dq[16], dkp[16], dkn[16];
 #pragma unroll
-  for (int bb = 0; bb < 2; ++bb) {
-    const int b = half * 2 + bb;
-    float qv[16], kv[16], dq[16], dkp[16], dkn[16];
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const int t = b * 16 + i;
-      const size_t gi = (static_cast<size_t>(ci.tok0 + t) * p.H + h) * KD + kk;
-      qv[i] = (t < len) ? __bfloat162float(p.q[gi]) : 0.f;
-      kv[i] = (t < len) ? __bfloat162float(p.k[gi]) : 0.f;
-      dq[i] = gq[static_cast<size_t>(t) * KD + kk];
-      dkp[i] = gp[static_cast<size_t>(t) * KD + kk];
-      dkn[i] = gn[static_cast<size_t>(t) * KD + kk];
-    }
-#pragma unroll
-    for (int t = 0; t < 16; ++t) {
-#pragma unroll
-      for (int j = 0; j <= t; ++j) {
-        const float2 a = sA[b][t][j];
-        const float D = ex2(Gc[bb * 16 + t] - Gc[bb * 16 + j]);
-        const float sa = p.scale * a.x;
-        const float kd = kv[j] * D;
-        dq[t] = fmaf(sa, kd, dq[t]);
-        dkp[t] = fmaf(a.y, kd, dkp[t]);
-        dkn[j] = fmaf(D, sa * qv[t] + a.y * kv[t], dkn[j]);
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const int t = b * 16 + i;
-      dGv[bb * 16 + i] = qv[i] * dq[i] + kv[i] * (dkp[i] - dkn[i]);
-      if (t < len) {
-        const size_t gi = (static_cast<size_t>(ci.tok0 + t) * p.H + h) * KD + kk;
-        p.dq[gi] = __float2bfloat16_rn(dq[i]);
-        p.dk[gi] = __float2bfloat16_rn(dkp[i] + dkn[i]);
-      }
+  for (int i = 0; i < 16; ++i) {
+    const int t = b * 16 + i;
+    const bool ok = t < len;
+    const size_t gi = (static_cast<size_t>(ci.tok0 + (ok ? t : 0)) * p.H + h) * KD + kk;
+    Gc[i] = ok ? __ldg(p.g + gi) : 0.f;
+    qv[i] = ok ? __bfloat162float(p.q[gi]) : 0.f;
+    kv[i] = ok ? __bfloat162float(p.k[gi]) : 0.f;
+    dq[i] = __ldcs(gq + static_cast<size_t>(t) * KD + kk);
+    dkp[i] = __ldcs(gp + static_cast<size_t>(t) * KD + kk);
+    dkn[i] = __ldcs(gn + static_cast<size_t>(t) * KD + kk);
+  }
+  {
+    const float* gD = p.DAD + tile * 2048;
+    for (int i = tid; i < 1024; i += 512) {
+      const int bb = i >> 8, r = (i >> 4) & 15, cc = i & 15;
+      sA[bb][r][cc] = make_float2(gD[i], gD[1024 + i]);
     }
   }
-  // dg = reverse cumsum of dG over the chunk (the last row also carries the chunk-end terms)
-  if (half == 1) dGv[31] += p.DGL[tile * KD + kk];
+  // log2-domain cumsum of g for this column: local prefix, then the totals of the earlier blocks
   {
     float run = 0.f;
 #pragma unroll
-    for (int i = 31; i >= 0; --i) {
-      run += dGv[i];
-      dGv[i] = run;
+    for (int i = 0; i < 16; ++i) {
+      run += Gc[i];
+      Gc[i] = run;
     }
-    if (half == 1) carryD[kk] = run;
+    carryG[b][kk] = run;
   }
   __syncthreads();
   {
-    const float add = half ? 0.f : carryD[kk];
+    float add = 0.f;
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      const int t = half * 32 + i;
+    for (int bb = 0; bb < 3; ++bb) add += (bb < b) ? carryG[bb][kk] : 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) Gc[i] = (Gc[i] + add) * LOG2E;
+  }
+#pragma unroll
+  for (int t = 0; t < 16; ++t) {
+#pragma unroll
+    for (int j = 0; j <= t; ++j) {
+      const float2 a = sA[b][t][j];
+      const float D = ex2(Gc[t] - Gc[j]);
+      const float sa = p.scale * a.x;
+      const float kd = kv[j] * D;
+      dq[t] = fmaf(sa, kd, dq[t]);
+      dkp[t] = fmaf(a.y, kd, dkp[t]);
+      dkn[j] = fmaf(D, sa * qv[t] + a.y * kv[t], dkn[j]);
+    }
+  }
+  // dG = q dq + k (dk+ - dk-); dg = reverse cumsum over the chunk (the last row also carries the chunk-end terms)
+  float dGv[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int t = b * 16 + i;
+    dGv[i] = qv[i] * dq[i] + kv[i] * (dkp[i] - dkn[i]);
+    if (t < len) {
+      const size_t gi = (static_cast<size_t>(ci.tok0 + t) * p.H + h) * KD + kk;
+      p.dq[gi] = __float2bfloat16_rn(dq[i]);
+      p.dk[gi] = __float2bfloat16_rn(dkp[i] + dkn[i]);
+    }
+  }
+  if (b == 3) dGv[15] += p.DGL[tile * KD + kk];
+  {
+    float run = 0.f;
+#pragma unroll
+    for (int i = 15; i >= 0; --i) {
+      run += dGv[i];
+      dGv[i] = run;
+    }
+    carryD[b][kk] = run;
+  }
+  __syncthreads();
+  {
+    float add = 0.f;
+#pragma unroll
+    for (int bb = 1; bb < 4; ++bb) add += (bb > b) ? carryD[bb][kk] : 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int t = b * 16 + i;
       if (t < len) p.dg[(static_cast<size_t>(ci.tok0 + t) * p.H + h) * KD + kk] = dGv[i] + add;
     }
   }
@@ -985,6 +984,8 @@ static cudaError_t set_bwd_attrs() {
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(kda_chunk_bwd_main_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                static_cast<int>(sizeof(MainSmem)));
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(kda_chunk_bwd_finish_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 25);
     g_battr_err = e;
   });
   return g_battr_err;
@@ -1058,7 +1059,7 @@ extern "C" int kda_chunk_bwd(const kda_chunk_args* args, void* stream) {
   fp.DQA = w.DQA; fp.DKP = w.DKP; fp.DKN = w.DKN; fp.DAD = w.DAD; fp.DGL = w.DGL;
   fp.dq = static_cast<__nv_bfloat16*>(a.dq); fp.dk = static_cast<__nv_bfloat16*>(a.dk); fp.dg = a.dg;
   fp.N = a.N; fp.H = a.H; fp.scale = a.scale;
-  kda_chunk_bwd_finish_kernel<<<dim3(NTmax, a.H), 256, 0, st>>>(fp);
+  kda_chunk_bwd_finish_kernel<<<dim3(NTmax, a.H), 512, 0, st>>>(fp);
   if ((e = cudaGetLastError()) != cudaSuccess) return static_cast<int>(e);
   prof_mark(prof, KDA_STAGE_BWD_FINISH, st);
 

@@ -53,18 +53,21 @@ __global__ void __launch_bounds__(1024) kda_chunk_tables_kernel(const int* __res
 // =================================================================================================
 constexpr int QS = 136;   // bf16 elements per padded row of the q/k/v tiles (272 B: ldmatrix rows hit distinct banks)
 constexpr int GS = 136;   // floats per padded row of G
-constexpr int AS = 68;    // floats per padded row of the 64x64 matrices
+constexpr int AS = 68;    // floats per padded row of the fp32 64x64 matrix
+constexpr int TS = 72;    // bf16 elements per padded row of the bf16 64x64 matrix (144 B)
 
+// 113,920 bytes: two CTAs per SM.
 struct PrepSmem {
-  __nv_bfloat16 q[C * QS];
+  __nv_bfloat16 q[C * QS];   // q; then the scratch X of the block-merge products; then k * Gam
   __nv_bfloat16 k[C * QS];
   __nv_bfloat16 v[C * QS];
-  float G[C * GS];        // log2-domain inclusive cumsum of g
-  float Akk[C * AS];      // beta_t <k_t D, k_j>, then overwritten by Tm = (I + Akk)^-1
-  float Aqk[C * AS];      // scale <q_t D, k_j>
-  float X[32 * 33];       // scratch of the block-merge products
+  float G[C * GS];           // log2-domain inclusive cumsum of g; at the very end the staged UT and W tiles
+  float Akk[C * AS];         // raw <k_t D, k_j>, then beta_t * raw, then Tm = (I + Akk)^-1
+  __nv_bfloat16 Aqk[C * TS]; // scale <q_t D, k_j>, lower triangle incl. diagonal
   float beta[C];
 };
+static_assert(32 * 33 * 4 <= C * QS * 2, "X must fit the q buffer");
+static_assert(TILE_VT + TILE_TK <= C * GS * 4, "staged tiles must fit the G buffer");
 
 struct PrepParams {
   const __nv_bfloat16 *q, *k, *v;
@@ -77,7 +80,86 @@ struct PrepParams {
   float scale;
 };
 
-__global__ void __launch_bounds__(256, 1) kda_chunk_prepare_kernel(const PrepParams p) {
+// Sum over the 32 lanes of 32 per-lane values at once: afterwards lane L holds the total of slot L.
+// 31 shuffles instead of 32 x 5.
+__device__ __forceinline__ float butterfly32(float (&v)[32], int lane) {
+#pragma unroll
+  for (int o = 16; o >= 1; o >>= 1) {
+    const bool up = (lane & o) != 0;
+#pragma unroll
+    for (int i = 0; i < o; ++i) {
+      const float mine = up ? v[i + o] : v[i];
+      const float other = up ? v[i] : v[i + o];
+      v[i] = mine + __shfl_xor_sync(0xffffffffu, other, o);
+    }
+  }
+  return v[0];
+}
+
+// Diagonal 16x16 block `b`, rows RS, RS+4, RS+8, RS+12 of the block, pairwise decay exp2(G_t - G_j).
+// Lanes own four key columns each; the per-lane partial dot products of up to 16 (t, j) pairs per matrix
+// are reduced together by butterfly32 (slots 0..15: q.k, slots 16..31: k.k).
+template <int RS>
+__device__ __forceinline__ void prep_diag_task(PrepSmem& s, const int b, const int lane, const float scale) {
+  const int r0 = 16 * b;
+  // pass A: rows RS and RS+4 (slots 0..3 / 4..11, and 16..19 / 20..27); pass B: row RS+8; pass C: row RS+12
+#pragma unroll
+  for (int pass = 0; pass < 3; ++pass) {
+    const int nrows = (pass == 0) ? 2 : 1;
+    const int rbase = (pass == 0) ? RS : (pass == 1 ? RS + 8 : RS + 12);      // first row of the pass
+    const int jmax = (pass == 0) ? RS + 4 : rbase;                            // last column needed
+    float4 Gt[2];
+    float qv[2][4], kv[2][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      if (i < nrows) {
+        const int t = r0 + rbase + 4 * i;
+        Gt[i] = *reinterpret_cast<const float4*>(&s.G[t * GS + lane * 4]);
+        const uint2 qr = *reinterpret_cast<const uint2*>(&s.q[t * QS + lane * 4]);
+        const uint2 kr = *reinterpret_cast<const uint2*>(&s.k[t * QS + lane * 4]);
+        const float2 q0 = unpack_bf16(qr.x), q1 = unpack_bf16(qr.y), k0 = unpack_bf16(kr.x), k1 = unpack_bf16(kr.y);
+        qv[i][0] = q0.x; qv[i][1] = q0.y; qv[i][2] = q1.x; qv[i][3] = q1.y;
+        kv[i][0] = k0.x; kv[i][1] = k0.y; kv[i][2] = k1.x; kv[i][3] = k1.y;
+      }
+    }
+    float val[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) val[i] = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      if (j <= jmax) {
+        const float4 Gj = *reinterpret_cast<const float4*>(&s.G[(r0 + j) * GS + lane * 4]);
+        const uint2 jr = *reinterpret_cast<const uint2*>(&s.k[(r0 + j) * QS + lane * 4]);
+        const float2 j0 = unpack_bf16(jr.x), j1 = unpack_bf16(jr.y);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          if (i < nrows && j <= rbase + 4 * i) {
+            const float d0 = j0.x * ex2(Gt[i].x - Gj.x), d1 = j0.y * ex2(Gt[i].y - Gj.y);
+            const float d2 = j1.x * ex2(Gt[i].z - Gj.z), d3 = j1.y * ex2(Gt[i].w - Gj.w);
+            const int slot = (pass == 0 && i == 1) ? 4 + j : j;
+            val[slot] = qv[i][0] * d0 + qv[i][1] * d1 + qv[i][2] * d2 + qv[i][3] * d3;
+            val[16 + slot] = kv[i][0] * d0 + kv[i][1] * d1 + kv[i][2] * d2 + kv[i][3] * d3;
+          }
+        }
+      }
+    }
+    const float x = butterfly32(val, lane);
+    // lane -> (row, column, matrix)
+    const int sl = lane & 15;
+    int i = 0, j = sl;
+    if (pass == 0 && sl >= 4) { i = 1; j = sl - 4; }
+    const int trow = rbase + 4 * i;                 // row inside the block
+    const bool in_range = (pass == 0) ? (sl < 12) : true;
+    const int t = r0 + trow;
+    if (lane < 16) {
+      if (in_range && j <= trow) s.Aqk[t * TS + r0 + j] = __float2bfloat16_rn(scale * x);
+    } else {
+      if (in_range && j < trow) s.Akk[t * AS + r0 + j] = x;   // raw; beta_t is applied later
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256, 2) kda_chunk_prepare_kernel(const PrepParams p) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   PrepSmem& s = *reinterpret_cast<PrepSmem*>(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gid = lane >> 2, tig = lane & 3;
@@ -105,10 +187,8 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_prepare_kernel(const PrepPar
     }
     cp_async_commit();
     if (tid < C) s.beta[tid] = (tid < len) ? __ldg(p.beta + static_cast<size_t>(ci.tok0 + tid) * p.H + h) : 0.f;
-    for (int i = tid; i < C * AS; i += 256) {
-      s.Akk[i] = 0.f;
-      s.Aqk[i] = 0.f;
-    }
+    for (int i = tid; i < C * AS; i += 256) s.Akk[i] = 0.f;
+    for (int i = tid; i < C * TS / 2; i += 256) reinterpret_cast<uint32_t*>(s.Aqk)[i] = 0u;
     cp_async_wait<0>();
     __syncthreads();
   }
@@ -129,46 +209,41 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_prepare_kernel(const PrepPar
     }
   }
 
-  // ---- P2: G = cumsum(g) * log2(e), one column per thread -----------------------------------------
-  if (tid < KD) {
+  // ---- P2: G = cumsum(g) * log2(e): two half-columns per column, then the carry ----------------------
+  {
+    const int col = tid & 127, half = tid >> 7;
+    float gv[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) gv[i] = s.G[(half * 32 + i) * GS + col];
     float run = 0.f;
-#pragma unroll 8
-    for (int t = 0; t < C; ++t) {
-      run += s.G[t * GS + tid];
-      s.G[t * GS + tid] = run * LOG2E;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      run += gv[i];
+      gv[i] = run;
+    }
+    if (half == 0) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) s.G[i * GS + col] = gv[i] * LOG2E;
+    }
+    __syncthreads();   // row 31 of the first half is final
+    if (half == 1) {
+      const float carry = s.G[31 * GS + col];          // already in the log2 domain
+#pragma unroll
+      for (int i = 0; i < 32; ++i) s.G[(32 + i) * GS + col] = carry + gv[i] * LOG2E;
     }
   }
   __syncthreads();
 
-  // ---- P3a: diagonal 16x16 blocks, pairwise decay exp2(G_t - G_j) (never a factorisation: range-safe)
-  // A warp takes rows {warp, 15-warp} of each block (equal work); lanes own 4 key columns each.
-  for (int b = 0; b < 4; ++b) {
-#pragma unroll 1
-    for (int rr = 0; rr < 2; ++rr) {
-      const int t = 16 * b + (rr ? 15 - warp : warp);
-      const float4 Gt = *reinterpret_cast<const float4*>(&s.G[t * GS + lane * 4]);
-      const uint2 qr = *reinterpret_cast<const uint2*>(&s.q[t * QS + lane * 4]);
-      const uint2 kr = *reinterpret_cast<const uint2*>(&s.k[t * QS + lane * 4]);
-      const float2 q0 = unpack_bf16(qr.x), q1 = unpack_bf16(qr.y), k0 = unpack_bf16(kr.x), k1 = unpack_bf16(kr.y);
-#pragma unroll 2
-      for (int j = 16 * b; j <= t; ++j) {
-        const float4 Gj = *reinterpret_cast<const float4*>(&s.G[j * GS + lane * 4]);
-        const uint2 jr = *reinterpret_cast<const uint2*>(&s.k[j * QS + lane * 4]);
-        const float2 j0 = unpack_bf16(jr.x), j1 = unpack_bf16(jr.y);
-        const float d0 = j0.x * ex2(Gt.x - Gj.x), d1 = j0.y * ex2(Gt.y - Gj.y);
-        const float d2 = j1.x * ex2(Gt.z - Gj.z), d3 = j1.y * ex2(Gt.w - Gj.w);
-        const float pq = q0.x * d0 + q0.y * d1 + q1.x * d2 + q1.y * d3;
-        const float pk = k0.x * d0 + k0.y * d1 + k1.x * d2 + k1.y * d3;
-        // lanes 0..15 end with sum(pq), lanes 16..31 with sum(pk)
-        const bool hi = lane & 16;
-        float x = (hi ? pk : pq) + __shfl_xor_sync(0xffffffffu, hi ? pq : pk, 16);
-        x += __shfl_xor_sync(0xffffffffu, x, 8);
-        x += __shfl_xor_sync(0xffffffffu, x, 4);
-        x += __shfl_xor_sync(0xffffffffu, x, 2);
-        x += __shfl_xor_sync(0xffffffffu, x, 1);
-        if (lane == 0) s.Aqk[t * AS + j] = p.scale * x;
-        if (lane == 16 && j < t) s.Akk[t * AS + j] = x;   // raw <k_t D, k_j>; beta_t is applied below
-      }
+  // ---- P3a: diagonal 16x16 blocks, pairwise decay exp2(G_t - G_j) (never a factorisation: range-safe).
+  // Task (block b, row set RS); a warp takes RS and 3-RS of one block so that every warp has 68 pairs.
+  {
+    const int b = warp & 3;
+    if (warp < 4) {
+      prep_diag_task<0>(s, b, lane, p.scale);
+      prep_diag_task<3>(s, b, lane, p.scale);
+    } else {
+      prep_diag_task<1>(s, b, lane, p.scale);
+      prep_diag_task<2>(s, b, lane, p.scale);
     }
   }
 
@@ -213,34 +288,65 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_prepare_kernel(const PrepPar
       mma16816(ck, ak, b0, b1);
     }
     const int col = nt * 8 + tig * 2;
-    s.Aqk[ta * AS + col] = p.scale * cq[0]; s.Aqk[ta * AS + col + 1] = p.scale * cq[1];
-    s.Aqk[tb * AS + col] = p.scale * cq[2]; s.Aqk[tb * AS + col + 1] = p.scale * cq[3];
-    s.Akk[ta * AS + col] = ck[0]; s.Akk[ta * AS + col + 1] = ck[1];
-    s.Akk[tb * AS + col] = ck[2]; s.Akk[tb * AS + col + 1] = ck[3];
+    *reinterpret_cast<uint32_t*>(&s.Aqk[ta * TS + col]) = pack_bf16(p.scale * cq[0], p.scale * cq[1]);
+    *reinterpret_cast<uint32_t*>(&s.Aqk[tb * TS + col]) = pack_bf16(p.scale * cq[2], p.scale * cq[3]);
+    *reinterpret_cast<float2*>(&s.Akk[ta * AS + col]) = make_float2(ck[0], ck[1]);
+    *reinterpret_cast<float2*>(&s.Akk[tb * AS + col]) = make_float2(ck[2], ck[3]);
   }
   __syncthreads();
 
-  // ---- P3c: keep the raw k-k products for the backward (dbeta), then Akk = beta_t * raw ----------------
+  // ---- P3c: keep the raw k-k products for the backward (dbeta), then Akk = beta_t * raw;
+  // ---- P5a: elementwise tiles straight to global in their swizzled images: QG, KG, AQK, GL ------------
   {
     unsigned char* gR = p.RKK ? p.RKK + tile * TILE_TT : nullptr;
+    unsigned char* gA = p.AQK + tile * TILE_TT;
     for (int i = tid; i < C * 8; i += 256) {
       const int r = i >> 3, pc = i & 7;
       float4 a0 = *reinterpret_cast<const float4*>(&s.Akk[r * AS + pc * 8]);
       float4 a1 = *reinterpret_cast<const float4*>(&s.Akk[r * AS + pc * 8 + 4]);
+      const uint32_t off = swz<128>(r, pc * 8);
       if (gR)
-        *reinterpret_cast<uint4*>(gR + swz<128>(r, pc * 8)) =
+        *reinterpret_cast<uint4*>(gR + off) =
             make_uint4(pack_bf16(a0.x, a0.y), pack_bf16(a0.z, a0.w), pack_bf16(a1.x, a1.y), pack_bf16(a1.z, a1.w));
       const float b = s.beta[r];
       a0.x *= b; a0.y *= b; a0.z *= b; a0.w *= b; a1.x *= b; a1.y *= b; a1.z *= b; a1.w *= b;
       *reinterpret_cast<float4*>(&s.Akk[r * AS + pc * 8]) = a0;
       *reinterpret_cast<float4*>(&s.Akk[r * AS + pc * 8 + 4]) = a1;
+      *reinterpret_cast<uint4*>(gA + off) = *reinterpret_cast<const uint4*>(&s.Aqk[r * TS + pc * 8]);
     }
+    unsigned char* gQG = p.QG + tile * TILE_TK;
+    unsigned char* gKG = p.KG + tile * TILE_TK;
+    for (int i = tid; i < C * 16; i += 256) {
+      const int r = i >> 4, pc = i & 15;
+      const uint4 qr = *reinterpret_cast<const uint4*>(&s.q[r * QS + pc * 8]);
+      const uint4 kr = *reinterpret_cast<const uint4*>(&s.k[r * QS + pc * 8]);
+      const float4 Ga = *reinterpret_cast<const float4*>(&s.G[r * GS + pc * 8]);
+      const float4 Gb = *reinterpret_cast<const float4*>(&s.G[r * GS + pc * 8 + 4]);
+      const float4 La = *reinterpret_cast<const float4*>(&s.G[(C - 1) * GS + pc * 8]);
+      const float4 Lb = *reinterpret_cast<const float4*>(&s.G[(C - 1) * GS + pc * 8 + 4]);
+      const float g8[8] = {Ga.x, Ga.y, Ga.z, Ga.w, Gb.x, Gb.y, Gb.z, Gb.w};
+      const float l8[8] = {La.x, La.y, La.z, La.w, Lb.x, Lb.y, Lb.z, Lb.w};
+      const uint32_t qw[4] = {qr.x, qr.y, qr.z, qr.w}, kw[4] = {kr.x, kr.y, kr.z, kr.w};
+      uint32_t oq[4], ok[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 qq = unpack_bf16(qw[e]), kk = unpack_bf16(kw[e]);
+        const float e0 = ex2(g8[2 * e]), e1 = ex2(g8[2 * e + 1]);
+        oq[e] = pack_bf16(p.scale * qq.x * e0, p.scale * qq.y * e1);
+        ok[e] = pack_bf16(kk.x * ex2(l8[2 * e] - g8[2 * e]), kk.y * ex2(l8[2 * e + 1] - g8[2 * e + 1]));
+      }
+      const uint32_t off = swz<256>(r, pc * 8);
+      *reinterpret_cast<uint4*>(gQG + off) = make_uint4(oq[0], oq[1], oq[2], oq[3]);
+      *reinterpret_cast<uint4*>(gKG + off) = make_uint4(ok[0], ok[1], ok[2], ok[3]);
+    }
+    if (tid < KD) reinterpret_cast<float*>(p.GL + tile * TILE_GL)[tid] = ex2(s.G[(C - 1) * GS + tid]);
   }
-  __syncthreads();
+  __syncthreads();   // every read of s.q is done: its buffer becomes the scratch X, later k * Gam
 
   // ---- P4: Tm = (I + Akk)^-1, fp32.  16x16 diagonal blocks by forward substitution (one column per
   // thread, in registers), then two levels of block merges  T21 = -T22 A21 T11.
   {
+    float* sX = reinterpret_cast<float*>(s.q);
     float x[16];
     if (tid < 64) {
       const int b = tid >> 4, cc = tid & 15;
@@ -268,7 +374,7 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_prepare_kernel(const PrepPar
       float* A21 = &s.Akk[(base + 16) * AS + base];
       const float* T11 = &s.Akk[base * AS + base];
       const float* T22 = &s.Akk[(base + 16) * AS + base + 16];
-      float* X = &s.X[pr * 16 * 17];
+      float* X = &sX[pr * 16 * 17];
       float r[2];
 #pragma unroll
       for (int o = 0; o < 2; ++o) {
@@ -317,7 +423,7 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_prepare_kernel(const PrepPar
 #pragma unroll
       for (int o = 0; o < 4; ++o) {
         const int idx = tid * 4 + o;
-        s.X[(idx >> 5) * 33 + (idx & 31)] = r[o];
+        sX[(idx >> 5) * 33 + (idx & 31)] = r[o];
       }
       __syncthreads();
 #pragma unroll
@@ -325,7 +431,7 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_prepare_kernel(const PrepPar
         const int idx = tid * 4 + o, i = idx >> 5, jj = idx & 31;
         float acc = 0.f;
 #pragma unroll 8
-        for (int m = 0; m < 32; ++m) acc += T22[i * AS + m] * s.X[m * 33 + jj];
+        for (int m = 0; m < 32; ++m) acc += T22[i * AS + m] * sX[m * 33 + jj];
         r[o] = -acc;
       }
       __syncthreads();
@@ -338,54 +444,17 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_prepare_kernel(const PrepPar
     }
   }
 
-  // ---- P5a: elementwise tiles straight to global in their swizzled images: QG, KG, AQK, TI, GL ---------
-  {
-    unsigned char* gQG = p.QG + tile * TILE_TK;
-    unsigned char* gKG = p.KG + tile * TILE_TK;
-    for (int i = tid; i < C * 16; i += 256) {
-      const int r = i >> 4, pc = i & 15;
-      const uint4 qr = *reinterpret_cast<const uint4*>(&s.q[r * QS + pc * 8]);
-      const uint4 kr = *reinterpret_cast<const uint4*>(&s.k[r * QS + pc * 8]);
-      const float4 Ga = *reinterpret_cast<const float4*>(&s.G[r * GS + pc * 8]);
-      const float4 Gb = *reinterpret_cast<const float4*>(&s.G[r * GS + pc * 8 + 4]);
-      const float4 La = *reinterpret_cast<const float4*>(&s.G[(C - 1) * GS + pc * 8]);
-      const float4 Lb = *reinterpret_cast<const float4*>(&s.G[(C - 1) * GS + pc * 8 + 4]);
-      const float g8[8] = {Ga.x, Ga.y, Ga.z, Ga.w, Gb.x, Gb.y, Gb.z, Gb.w};
-      const float l8[8] = {La.x, La.y, La.z, La.w, Lb.x, Lb.y, Lb.z, Lb.w};
-      const uint32_t qw[4] = {qr.x, qr.y, qr.z, qr.w}, kw[4] = {kr.x, kr.y, kr.z, kr.w};
-      uint32_t oq[4], ok[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float2 qq = unpack_bf16(qw[e]), kk = unpack_bf16(kw[e]);
-        const float e0 = ex2(g8[2 * e]), e1 = ex2(g8[2 * e + 1]);
-        oq[e] = pack_bf16(p.scale * qq.x * e0, p.scale * qq.y * e1);
-        ok[e] = pack_bf16(kk.x * ex2(l8[2 * e] - g8[2 * e]), kk.y * ex2(l8[2 * e + 1] - g8[2 * e + 1]));
-      }
-      const uint32_t off = swz<256>(r, pc * 8);
-      *reinterpret_cast<uint4*>(gQG + off) = make_uint4(oq[0], oq[1], oq[2], oq[3]);
-      *reinterpret_cast<uint4*>(gKG + off) = make_uint4(ok[0], ok[1], ok[2], ok[3]);
-    }
-    unsigned char* gA = p.AQK + tile * TILE_TT;
-    unsigned char* gT = p.TI ? p.TI + tile * TILE_TT : nullptr;
+  // ---- P5b: Tm (bf16) to global for the backward; kGam = k * exp2(G) (bf16) into the q buffer ----------
+  if (p.TI) {
+    unsigned char* gT = p.TI + tile * TILE_TT;
     for (int i = tid; i < C * 8; i += 256) {
       const int r = i >> 3, pc = i & 7;
-      const float4 a0 = *reinterpret_cast<const float4*>(&s.Aqk[r * AS + pc * 8]);
-      const float4 a1 = *reinterpret_cast<const float4*>(&s.Aqk[r * AS + pc * 8 + 4]);
-      const uint32_t off = swz<128>(r, pc * 8);
-      *reinterpret_cast<uint4*>(gA + off) =
-          make_uint4(pack_bf16(a0.x, a0.y), pack_bf16(a0.z, a0.w), pack_bf16(a1.x, a1.y), pack_bf16(a1.z, a1.w));
-      if (gT) {
-        const float4 t0 = *reinterpret_cast<const float4*>(&s.Akk[r * AS + pc * 8]);
-        const float4 t1 = *reinterpret_cast<const float4*>(&s.Akk[r * AS + pc * 8 + 4]);
-        *reinterpret_cast<uint4*>(gT + off) =
-            make_uint4(pack_bf16(t0.x, t0.y), pack_bf16(t0.z, t0.w), pack_bf16(t1.x, t1.y), pack_bf16(t1.z, t1.w));
-      }
+      const float4 t0 = *reinterpret_cast<const float4*>(&s.Akk[r * AS + pc * 8]);
+      const float4 t1 = *reinterpret_cast<const float4*>(&s.Akk[r * AS + pc * 8 + 4]);
+      *reinterpret_cast<uint4*>(gT + swz<128>(r, pc * 8)) =
+          make_uint4(pack_bf16(t0.x, t0.y), pack_bf16(t0.z, t0.w), pack_bf16(t1.x, t1.y), pack_bf16(t1.z, t1.w));
     }
-    if (tid < KD) reinterpret_cast<float*>(p.GL + tile * TILE_GL)[tid] = ex2(s.G[(C - 1) * GS + tid]);
   }
-  __syncthreads();   // every read of s.q is done: its buffer becomes k * Gam
-
-  // ---- P5b: kGam = k * exp2(G) (bf16) into the q buffer ---------------------------------------------
   for (int i = tid; i < C * 16; i += 256) {
     const int r = i >> 4, pc = i & 15;
     const uint4 kr = *reinterpret_cast<const uint4*>(&s.k[r * QS + pc * 8]);
@@ -396,10 +465,13 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_prepare_kernel(const PrepPar
         make_uint4(pack_bf16(k0.x * ex2(Ga.x), k0.y * ex2(Ga.y)), pack_bf16(k1.x * ex2(Ga.z), k1.y * ex2(Ga.w)),
                    pack_bf16(k2.x * ex2(Gb.x), k2.y * ex2(Gb.y)), pack_bf16(k3.x * ex2(Gb.z), k3.y * ex2(Gb.w)));
   }
-  __syncthreads();
+  __syncthreads();   // G is dead from here on: its buffer stages the UT and W tiles
 
   // ---- P5c: u = (Tm beta) v,  w = (Tm beta) kGam on tensor cores.  Warp = (row tile mt, column half nh).
+  // The accumulators are written into swizzled tile images in shared memory and leave with two TMA bulk stores.
   {
+    unsigned char* stUT = reinterpret_cast<unsigned char*>(s.G);
+    unsigned char* stW = stUT + TILE_VT;
     const int mt = warp & 3, nh = warp >> 2;
     uint32_t a[4][4];
 #pragma unroll
@@ -416,8 +488,6 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_prepare_kernel(const PrepPar
       a[ks][2] = pack_bf16(t01.x * b1.x, t01.y * b1.y);
       a[ks][3] = pack_bf16(t11.x * b1.x, t11.y * b1.y);
     }
-    unsigned char* gW = p.W + tile * TILE_TK;
-    unsigned char* gUT = p.UT + tile * TILE_VT;
 #pragma unroll 1
     for (int which = 0; which < 2; ++which) {
       const __nv_bfloat16* Bs = which ? s.q : s.v;   // kGam or v, [token j][column]
@@ -441,15 +511,23 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_prepare_kernel(const PrepPar
       for (int n = 0; n < 8; ++n) {
         const int col = nh * 64 + n * 8 + tig * 2;
         if (which) {   // W tile [t][k]
-          *reinterpret_cast<uint32_t*>(gW + swz<256>(ta, col)) = pack_bf16(acc[n][0], acc[n][1]);
-          *reinterpret_cast<uint32_t*>(gW + swz<256>(tb, col)) = pack_bf16(acc[n][2], acc[n][3]);
+          *reinterpret_cast<uint32_t*>(stW + swz<256>(ta, col)) = pack_bf16(acc[n][0], acc[n][1]);
+          *reinterpret_cast<uint32_t*>(stW + swz<256>(tb, col)) = pack_bf16(acc[n][2], acc[n][3]);
         } else {       // UT tile [v][t]
-          *reinterpret_cast<__nv_bfloat16*>(gUT + swz<128>(col, ta)) = __float2bfloat16_rn(acc[n][0]);
-          *reinterpret_cast<__nv_bfloat16*>(gUT + swz<128>(col + 1, ta)) = __float2bfloat16_rn(acc[n][1]);
-          *reinterpret_cast<__nv_bfloat16*>(gUT + swz<128>(col, tb)) = __float2bfloat16_rn(acc[n][2]);
-          *reinterpret_cast<__nv_bfloat16*>(gUT + swz<128>(col + 1, tb)) = __float2bfloat16_rn(acc[n][3]);
+          *reinterpret_cast<__nv_bfloat16*>(stUT + swz<128>(col, ta)) = __float2bfloat16_rn(acc[n][0]);
+          *reinterpret_cast<__nv_bfloat16*>(stUT + swz<128>(col + 1, ta)) = __float2bfloat16_rn(acc[n][1]);
+          *reinterpret_cast<__nv_bfloat16*>(stUT + swz<128>(col, tb)) = __float2bfloat16_rn(acc[n][2]);
+          *reinterpret_cast<__nv_bfloat16*>(stUT + swz<128>(col + 1, tb)) = __float2bfloat16_rn(acc[n][3]);
         }
       }
+    }
+    fence_proxy_async();   // the staged tiles (generic-proxy writes) are read next by the bulk-copy engine
+    __syncthreads();
+    if (tid == 0) {
+      bulk_s2g(p.UT + tile * TILE_VT, stUT, TILE_VT);
+      bulk_s2g(p.W + tile * TILE_TK, stW, TILE_TK);
+      bulk_commit();
+      bulk_wait_read<0>();   // shared memory must stay valid until the engine has read it
     }
   }
 }
@@ -709,6 +787,9 @@ static cudaError_t set_attrs() {
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(kda_chunk_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                static_cast<int>(sizeof(ScanSmem)));
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(kda_chunk_prepare_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                               cudaSharedmemCarveoutMaxShared);
     g_attr_err = e;
   });
   return g_attr_err;
