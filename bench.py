@@ -52,8 +52,7 @@ KERNEL_WORK = {
     "scan": (6 * K_ * V_ + 2 * C_ * V_, 4 * _TK + _TT + 8 + 2 * V_ + _VK + _TK),
     "bwd_scan": (6 * K_ * V_ + 2 * C_ * V_, 3 * _TK + _TT + 8 + 2 * V_ + _VK + _TK),
     "bwd_main": (6 * K_ * V_ + 12 * C_ * K_ + 6 * C_ * V_ + 4 * C_ * C_,
-                 _IN + 2 * V_ + 2 * _TT + 2 * _VK + 2 * _TK + 2 * V_ + 4 + 3 * 4 * K_ + 128 + 8),
-    "bwd_finish": (8 * C_ * K_ / 4.0, 2 * K_ * 2 + 4 * K_ + 3 * 4 * K_ + 128 + 8 + 2 * 2 * K_ + 4 * K_),
+                 _IN + 2 * V_ + 2 * _TT + 2 * _VK + 2 * _TK + (2 * K_ + 2 * K_ + 2 * V_ + 4 * K_ + 4)),
 }
 
 
@@ -229,7 +228,7 @@ def main():
                               output_final_state=True, cu_seqlens=cu)
             grads = torch.autograd.grad([o, ht], leaves, [x["do"], x["dht"]])
             return (o, ht) + tuple(grads)
-        launches_per_step = 6
+        launches_per_step = 5
     else:
         grad_names = []
 

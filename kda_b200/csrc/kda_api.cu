@@ -29,6 +29,8 @@ extern "C" const char* kda_b200_strerror(int code) {
 
 namespace kda {
 
+long long* g_dbg_clocks = nullptr;
+
 constexpr int PROF_RING = 256;          // calls kept between two reads
 constexpr int PROF_MARKS = 6;           // marks per call (a forward uses 3, a backward up to 5)
 
@@ -103,4 +105,9 @@ extern "C" int kda_b200_profile_read(float* stage_ms, int* stage_launches, int r
   }
   if (reset) g_prof_used = 0;
   return KDA_OK;
+}
+
+// development aid (not part of the public header): device buffer of >= 64 long long for phase clocks
+extern "C" __attribute__((visibility("default"))) void kda_b200_debug_clocks(void* device_buffer) {
+  kda::g_dbg_clocks = static_cast<long long*>(device_buffer);
 }

@@ -32,9 +32,6 @@ struct ChunkWs {
   unsigned char *W, *UT, *KG, *QG, *AQK, *GL;          // always
   unsigned char *TI, *RKK, *HS, *VNEWT;                // save_for_backward only
   unsigned char *DH, *DVNEWT;                          // backward scratch (bf16 tiles)
-  float *DQA, *DKP, *DKN;                              // fp32 [tile][64][128] partial dq, dk(+), dk(-)
-  float *DAD;                                          // fp32 [tile][2][4][16][16] diagonal blocks of dAqk, beta*dAkk
-  float *DGL;                                          // fp32 [tile][128] extra gradient of G at the chunk's last row
   __nv_bfloat16 *QN, *KN;                              // [tokens][H][128] normalised q, k (use_qk_l2norm only)
   float *RSTD;                                         // [2][tokens][H]
   size_t fwd_bytes, bwd_bytes;
@@ -70,11 +67,6 @@ inline ChunkWs carve_ws(unsigned char* base, unsigned char* bwd_base, int64_t to
   auto takeb = [&](size_t bytes) { unsigned char* p = bwd_base ? bwd_base + boff : nullptr; boff += align_up(bytes); return p; };
   w.DH = takeb(tiles * TILE_VK);
   w.DVNEWT = takeb(tiles * TILE_VT);
-  w.DQA = reinterpret_cast<float*>(takeb(tiles * C * KD * 4));
-  w.DKP = reinterpret_cast<float*>(takeb(tiles * C * KD * 4));
-  w.DKN = reinterpret_cast<float*>(takeb(tiles * C * KD * 4));
-  w.DAD = reinterpret_cast<float*>(takeb(tiles * 2 * 4 * 256 * 4));
-  w.DGL = reinterpret_cast<float*>(takeb(tiles * KD * 4));
   if (l2norm) {
     w.QN = reinterpret_cast<__nv_bfloat16*>(takeb(static_cast<size_t>(tokens) * H * KD * 2));
     w.KN = reinterpret_cast<__nv_bfloat16*>(takeb(static_cast<size_t>(tokens) * H * KD * 2));
@@ -99,6 +91,13 @@ __device__ __forceinline__ ChunkInfo chunk_info(const int* seq_chunk_off, const 
   ci.len = rem < C ? static_cast<int>(rem) : C;
   return ci;
 }
+
+// ---- development aid: phase clocks of CTA (0,0), written when a buffer has been registered --------------
+extern long long* g_dbg_clocks;   // device pointer or NULL
+#define KDA_DBG_CLOCK(ptr, idx)                                                        \
+  do {                                                                                 \
+    if ((ptr) != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) (ptr)[idx] = clock64(); \
+  } while (0)
 
 // ---- optional per-kernel timing (host side, see kda_b200_profile_* in the public header) ------------
 struct ProfCall;                                  // one call's worth of events

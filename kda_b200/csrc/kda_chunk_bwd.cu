@@ -1,4 +1,4 @@
-// Chunked KDA backward for sm_100a.  Three kernels, all reading the tiles the forward left behind:
+// Chunked KDA backward for sm_100a.  Two kernels, both reading the tiles the forward left behind:
 //
 //  kda_chunk_bwd_scan_kernel   one CTA per (sequence, head): chunks in REVERSE order with the fp32 state
 //                              gradient in registers (transposed, one warp per 16 value columns):
@@ -6,10 +6,9 @@
 //                              stores dh' (gradient w.r.t. the state at the chunk's end) and dv_new per chunk.
 //  kda_chunk_bwd_main_kernel   one CTA per (chunk, head): every tensor-core product of the chunk's backward
 //                              (state-dependent terms, the backward through Tm = (I+Akk)^-1, the
-//                              off-diagonal 16x16 blocks of the intra-chunk terms); writes dv, dbeta and fp32
-//                              partial dq / dk(+) / dk(-) plus the diagonal blocks of dAqk, dAkk.
-//  kda_chunk_bwd_finish_kernel one CTA per (chunk, head), one thread per key column: the diagonal 16x16
-//                              blocks pairwise (range-safe), dg = reverse cumsum, final dq, dk, dg.
+//                              off-diagonal 16x16 blocks of the intra-chunk terms), then, one thread per key
+//                              column, the diagonal 16x16 blocks pairwise (range-safe), dg = reverse cumsum,
+//                              and the final dq, dk, dv, dg, dbeta.
 //
 // Gradient identities (G = in-chunk cumsum of g, Gam = exp G, D[t,j] = exp(G_t - G_j)):
 //   dqg = dO h^T,  dAqk = tril(dO v_new^T),  dkg = v_new dh'^T,  dw = -dv_new h^T,  du = dv_new
@@ -282,8 +281,13 @@ struct MainSmem {
   __nv_bfloat16 v[C * QS];
   float G[C * GS];
   float beta[C];
-  float red[8][C];          // per-warp partial row sums of dbeta
-  float hdh[4][KD];         // partial sums over v of h * dh'
+  union {
+    float red[8][C];        // per-warp partial row sums of dbeta (end of the kernel)
+    float hdh[4][KD];       // partial sums over v of h * dh' (phase A)
+  };
+  float dgl[KD];            // extra gradient of G at the chunk's last row
+  float carry[KD];          // cross-half carry of the reverse cumsum
+  float2 Ad[4][16][16];     // diagonal 16x16 blocks of (dAqk, beta dAkk), fp32
   unsigned char TI[TILE_TT];
   unsigned char RKK[TILE_TT];
   __nv_bfloat16 dO[C * QS];            // phase A;  later X  [64][TS]
@@ -291,8 +295,10 @@ struct MainSmem {
   unsigned char DH[TILE_VK];           // phase A;  later dw [64][QS] + dAk [64][TS]
   unsigned char VN[TILE_VT];           // phase A;  later dAq [64][TS]
   unsigned char DVN[TILE_VT];          // phases A and B
-  uint64_t bar;
+  uint64_t bar, bar2;
 };
+constexpr int FS = 136;   // floats per padded row of the staged fp32 [64][128] matrices
+static_assert(3 * C * FS * 4 <= C * QS * 2 + 2 * TILE_VK + 2 * TILE_VT, "staged dq/dk+/dk- must fit the dead regions");
 static_assert(sizeof(MainSmem) <= 227 * 1024, "MainSmem too large");
 static_assert(C * QS * 2 + C * TS * 2 <= TILE_VK, "aliasing of HS/DH regions");
 static_assert(C * TS * 2 <= TILE_VT && C * TS * 2 <= C * QS * 2, "aliasing of VN/dO regions");
@@ -303,10 +309,10 @@ struct MainParams {
   const int* cu;
   const int *seq_chunk_off, *chunk_seq;
   const unsigned char *TI, *RKK, *HS, *VNEWT, *DH, *DVNEWT;
-  __nv_bfloat16* dv;
-  float* dbeta;
-  float *DQA, *DKP, *DKN, *DAD, *DGL;
+  __nv_bfloat16 *dv, *dq, *dk;
+  float *dbeta, *dg;
   unsigned* status;
+  long long* dbg;
   int N, H;
   float scale;
 };
@@ -320,19 +326,29 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_kernel(const MainPa
   const ChunkInfo ci = chunk_info(p.seq_chunk_off, p.chunk_seq, p.cu, c);
   const int len = ci.len;
   const size_t tile = static_cast<size_t>(c) * p.H + h;
+  KDA_DBG_CLOCK(p.dbg, 0);
 
-  // ---- loads: tiles by bulk copy (one lane), token rows by 16-byte async copies ---------------------
+  // ---- loads in two groups: what phase A needs first (state tiles, dO), the rest lands behind phase A ----
   if (tid == 0) {
     mbar_init(&s.bar, 1);
+    mbar_init(&s.bar2, 1);
     fence_mbar_init();
-    mbar_expect_tx(&s.bar, 2 * TILE_TT + 2 * TILE_VK + 2 * TILE_VT);
-    bulk_g2s(s.TI, p.TI + tile * TILE_TT, TILE_TT, &s.bar);
-    bulk_g2s(s.RKK, p.RKK + tile * TILE_TT, TILE_TT, &s.bar);
+    mbar_expect_tx(&s.bar, 2 * TILE_VK + 2 * TILE_VT);
     bulk_g2s(s.HS, p.HS + tile * TILE_VK, TILE_VK, &s.bar);
     bulk_g2s(s.DH, p.DH + tile * TILE_VK, TILE_VK, &s.bar);
     bulk_g2s(s.VN, p.VNEWT + tile * TILE_VT, TILE_VT, &s.bar);
     bulk_g2s(s.DVN, p.DVNEWT + tile * TILE_VT, TILE_VT, &s.bar);
+    mbar_expect_tx(&s.bar2, 2 * TILE_TT);
+    bulk_g2s(s.TI, p.TI + tile * TILE_TT, TILE_TT, &s.bar2);
+    bulk_g2s(s.RKK, p.RKK + tile * TILE_TT, TILE_TT, &s.bar2);
   }
+  for (int i = tid; i < C * 16; i += 256) {
+    const int r = i >> 4, pc = i & 15;
+    const bool ok = r < len;
+    const size_t row = (static_cast<size_t>(ci.tok0 + (ok ? r : 0)) * p.H + h) * KD + pc * 8;
+    cp_async16(&s.dO[r * QS + pc * 8], p.d_o + row, ok);
+  }
+  cp_async_commit();
   for (int i = tid; i < C * 16; i += 256) {
     const int r = i >> 4, pc = i & 15;
     const bool ok = r < len;
@@ -340,7 +356,6 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_kernel(const MainPa
     cp_async16(&s.q[r * QS + pc * 8], p.q + row, ok);
     cp_async16(&s.k[r * QS + pc * 8], p.k + row, ok);
     cp_async16(&s.v[r * QS + pc * 8], p.v + row, ok);
-    cp_async16(&s.dO[r * QS + pc * 8], p.d_o + row, ok);
   }
   for (int i = tid; i < C * 32; i += 256) {
     const int r = i >> 5, pc = i & 31;
@@ -350,20 +365,12 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_kernel(const MainPa
   }
   cp_async_commit();
   if (tid < C) s.beta[tid] = (tid < len) ? __ldg(p.beta + static_cast<size_t>(ci.tok0 + tid) * p.H + h) : 0.f;
-  cp_async_wait<0>();
-  __syncthreads();   // also publishes the mbarrier init
-  if (tid < KD) {
-    float run = 0.f;
-#pragma unroll 8
-    for (int t = 0; t < C; ++t) {
-      run += s.G[t * GS + tid];
-      s.G[t * GS + tid] = run * LOG2E;
-    }
-  }
+  cp_async_wait<1>();   // dO has landed (this thread's pieces)
+  __syncthreads();      // everyone's dO pieces; also publishes the mbarrier inits
   const bool tiles_ok = mbar_wait(&s.bar, 0);
   if (!tiles_ok && tid == 0) atomicOr(p.status, 16u);
-  __syncthreads();
 
+  KDA_DBG_CLOCK(p.dbg, 1);
   const int n0 = warp * 16;                                    // this warp's 16 output columns (kk or v)
   const int j0 = warp * 8;                                     // this warp's 8 columns of the 64x64 products
   const int trow = (lane & 7) + (((lane >> 3) & 1) << 3), tcol = (lane >> 4) << 3;   // B stored [k][n]
@@ -429,7 +436,33 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_kernel(const MainPa
     s.hdh[vq][2 * kp] = ax;
     s.hdh[vq][2 * kp + 1] = ay;
   }
-  __syncthreads();   // (1) HS, DH, VN, dO are dead from here on
+  cp_async_wait<0>();
+  __syncthreads();   // (1) HS, DH, VN, dO are dead from here on; q, k, v, g have landed
+  KDA_DBG_CLOCK(p.dbg, 2);
+  {  // G = cumsum(g) * log2(e): two half-columns per column, then the carry
+    const int col = tid & 127, half = tid >> 7;
+    float gv[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) gv[i] = s.G[(half * 32 + i) * GS + col];
+    float run = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      run += gv[i];
+      gv[i] = run;
+    }
+    if (half == 0) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) s.G[i * GS + col] = gv[i] * LOG2E;
+    }
+    __syncthreads();
+    if (half == 1) {
+      const float carry = s.G[31 * GS + col];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) s.G[(32 + i) * GS + col] = carry + gv[i] * LOG2E;
+    }
+    if (!mbar_wait(&s.bar2, 0) && tid == 0) atomicOr(p.status, 16u);
+    __syncthreads();
+  }
 
   // ---- re-use of the dead regions --------------------------------------------------------------------
   __nv_bfloat16* sKG = reinterpret_cast<__nv_bfloat16*>(s.HS);                    // k * Gam      [64][QS]
@@ -438,7 +471,6 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_kernel(const MainPa
   __nv_bfloat16* sDAK = reinterpret_cast<__nv_bfloat16*>(s.DH + C * QS * 2);      // beta dAkk    [64][TS]
   __nv_bfloat16* sDAQ = reinterpret_cast<__nv_bfloat16*>(s.VN);                   // dAqk         [64][TS]
   __nv_bfloat16* sX = s.dO;                                                       // dTm Tm^T     [64][TS]
-  float* gDAD = p.DAD + tile * 2048;
 
   {
     // dw -> shared (bf16); dq(a) = scale Gam dqg; dk-(a) = dkg exp2(G_last - G); column sums of k dk_end
@@ -475,7 +507,7 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_kernel(const MainPa
         if (gid == 0) {
           const int col = n0 + nt * 8 + tig * 2 + e;
           const float hd = s.hdh[0][col] + s.hdh[1][col] + s.hdh[2][col] + s.hdh[3][col];
-          p.DGL[tile * KD + col] = x + ex2(s.G[(C - 1) * GS + col]) * hd;
+          s.dgl[col] = x + ex2(s.G[(C - 1) * GS + col]) * hd;
         }
       }
     }
@@ -488,8 +520,10 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_kernel(const MainPa
         const float x0 = (col <= row) ? dAq[mt][2 * hh] : 0.f;
         const float x1 = (col + 1 <= row) ? dAq[mt][2 * hh + 1] : 0.f;
         *reinterpret_cast<uint32_t*>(&sDAQ[row * TS + col]) = pack_bf16(x0, x1);
-        if ((warp >> 1) == mt)
-          *reinterpret_cast<float2*>(&gDAD[(0 * 4 + mt) * 256 + (gid + hh * 8) * 16 + (col & 15)]) = make_float2(x0, x1);
+        if ((warp >> 1) == mt) {
+          s.Ad[mt][gid + hh * 8][col & 15].x = x0;
+          s.Ad[mt][gid + hh * 8][(col & 15) + 1].x = x1;
+        }
       }
     }
     // k * Gam
@@ -505,6 +539,7 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_kernel(const MainPa
     }
   }
   __syncthreads();   // (2)
+  KDA_DBG_CLOCK(p.dbg, 3);
 
   // =========================== phase B: through Tm = (I + Akk)^-1 =====================================
   float pb[4][2];    // dbeta partial row sums: rows mt*16 + gid (+8)
@@ -544,6 +579,7 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_kernel(const MainPa
     }
   }
   __syncthreads();   // (3)
+  KDA_DBG_CLOCK(p.dbg, 4);
   {
     // X = dTm Tm^T
     float acc[4][4];
@@ -572,6 +608,7 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_kernel(const MainPa
     }
   }
   __syncthreads();   // (4)
+  KDA_DBG_CLOCK(p.dbg, 5);
   // Tm^T as A fragments: A[m=i][k=m'] = Tm[m'][i]
   uint32_t tA[4][4][4];
 #pragma unroll
@@ -605,8 +642,10 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_kernel(const MainPa
         pb[mt][hh] += x0 * raw.x + x1 * raw.y;
         const float br = s.beta[row];
         *reinterpret_cast<uint32_t*>(&sDAK[row * TS + col]) = pack_bf16(br * x0, br * x1);
-        if ((warp >> 1) == mt)
-          *reinterpret_cast<float2*>(&gDAD[(1 * 4 + mt) * 256 + (gid + hh * 8) * 16 + (col & 15)]) = make_float2(br * x0, br * x1);
+        if ((warp >> 1) == mt) {
+          s.Ad[mt][gid + hh * 8][col & 15].y = br * x0;
+          s.Ad[mt][gid + hh * 8][(col & 15) + 1].y = br * x1;
+        }
       }
     }
   }
@@ -680,6 +719,7 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_kernel(const MainPa
     }
   }
   __syncthreads();   // (5) dAq / dAk (bf16) complete
+  KDA_DBG_CLOCK(p.dbg, 6);
 
   // =========================== phase C: off-diagonal 16x16 blocks of the intra-chunk terms ============
   // decay factored around the first row r0 = 16 I of row block I (both factors <= 1), as in the forward
@@ -774,21 +814,23 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_kernel(const MainPa
     }
   }
 
-  // ---- results: fp32 partials (row-major [64][128]) and dbeta --------------------------------------
+  KDA_DBG_CLOCK(p.dbg, 7);
+  __syncthreads();   // (6) every shared-memory operand of phase C has been read: the regions become staging
+  // ---- stage the fp32 partial dq / dk+ / dk- as [64][FS] matrices; dbeta partial row sums --------------
+  float* stq = reinterpret_cast<float*>(s.dO);
+  float* stp = stq + C * FS;
+  float* stn = stp + C * FS;
   {
-    float* gq = p.DQA + tile * (C * KD);
-    float* gp = p.DKP + tile * (C * KD);
-    float* gn = p.DKN + tile * (C * KD);
 #pragma unroll
     for (int mt = 0; mt < 4; ++mt) {
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt) {
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
-          const size_t o = static_cast<size_t>(mt * 16 + gid + hh * 8) * KD + n0 + nt * 8 + tig * 2;
-          *reinterpret_cast<float2*>(gq + o) = make_float2(dqa[mt][nt][2 * hh], dqa[mt][nt][2 * hh + 1]);
-          *reinterpret_cast<float2*>(gp + o) = make_float2(dkp[mt][nt][2 * hh], dkp[mt][nt][2 * hh + 1]);
-          *reinterpret_cast<float2*>(gn + o) = make_float2(dkn[mt][nt][2 * hh], dkn[mt][nt][2 * hh + 1]);
+          const int o = (mt * 16 + gid + hh * 8) * FS + n0 + nt * 8 + tig * 2;
+          *reinterpret_cast<float2*>(stq + o) = make_float2(dqa[mt][nt][2 * hh], dqa[mt][nt][2 * hh + 1]);
+          *reinterpret_cast<float2*>(stp + o) = make_float2(dkp[mt][nt][2 * hh], dkp[mt][nt][2 * hh + 1]);
+          *reinterpret_cast<float2*>(stn + o) = make_float2(dkn[mt][nt][2 * hh], dkn[mt][nt][2 * hh + 1]);
         }
       }
     }
@@ -803,128 +845,80 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_kernel(const MainPa
       }
     }
   }
-  __syncthreads();   // (6)
+  __syncthreads();   // (7)
+  KDA_DBG_CLOCK(p.dbg, 8);
   if (tid < len) {
     float x = 0.f;
 #pragma unroll
     for (int w = 0; w < 8; ++w) x += s.red[w][tid];
     p.dbeta[static_cast<size_t>(ci.tok0 + tid) * p.H + h] = x;
   }
-}
 
-// =================================================================================================
-// per-chunk backward: diagonal blocks pairwise + epilogue, one thread per key column
-// =================================================================================================
-struct FinParams {
-  const __nv_bfloat16 *q, *k;
-  const float* g;
-  const int* cu;
-  const int *seq_chunk_off, *chunk_seq;
-  const float *DQA, *DKP, *DKN, *DAD, *DGL;
-  __nv_bfloat16 *dq, *dk;
-  float* dg;
-  int N, H;
-  float scale;
-};
-
-__global__ void __launch_bounds__(512, 1) kda_chunk_bwd_finish_kernel(const FinParams p) {
-  __shared__ float2 sA[4][16][16];     // (dAqk, beta dAkk) diagonal blocks
-  __shared__ float carryG[4][KD], carryD[4][KD];
-  const int tid = threadIdx.x, kk = tid & 127, b = tid >> 7;   // one thread per (key column, 16-row block)
-  const int c = blockIdx.x, h = blockIdx.y;
-  if (c >= p.seq_chunk_off[p.N]) return;
-  const ChunkInfo ci = chunk_info(p.seq_chunk_off, p.chunk_seq, p.cu, c);
-  const int len = ci.len;
-  const size_t tile = static_cast<size_t>(c) * p.H + h;
-  const float* gq = p.DQA + tile * (C * KD);
-  const float* gp = p.DKP + tile * (C * KD);
-  const float* gn = p.DKN + tile * (C * KD);
-
-  // issue every global load of this thread up front (all independent)
-  float Gc[16], qv[16], kv[16], dq[16], dkp[16], dkn[16];
-#pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const int t = b * 16 + i;
-    const bool ok = t < len;
-    const size_t gi = (static_cast<size_t>(ci.tok0 + (ok ? t : 0)) * p.H + h) * KD + kk;
-    Gc[i] = ok ? __ldg(p.g + gi) : 0.f;
-    qv[i] = ok ? __bfloat162float(p.q[gi]) : 0.f;
-    kv[i] = ok ? __bfloat162float(p.k[gi]) : 0.f;
-    dq[i] = __ldcs(gq + static_cast<size_t>(t) * KD + kk);
-    dkp[i] = __ldcs(gp + static_cast<size_t>(t) * KD + kk);
-    dkn[i] = __ldcs(gn + static_cast<size_t>(t) * KD + kk);
-  }
+  // =========================== phase D: diagonal 16x16 blocks pairwise + epilogue =======================
+  // One thread per key column and half chunk (two 16-row blocks): exp2(G_t - G_j) pairwise (range-safe),
+  // dG = q dq + k (dk+ - dk-), dg = reverse cumsum over the chunk, final dq / dk / dg.
   {
-    const float* gD = p.DAD + tile * 2048;
-    for (int i = tid; i < 1024; i += 512) {
-      const int bb = i >> 8, r = (i >> 4) & 15, cc = i & 15;
-      sA[bb][r][cc] = make_float2(gD[i], gD[1024 + i]);
+    const int kk = tid & 127, half = tid >> 7;
+    float dGv[32];
+#pragma unroll
+    for (int bb = 0; bb < 2; ++bb) {
+      const int b = half * 2 + bb;
+      float Gc[16], qv[16], kv[16], dq[16], dkp2[16], dkn2[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const int t = b * 16 + i;
+        Gc[i] = s.G[t * GS + kk];
+        qv[i] = __bfloat162float(s.q[t * QS + kk]);
+        kv[i] = __bfloat162float(s.k[t * QS + kk]);
+        dq[i] = stq[t * FS + kk];
+        dkp2[i] = stp[t * FS + kk];
+        dkn2[i] = stn[t * FS + kk];
+      }
+#pragma unroll
+      for (int t = 0; t < 16; ++t) {
+#pragma unroll
+        for (int j = 0; j <= t; ++j) {
+          const float2 a = s.Ad[b][t][j];
+          const float D = ex2(Gc[t] - Gc[j]);
+          const float sa = p.scale * a.x;
+          const float kd = kv[j] * D;
+          dq[t] = fmaf(sa, kd, dq[t]);
+          dkp2[t] = fmaf(a.y, kd, dkp2[t]);
+          dkn2[j] = fmaf(D, sa * qv[t] + a.y * kv[t], dkn2[j]);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const int t = b * 16 + i;
+        dGv[bb * 16 + i] = qv[i] * dq[i] + kv[i] * (dkp2[i] - dkn2[i]);
+        if (t < len) {
+          const size_t gi = (static_cast<size_t>(ci.tok0 + t) * p.H + h) * KD + kk;
+          p.dq[gi] = __float2bfloat16_rn(dq[i]);
+          p.dk[gi] = __float2bfloat16_rn(dkp2[i] + dkn2[i]);
+        }
+      }
+    }
+    if (half == 1) dGv[31] += s.dgl[kk];
+    {
+      float run = 0.f;
+#pragma unroll
+      for (int i = 31; i >= 0; --i) {
+        run += dGv[i];
+        dGv[i] = run;
+      }
+      if (half == 1) s.carry[kk] = run;
+    }
+    __syncthreads();
+    {
+      const float add = half ? 0.f : s.carry[kk];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const int t = half * 32 + i;
+        if (t < len) p.dg[(static_cast<size_t>(ci.tok0 + t) * p.H + h) * KD + kk] = dGv[i] + add;
+      }
     }
   }
-  // log2-domain cumsum of g for this column: local prefix, then the totals of the earlier blocks
-  {
-    float run = 0.f;
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      run += Gc[i];
-      Gc[i] = run;
-    }
-    carryG[b][kk] = run;
-  }
-  __syncthreads();
-  {
-    float add = 0.f;
-#pragma unroll
-    for (int bb = 0; bb < 3; ++bb) add += (bb < b) ? carryG[bb][kk] : 0.f;
-#pragma unroll
-    for (int i = 0; i < 16; ++i) Gc[i] = (Gc[i] + add) * LOG2E;
-  }
-#pragma unroll
-  for (int t = 0; t < 16; ++t) {
-#pragma unroll
-    for (int j = 0; j <= t; ++j) {
-      const float2 a = sA[b][t][j];
-      const float D = ex2(Gc[t] - Gc[j]);
-      const float sa = p.scale * a.x;
-      const float kd = kv[j] * D;
-      dq[t] = fmaf(sa, kd, dq[t]);
-      dkp[t] = fmaf(a.y, kd, dkp[t]);
-      dkn[j] = fmaf(D, sa * qv[t] + a.y * kv[t], dkn[j]);
-    }
-  }
-  // dG = q dq + k (dk+ - dk-); dg = reverse cumsum over the chunk (the last row also carries the chunk-end terms)
-  float dGv[16];
-#pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const int t = b * 16 + i;
-    dGv[i] = qv[i] * dq[i] + kv[i] * (dkp[i] - dkn[i]);
-    if (t < len) {
-      const size_t gi = (static_cast<size_t>(ci.tok0 + t) * p.H + h) * KD + kk;
-      p.dq[gi] = __float2bfloat16_rn(dq[i]);
-      p.dk[gi] = __float2bfloat16_rn(dkp[i] + dkn[i]);
-    }
-  }
-  if (b == 3) dGv[15] += p.DGL[tile * KD + kk];
-  {
-    float run = 0.f;
-#pragma unroll
-    for (int i = 15; i >= 0; --i) {
-      run += dGv[i];
-      dGv[i] = run;
-    }
-    carryD[b][kk] = run;
-  }
-  __syncthreads();
-  {
-    float add = 0.f;
-#pragma unroll
-    for (int bb = 1; bb < 4; ++bb) add += (bb > b) ? carryD[bb][kk] : 0.f;
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const int t = b * 16 + i;
-      if (t < len) p.dg[(static_cast<size_t>(ci.tok0 + t) * p.H + h) * KD + kk] = dGv[i] + add;
-    }
-  }
+  KDA_DBG_CLOCK(p.dbg, 9);
 }
 
 // =================================================================================================
@@ -984,8 +978,6 @@ static cudaError_t set_bwd_attrs() {
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(kda_chunk_bwd_main_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                static_cast<int>(sizeof(MainSmem)));
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(kda_chunk_bwd_finish_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 25);
     g_battr_err = e;
   });
   return g_battr_err;
@@ -1047,24 +1039,15 @@ extern "C" int kda_chunk_bwd(const kda_chunk_args* args, void* stream) {
   mp.q = q; mp.k = k; mp.v = static_cast<const __nv_bfloat16*>(a.v); mp.d_o = static_cast<const __nv_bfloat16*>(a.d_o);
   mp.g = a.g; mp.beta = a.beta; mp.cu = a.cu_seqlens; mp.seq_chunk_off = w.seq_chunk_off; mp.chunk_seq = w.chunk_seq;
   mp.TI = w.TI; mp.RKK = w.RKK; mp.HS = w.HS; mp.VNEWT = w.VNEWT; mp.DH = w.DH; mp.DVNEWT = w.DVNEWT;
-  mp.dv = static_cast<__nv_bfloat16*>(a.dv); mp.dbeta = a.dbeta;
-  mp.DQA = w.DQA; mp.DKP = w.DKP; mp.DKN = w.DKN; mp.DAD = w.DAD; mp.DGL = w.DGL; mp.status = w.status;
+  mp.dv = static_cast<__nv_bfloat16*>(a.dv); mp.dq = static_cast<__nv_bfloat16*>(a.dq); mp.dk = static_cast<__nv_bfloat16*>(a.dk);
+  mp.dbeta = a.dbeta; mp.dg = a.dg; mp.status = w.status; mp.dbg = g_dbg_clocks;
   mp.N = a.N; mp.H = a.H; mp.scale = a.scale;
   kda_chunk_bwd_main_kernel<<<dim3(NTmax, a.H), 256, sizeof(MainSmem), st>>>(mp);
   if ((e = cudaGetLastError()) != cudaSuccess) return static_cast<int>(e);
   prof_mark(prof, KDA_STAGE_BWD_MAIN, st);
 
-  FinParams fp{};
-  fp.q = q; fp.k = k; fp.g = a.g; fp.cu = a.cu_seqlens; fp.seq_chunk_off = w.seq_chunk_off; fp.chunk_seq = w.chunk_seq;
-  fp.DQA = w.DQA; fp.DKP = w.DKP; fp.DKN = w.DKN; fp.DAD = w.DAD; fp.DGL = w.DGL;
-  fp.dq = static_cast<__nv_bfloat16*>(a.dq); fp.dk = static_cast<__nv_bfloat16*>(a.dk); fp.dg = a.dg;
-  fp.N = a.N; fp.H = a.H; fp.scale = a.scale;
-  kda_chunk_bwd_finish_kernel<<<dim3(NTmax, a.H), 512, 0, st>>>(fp);
-  if ((e = cudaGetLastError()) != cudaSuccess) return static_cast<int>(e);
-  prof_mark(prof, KDA_STAGE_BWD_FINISH, st);
-
   if (l2) {
-    kda_l2norm_bwd_kernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, st>>>(w.QN, w.KN, w.RSTD, fp.dq, fp.dk, rows);
+    kda_l2norm_bwd_kernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, st>>>(w.QN, w.KN, w.RSTD, mp.dq, mp.dk, rows);
     if ((e = cudaGetLastError()) != cudaSuccess) return static_cast<int>(e);
     prof_mark(prof, KDA_STAGE_L2NORM, st);
   }

@@ -75,6 +75,7 @@ struct PrepParams {
   const int* cu;
   const int *seq_chunk_off, *chunk_seq;
   unsigned char *W, *UT, *KG, *QG, *AQK, *GL, *TI, *RKK;   // TI, RKK may be NULL
+  long long* dbg;
   int N, H;
   int use_l2norm;
   float scale;
@@ -168,6 +169,7 @@ __global__ void __launch_bounds__(256, 2) kda_chunk_prepare_kernel(const PrepPar
   const ChunkInfo ci = chunk_info(p.seq_chunk_off, p.chunk_seq, p.cu, c);
   const int len = ci.len;
   const size_t tile = static_cast<size_t>(c) * p.H + h;
+  KDA_DBG_CLOCK(p.dbg, 16);
 
   // ---- P1: stage q, k, v, g, beta; rows >= len are zero-filled -----------------------------------
   {
@@ -193,6 +195,7 @@ __global__ void __launch_bounds__(256, 2) kda_chunk_prepare_kernel(const PrepPar
     __syncthreads();
   }
 
+  KDA_DBG_CLOCK(p.dbg, 17);
   // ---- P1b: optional L2 normalisation of q and k rows (result rounded to bf16, as the unfused op does)
   if (p.use_l2norm) {
     for (int r = warp; r < C; r += 8) {
@@ -234,6 +237,7 @@ __global__ void __launch_bounds__(256, 2) kda_chunk_prepare_kernel(const PrepPar
   }
   __syncthreads();
 
+  KDA_DBG_CLOCK(p.dbg, 18);
   // ---- P3a: diagonal 16x16 blocks, pairwise decay exp2(G_t - G_j) (never a factorisation: range-safe).
   // Task (block b, row set RS); a warp takes RS and 3-RS of one block so that every warp has 68 pairs.
   {
@@ -247,6 +251,7 @@ __global__ void __launch_bounds__(256, 2) kda_chunk_prepare_kernel(const PrepPar
     }
   }
 
+  KDA_DBG_CLOCK(p.dbg, 19);
   // ---- P3b: off-diagonal 16x16 blocks on tensor cores.  For row block I the decay is factored around
   // the block's first row r0 = 16 I:  exp2(G_t - G_r0) * exp2(G_r0 - G_j), both factors <= 1 for j < r0 <= t.
   for (int u = warp; u < 12; u += 8) {
@@ -295,6 +300,7 @@ __global__ void __launch_bounds__(256, 2) kda_chunk_prepare_kernel(const PrepPar
   }
   __syncthreads();
 
+  KDA_DBG_CLOCK(p.dbg, 20);
   // ---- P3c: keep the raw k-k products for the backward (dbeta), then Akk = beta_t * raw;
   // ---- P5a: elementwise tiles straight to global in their swizzled images: QG, KG, AQK, GL ------------
   {
@@ -342,6 +348,7 @@ __global__ void __launch_bounds__(256, 2) kda_chunk_prepare_kernel(const PrepPar
     if (tid < KD) reinterpret_cast<float*>(p.GL + tile * TILE_GL)[tid] = ex2(s.G[(C - 1) * GS + tid]);
   }
   __syncthreads();   // every read of s.q is done: its buffer becomes the scratch X, later k * Gam
+  KDA_DBG_CLOCK(p.dbg, 21);
 
   // ---- P4: Tm = (I + Akk)^-1, fp32.  16x16 diagonal blocks by forward substitution (one column per
   // thread, in registers), then two levels of block merges  T21 = -T22 A21 T11.
@@ -444,6 +451,7 @@ __global__ void __launch_bounds__(256, 2) kda_chunk_prepare_kernel(const PrepPar
     }
   }
 
+  KDA_DBG_CLOCK(p.dbg, 22);
   // ---- P5b: Tm (bf16) to global for the backward; kGam = k * exp2(G) (bf16) into the q buffer ----------
   if (p.TI) {
     unsigned char* gT = p.TI + tile * TILE_TT;
@@ -466,6 +474,7 @@ __global__ void __launch_bounds__(256, 2) kda_chunk_prepare_kernel(const PrepPar
                    pack_bf16(k2.x * ex2(Gb.x), k2.y * ex2(Gb.y)), pack_bf16(k3.x * ex2(Gb.z), k3.y * ex2(Gb.w)));
   }
   __syncthreads();   // G is dead from here on: its buffer stages the UT and W tiles
+  KDA_DBG_CLOCK(p.dbg, 23);
 
   // ---- P5c: u = (Tm beta) v,  w = (Tm beta) kGam on tensor cores.  Warp = (row tile mt, column half nh).
   // The accumulators are written into swizzled tile images in shared memory and leave with two TMA bulk stores.
@@ -529,6 +538,7 @@ __global__ void __launch_bounds__(256, 2) kda_chunk_prepare_kernel(const PrepPar
       bulk_commit();
       bulk_wait_read<0>();   // shared memory must stay valid until the engine has read it
     }
+    KDA_DBG_CLOCK(p.dbg, 24);
   }
 }
 
@@ -862,7 +872,7 @@ extern "C" int kda_chunk_fwd(const kda_chunk_args* args, void* stream) {
   pp.g = a.g; pp.beta = a.beta; pp.cu = a.cu_seqlens;
   pp.seq_chunk_off = w.seq_chunk_off; pp.chunk_seq = w.chunk_seq;
   pp.W = w.W; pp.UT = w.UT; pp.KG = w.KG; pp.QG = w.QG; pp.AQK = w.AQK; pp.GL = w.GL; pp.TI = save ? w.TI : nullptr; pp.RKK = save ? w.RKK : nullptr;
-  pp.N = a.N; pp.H = a.H; pp.use_l2norm = a.use_qk_l2norm; pp.scale = a.scale;
+  pp.dbg = g_dbg_clocks; pp.N = a.N; pp.H = a.H; pp.use_l2norm = a.use_qk_l2norm; pp.scale = a.scale;
   kda_chunk_prepare_kernel<<<dim3(NTmax, a.H), 256, sizeof(PrepSmem), st>>>(pp);
   if ((e = cudaGetLastError()) != cudaSuccess) return static_cast<int>(e);
   prof_mark(prof, KDA_STAGE_PREPARE, st);
