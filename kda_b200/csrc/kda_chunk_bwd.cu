@@ -321,34 +321,55 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_kernel(const MainPa
   extern __shared__ __align__(128) unsigned char smem_raw[];
   MainSmem& s = *reinterpret_cast<MainSmem*>(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gid = lane >> 2, tig = lane & 3;
-  const int c = blockIdx.x, h = blockIdx.y;
-  if (c >= p.seq_chunk_off[p.N]) return;
-  const ChunkInfo ci = chunk_info(p.seq_chunk_off, p.chunk_seq, p.cu, c);
-  const int len = ci.len;
-  const size_t tile = static_cast<size_t>(c) * p.H + h;
-  KDA_DBG_CLOCK(p.dbg, 0);
-
-  // ---- loads in two groups: what phase A needs first (state tiles, dO), the rest lands behind phase A ----
+  // Persistent CTAs: tile = (chunk, head), walked with stride gridDim.x.  The state tiles and dO of the NEXT
+  // tile are fetched while this tile's last phase runs, so only the first tile waits for its loads.
+  const long long total_tiles = static_cast<long long>(p.seq_chunk_off[p.N]) * p.H;
   if (tid == 0) {
     mbar_init(&s.bar, 1);
     mbar_init(&s.bar2, 1);
     fence_mbar_init();
+  }
+  __syncthreads();
+  auto fetch_state = [&](long long idx) {      // thread 0: HS, DH, v_new^T, dv_new^T of tile idx
+    const size_t tl = static_cast<size_t>(idx);
     mbar_expect_tx(&s.bar, 2 * TILE_VK + 2 * TILE_VT);
-    bulk_g2s(s.HS, p.HS + tile * TILE_VK, TILE_VK, &s.bar);
-    bulk_g2s(s.DH, p.DH + tile * TILE_VK, TILE_VK, &s.bar);
-    bulk_g2s(s.VN, p.VNEWT + tile * TILE_VT, TILE_VT, &s.bar);
-    bulk_g2s(s.DVN, p.DVNEWT + tile * TILE_VT, TILE_VT, &s.bar);
+    bulk_g2s(s.HS, p.HS + tl * TILE_VK, TILE_VK, &s.bar);
+    bulk_g2s(s.DH, p.DH + tl * TILE_VK, TILE_VK, &s.bar);
+    bulk_g2s(s.VN, p.VNEWT + tl * TILE_VT, TILE_VT, &s.bar);
+    bulk_g2s(s.DVN, p.DVNEWT + tl * TILE_VT, TILE_VT, &s.bar);
+  };
+  auto fetch_do = [&](long long idx) {          // all threads: dO rows of tile idx (one cp.async group)
+    const int cc = static_cast<int>(idx / p.H), hh = static_cast<int>(idx % p.H);
+    const ChunkInfo cn = chunk_info(p.seq_chunk_off, p.chunk_seq, p.cu, cc);
+    for (int i = tid; i < C * 16; i += 256) {
+      const int r = i >> 4, pc = i & 15;
+      const bool ok = r < cn.len;
+      const size_t row = (static_cast<size_t>(cn.tok0 + (ok ? r : 0)) * p.H + hh) * KD + pc * 8;
+      cp_async16(&s.dO[r * QS + pc * 8], p.d_o + row, ok);
+    }
+    cp_async_commit();
+  };
+  if (static_cast<long long>(blockIdx.x) < total_tiles) {
+    if (tid == 0) fetch_state(blockIdx.x);
+    fetch_do(blockIdx.x);
+  }
+
+  int it = 0;
+  for (long long idx = blockIdx.x; idx < total_tiles; idx += gridDim.x, ++it) {
+  const int c = static_cast<int>(idx / p.H), h = static_cast<int>(idx % p.H);
+  const ChunkInfo ci = chunk_info(p.seq_chunk_off, p.chunk_seq, p.cu, c);
+  const int len = ci.len;
+  const size_t tile = static_cast<size_t>(idx);
+  const long long next_idx = idx + gridDim.x;
+  long long* const dbg = (it == 2) ? p.dbg : nullptr;   // development aid: clocks of a steady-state tile
+  KDA_DBG_CLOCK(dbg, 0);
+
+  // ---- second load group (q, k, v, g, Tm, raw kk): lands behind phase A ------------------------------
+  if (tid == 0) {
     mbar_expect_tx(&s.bar2, 2 * TILE_TT);
     bulk_g2s(s.TI, p.TI + tile * TILE_TT, TILE_TT, &s.bar2);
     bulk_g2s(s.RKK, p.RKK + tile * TILE_TT, TILE_TT, &s.bar2);
   }
-  for (int i = tid; i < C * 16; i += 256) {
-    const int r = i >> 4, pc = i & 15;
-    const bool ok = r < len;
-    const size_t row = (static_cast<size_t>(ci.tok0 + (ok ? r : 0)) * p.H + h) * KD + pc * 8;
-    cp_async16(&s.dO[r * QS + pc * 8], p.d_o + row, ok);
-  }
-  cp_async_commit();
   for (int i = tid; i < C * 16; i += 256) {
     const int r = i >> 4, pc = i & 15;
     const bool ok = r < len;
@@ -365,12 +386,12 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_kernel(const MainPa
   }
   cp_async_commit();
   if (tid < C) s.beta[tid] = (tid < len) ? __ldg(p.beta + static_cast<size_t>(ci.tok0 + tid) * p.H + h) : 0.f;
-  cp_async_wait<1>();   // dO has landed (this thread's pieces)
-  __syncthreads();      // everyone's dO pieces; also publishes the mbarrier inits
-  const bool tiles_ok = mbar_wait(&s.bar, 0);
+  cp_async_wait<1>();   // this tile's dO (issued one tile ago, or in the prologue) has landed
+  __syncthreads();
+  const bool tiles_ok = mbar_wait(&s.bar, it & 1);
   if (!tiles_ok && tid == 0) atomicOr(p.status, 16u);
 
-  KDA_DBG_CLOCK(p.dbg, 1);
+  KDA_DBG_CLOCK(dbg, 1);
   const int n0 = warp * 16;                                    // this warp's 16 output columns (kk or v)
   const int j0 = warp * 8;                                     // this warp's 8 columns of the 64x64 products
   const int trow = (lane & 7) + (((lane >> 3) & 1) << 3), tcol = (lane >> 4) << 3;   // B stored [k][n]
@@ -438,7 +459,7 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_kernel(const MainPa
   }
   cp_async_wait<0>();
   __syncthreads();   // (1) HS, DH, VN, dO are dead from here on; q, k, v, g have landed
-  KDA_DBG_CLOCK(p.dbg, 2);
+  KDA_DBG_CLOCK(dbg, 2);
   {  // G = cumsum(g) * log2(e): two half-columns per column, then the carry
     const int col = tid & 127, half = tid >> 7;
     float gv[32];
@@ -460,7 +481,7 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_kernel(const MainPa
 #pragma unroll
       for (int i = 0; i < 32; ++i) s.G[(32 + i) * GS + col] = carry + gv[i] * LOG2E;
     }
-    if (!mbar_wait(&s.bar2, 0) && tid == 0) atomicOr(p.status, 16u);
+    if (!mbar_wait(&s.bar2, it & 1) && tid == 0) atomicOr(p.status, 16u);
     __syncthreads();
   }
 
@@ -521,8 +542,8 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_kernel(const MainPa
         const float x1 = (col + 1 <= row) ? dAq[mt][2 * hh + 1] : 0.f;
         *reinterpret_cast<uint32_t*>(&sDAQ[row * TS + col]) = pack_bf16(x0, x1);
         if ((warp >> 1) == mt) {
-          s.Ad[mt][gid + hh * 8][col & 15].x = x0;
-          s.Ad[mt][gid + hh * 8][(col & 15) + 1].x = x1;
+          s.Ad[mt][gid + hh * 8][col & 15].x = p.scale * x0;      // scale folded in for phase D
+          s.Ad[mt][gid + hh * 8][(col & 15) + 1].x = p.scale * x1;
         }
       }
     }
@@ -539,7 +560,7 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_kernel(const MainPa
     }
   }
   __syncthreads();   // (2)
-  KDA_DBG_CLOCK(p.dbg, 3);
+  KDA_DBG_CLOCK(dbg, 3);
 
   // =========================== phase B: through Tm = (I + Akk)^-1 =====================================
   float pb[4][2];    // dbeta partial row sums: rows mt*16 + gid (+8)
@@ -579,7 +600,7 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_kernel(const MainPa
     }
   }
   __syncthreads();   // (3)
-  KDA_DBG_CLOCK(p.dbg, 4);
+  KDA_DBG_CLOCK(dbg, 4);
   {
     // X = dTm Tm^T
     float acc[4][4];
@@ -608,7 +629,7 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_kernel(const MainPa
     }
   }
   __syncthreads();   // (4)
-  KDA_DBG_CLOCK(p.dbg, 5);
+  KDA_DBG_CLOCK(dbg, 5);
   // Tm^T as A fragments: A[m=i][k=m'] = Tm[m'][i]
   uint32_t tA[4][4][4];
 #pragma unroll
@@ -719,7 +740,7 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_kernel(const MainPa
     }
   }
   __syncthreads();   // (5) dAq / dAk (bf16) complete
-  KDA_DBG_CLOCK(p.dbg, 6);
+  KDA_DBG_CLOCK(dbg, 6);
 
   // =========================== phase C: off-diagonal 16x16 blocks of the intra-chunk terms ============
   // decay factored around the first row r0 = 16 I of row block I (both factors <= 1), as in the forward
@@ -814,7 +835,7 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_kernel(const MainPa
     }
   }
 
-  KDA_DBG_CLOCK(p.dbg, 7);
+  KDA_DBG_CLOCK(dbg, 7);
   __syncthreads();   // (6) every shared-memory operand of phase C has been read: the regions become staging
   // ---- stage the fp32 partial dq / dk+ / dk- as [64][FS] matrices; dbeta partial row sums --------------
   float* stq = reinterpret_cast<float*>(s.dO);
@@ -846,7 +867,7 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_kernel(const MainPa
     }
   }
   __syncthreads();   // (7)
-  KDA_DBG_CLOCK(p.dbg, 8);
+  KDA_DBG_CLOCK(dbg, 8);
   if (tid < len) {
     float x = 0.f;
 #pragma unroll
@@ -855,48 +876,65 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_kernel(const MainPa
   }
 
   // =========================== phase D: diagonal 16x16 blocks pairwise + epilogue =======================
-  // One thread per key column and half chunk (two 16-row blocks): exp2(G_t - G_j) pairwise (range-safe),
+  // One thread per key column and half chunk (two 16-row blocks).  The decay between rows of a block is the
+  // running product of the per-row factors lam_s = exp2(G_s - G_{s-1}) <= 1 (range-safe, no exp per pair).
   // dG = q dq + k (dk+ - dk-), dg = reverse cumsum over the chunk, final dq / dk / dg.
   {
     const int kk = tid & 127, half = tid >> 7;
+    float cq[32], cp[32], cn[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const int t = half * 32 + i;
+      cq[i] = stq[t * FS + kk];
+      cp[i] = stp[t * FS + kk];
+      cn[i] = stn[t * FS + kk];
+    }
+    fence_proxy_async();
+    __syncthreads();   // (8) the staging regions are free again: fetch the next tile's phase-A operands
+    if (next_idx < total_tiles) {
+      if (tid == 0) fetch_state(next_idx);
+      fetch_do(next_idx);
+    }
+    KDA_DBG_CLOCK(dbg, 10);
     float dGv[32];
 #pragma unroll
     for (int bb = 0; bb < 2; ++bb) {
       const int b = half * 2 + bb;
-      float Gc[16], qv[16], kv[16], dq[16], dkp2[16], dkn2[16];
+      float lam[16], qv[16], kv[16];
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
         const int t = b * 16 + i;
-        Gc[i] = s.G[t * GS + kk];
+        const float Gt = s.G[t * GS + kk];
+        const float Gp = (i > 0) ? s.G[(t - 1) * GS + kk] : Gt;
+        lam[i] = ex2(Gt - Gp);
         qv[i] = __bfloat162float(s.q[t * QS + kk]);
         kv[i] = __bfloat162float(s.k[t * QS + kk]);
-        dq[i] = stq[t * FS + kk];
-        dkp2[i] = stp[t * FS + kk];
-        dkn2[i] = stn[t * FS + kk];
       }
 #pragma unroll
       for (int t = 0; t < 16; ++t) {
+        float D = 1.f;
 #pragma unroll
-        for (int j = 0; j <= t; ++j) {
+        for (int j = t; j >= 0; --j) {
           const float2 a = s.Ad[b][t][j];
-          const float D = ex2(Gc[t] - Gc[j]);
-          const float sa = p.scale * a.x;
+          const float sa = a.x;
           const float kd = kv[j] * D;
-          dq[t] = fmaf(sa, kd, dq[t]);
-          dkp2[t] = fmaf(a.y, kd, dkp2[t]);
-          dkn2[j] = fmaf(D, sa * qv[t] + a.y * kv[t], dkn2[j]);
+          cq[bb * 16 + t] = fmaf(sa, kd, cq[bb * 16 + t]);
+          cp[bb * 16 + t] = fmaf(a.y, kd, cp[bb * 16 + t]);
+          cn[bb * 16 + j] = fmaf(D, sa * qv[t] + a.y * kv[t], cn[bb * 16 + j]);
+          D *= lam[j];      // decay from row j-1 to row t
         }
       }
+      KDA_DBG_CLOCK(dbg, 11 + 2 * bb);
+      // dq, dk replace this thread's own q, k elements in shared memory (nobody else reads them any more)
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
         const int t = b * 16 + i;
-        dGv[bb * 16 + i] = qv[i] * dq[i] + kv[i] * (dkp2[i] - dkn2[i]);
-        if (t < len) {
-          const size_t gi = (static_cast<size_t>(ci.tok0 + t) * p.H + h) * KD + kk;
-          p.dq[gi] = __float2bfloat16_rn(dq[i]);
-          p.dk[gi] = __float2bfloat16_rn(dkp2[i] + dkn2[i]);
-        }
+        const int r = bb * 16 + i;
+        dGv[r] = qv[i] * cq[r] + kv[i] * (cp[r] - cn[r]);
+        s.q[t * QS + kk] = __float2bfloat16_rn(cq[r]);
+        s.k[t * QS + kk] = __float2bfloat16_rn(cp[r] + cn[r]);
       }
+      KDA_DBG_CLOCK(dbg, 12 + 2 * bb);
     }
     if (half == 1) dGv[31] += s.dgl[kk];
     {
@@ -912,13 +950,29 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_kernel(const MainPa
     {
       const float add = half ? 0.f : s.carry[kk];
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const int t = half * 32 + i;
-        if (t < len) p.dg[(static_cast<size_t>(ci.tok0 + t) * p.H + h) * KD + kk] = dGv[i] + add;
+      for (int i = 0; i < 32; ++i) s.G[(half * 32 + i) * GS + kk] = dGv[i] + add;   // dg replaces G
+    }
+    __syncthreads();
+    // coalesced 16-byte stores of dq, dk (bf16) and dg (fp32) rows
+    for (int i = tid; i < C * 16; i += 256) {
+      const int r = i >> 4, pc = i & 15;
+      if (r < len) {
+        const size_t row = (static_cast<size_t>(ci.tok0 + r) * p.H + h) * KD + pc * 8;
+        *reinterpret_cast<uint4*>(p.dq + row) = *reinterpret_cast<const uint4*>(&s.q[r * QS + pc * 8]);
+        *reinterpret_cast<uint4*>(p.dk + row) = *reinterpret_cast<const uint4*>(&s.k[r * QS + pc * 8]);
+      }
+    }
+    for (int i = tid; i < C * 32; i += 256) {
+      const int r = i >> 5, pc = i & 31;
+      if (r < len) {
+        const size_t row = (static_cast<size_t>(ci.tok0 + r) * p.H + h) * KD + pc * 4;
+        *reinterpret_cast<float4*>(p.dg + row) = *reinterpret_cast<const float4*>(&s.G[r * GS + pc * 4]);
       }
     }
   }
-  KDA_DBG_CLOCK(p.dbg, 9);
+  KDA_DBG_CLOCK(dbg, 9);
+  __syncthreads();   // (9) q, k, G, beta, Ad, dgl, carry may be overwritten by the next tile
+  }  // tile loop
 }
 
 // =================================================================================================
@@ -967,6 +1021,14 @@ __global__ void __launch_bounds__(256) kda_l2norm_bwd_kernel(const __nv_bfloat16
     dr.y = pack_bf16(rs * (d1.x - y1.x * dot), rs * (d1.y - y1.y * dot));
     *reinterpret_cast<uint2*>(d + r * KD + lane * 4) = dr;
   }
+}
+
+// one persistent CTA per SM (the kernel needs a whole SM's shared memory), never more CTAs than tiles
+static int main_grid(int max_chunks, int H) {
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const long long tiles = static_cast<long long>(max_chunks) * H;
+  return static_cast<int>(tiles < sms ? (tiles > 0 ? tiles : 1) : sms);
 }
 
 static std::once_flag g_battr_once;
@@ -1042,7 +1104,7 @@ extern "C" int kda_chunk_bwd(const kda_chunk_args* args, void* stream) {
   mp.dv = static_cast<__nv_bfloat16*>(a.dv); mp.dq = static_cast<__nv_bfloat16*>(a.dq); mp.dk = static_cast<__nv_bfloat16*>(a.dk);
   mp.dbeta = a.dbeta; mp.dg = a.dg; mp.status = w.status; mp.dbg = g_dbg_clocks;
   mp.N = a.N; mp.H = a.H; mp.scale = a.scale;
-  kda_chunk_bwd_main_kernel<<<dim3(NTmax, a.H), 256, sizeof(MainSmem), st>>>(mp);
+  kda_chunk_bwd_main_kernel<<<main_grid(NTmax, a.H), 256, sizeof(MainSmem), st>>>(mp);
   if ((e = cudaGetLastError()) != cudaSuccess) return static_cast<int>(e);
   prof_mark(prof, KDA_STAGE_BWD_MAIN, st);
 

@@ -58,15 +58,14 @@ constexpr int TS = 72;    // bf16 elements per padded row of the bf16 64x64 matr
 
 // 113,920 bytes: two CTAs per SM.
 struct PrepSmem {
-  __nv_bfloat16 q[C * QS];   // q; then the scratch X of the block-merge products; then k * Gam
+  __nv_bfloat16 q[C * QS];   // q; from P5a on k * Gam
   __nv_bfloat16 k[C * QS];
   __nv_bfloat16 v[C * QS];
   float G[C * GS];           // log2-domain inclusive cumsum of g; at the very end the staged UT and W tiles
   float Akk[C * AS];         // raw <k_t D, k_j>, then beta_t * raw, then Tm = (I + Akk)^-1
-  __nv_bfloat16 Aqk[C * TS]; // scale <q_t D, k_j>, lower triangle incl. diagonal
+  __nv_bfloat16 Aqk[C * TS]; // scale <q_t D, k_j>, lower triangle incl. diagonal; after P5a the scratch X of P4
   float beta[C];
 };
-static_assert(32 * 33 * 4 <= C * QS * 2, "X must fit the q buffer");
 static_assert(TILE_VT + TILE_TK <= C * GS * 4, "staged tiles must fit the G buffer");
 
 struct PrepParams {
@@ -254,11 +253,15 @@ __global__ void __launch_bounds__(256, 2) kda_chunk_prepare_kernel(const PrepPar
   KDA_DBG_CLOCK(p.dbg, 19);
   // ---- P3b: off-diagonal 16x16 blocks on tensor cores.  For row block I the decay is factored around
   // the block's first row r0 = 16 I:  exp2(G_t - G_r0) * exp2(G_r0 - G_j), both factors <= 1 for j < r0 <= t.
-  for (int u = warp; u < 12; u += 8) {
-    const int I = (u < 2) ? 1 : (u < 6 ? 2 : 3);
-    const int nt = (u < 2) ? u : (u < 6 ? u - 2 : u - 6);
-    const int r0 = 16 * I, ta = r0 + gid, tb = ta + 8, j = nt * 8 + gid;
-    float cq[4] = {0.f, 0.f, 0.f, 0.f}, ck[4] = {0.f, 0.f, 0.f, 0.f};
+  // Six units (I, 16 columns j): I=1 -> 1, I=2 -> 2, I=3 -> 3; warps 0..5 take one each.
+  if (warp < 6) {
+    const int I = (warp < 1) ? 1 : (warp < 3 ? 2 : 3);
+    const int np = (warp < 1) ? 0 : (warp < 3 ? warp - 1 : warp - 3);
+    const int r0 = 16 * I, ta = r0 + gid, tb = ta + 8;
+    const int ja = np * 16 + gid, jb = ja + 8;
+    float cq[2][4], ck[2][4];
+#pragma unroll
+    for (int n = 0; n < 2; ++n) cq[n][0] = cq[n][1] = cq[n][2] = cq[n][3] = ck[n][0] = ck[n][1] = ck[n][2] = ck[n][3] = 0.f;
 #pragma unroll 2
     for (int ks = 0; ks < 8; ++ks) {
       const int k0 = ks * 16 + tig * 2, k1 = k0 + 8;
@@ -268,8 +271,6 @@ __global__ void __launch_bounds__(256, 2) kda_chunk_prepare_kernel(const PrepPar
       const float2 Ga1 = *reinterpret_cast<const float2*>(&s.G[ta * GS + k1]);
       const float2 Gb0 = *reinterpret_cast<const float2*>(&s.G[tb * GS + k0]);
       const float2 Gb1 = *reinterpret_cast<const float2*>(&s.G[tb * GS + k1]);
-      const float2 Gj0 = *reinterpret_cast<const float2*>(&s.G[j * GS + k0]);
-      const float2 Gj1 = *reinterpret_cast<const float2*>(&s.G[j * GS + k1]);
       const float ea0x = ex2(Ga0.x - R0.x), ea0y = ex2(Ga0.y - R0.y), ea1x = ex2(Ga1.x - R1.x), ea1y = ex2(Ga1.y - R1.y);
       const float eb0x = ex2(Gb0.x - R0.x), eb0y = ex2(Gb0.y - R0.y), eb1x = ex2(Gb1.x - R1.x), eb1y = ex2(Gb1.y - R1.y);
       const float2 qa0 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.q[ta * QS + k0]));
@@ -280,23 +281,32 @@ __global__ void __launch_bounds__(256, 2) kda_chunk_prepare_kernel(const PrepPar
       const float2 ka1 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.k[ta * QS + k1]));
       const float2 kb0 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.k[tb * QS + k0]));
       const float2 kb1 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.k[tb * QS + k1]));
-      const float2 kj0 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.k[j * QS + k0]));
-      const float2 kj1 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.k[j * QS + k1]));
       uint32_t aq[4], ak[4];
       aq[0] = pack_bf16(qa0.x * ea0x, qa0.y * ea0y); aq[1] = pack_bf16(qb0.x * eb0x, qb0.y * eb0y);
       aq[2] = pack_bf16(qa1.x * ea1x, qa1.y * ea1y); aq[3] = pack_bf16(qb1.x * eb1x, qb1.y * eb1y);
       ak[0] = pack_bf16(ka0.x * ea0x, ka0.y * ea0y); ak[1] = pack_bf16(kb0.x * eb0x, kb0.y * eb0y);
       ak[2] = pack_bf16(ka1.x * ea1x, ka1.y * ea1y); ak[3] = pack_bf16(kb1.x * eb1x, kb1.y * eb1y);
-      const uint32_t b0 = pack_bf16(kj0.x * ex2(R0.x - Gj0.x), kj0.y * ex2(R0.y - Gj0.y));
-      const uint32_t b1 = pack_bf16(kj1.x * ex2(R1.x - Gj1.x), kj1.y * ex2(R1.y - Gj1.y));
-      mma16816(cq, aq, b0, b1);
-      mma16816(ck, ak, b0, b1);
+#pragma unroll
+      for (int n = 0; n < 2; ++n) {
+        const int j = n ? jb : ja;
+        const float2 Gj0 = *reinterpret_cast<const float2*>(&s.G[j * GS + k0]);
+        const float2 Gj1 = *reinterpret_cast<const float2*>(&s.G[j * GS + k1]);
+        const float2 kj0 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.k[j * QS + k0]));
+        const float2 kj1 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.k[j * QS + k1]));
+        const uint32_t b0 = pack_bf16(kj0.x * ex2(R0.x - Gj0.x), kj0.y * ex2(R0.y - Gj0.y));
+        const uint32_t b1 = pack_bf16(kj1.x * ex2(R1.x - Gj1.x), kj1.y * ex2(R1.y - Gj1.y));
+        mma16816(cq[n], aq, b0, b1);
+        mma16816(ck[n], ak, b0, b1);
+      }
     }
-    const int col = nt * 8 + tig * 2;
-    *reinterpret_cast<uint32_t*>(&s.Aqk[ta * TS + col]) = pack_bf16(p.scale * cq[0], p.scale * cq[1]);
-    *reinterpret_cast<uint32_t*>(&s.Aqk[tb * TS + col]) = pack_bf16(p.scale * cq[2], p.scale * cq[3]);
-    *reinterpret_cast<float2*>(&s.Akk[ta * AS + col]) = make_float2(ck[0], ck[1]);
-    *reinterpret_cast<float2*>(&s.Akk[tb * AS + col]) = make_float2(ck[2], ck[3]);
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {
+      const int col = np * 16 + n * 8 + tig * 2;
+      *reinterpret_cast<uint32_t*>(&s.Aqk[ta * TS + col]) = pack_bf16(p.scale * cq[n][0], p.scale * cq[n][1]);
+      *reinterpret_cast<uint32_t*>(&s.Aqk[tb * TS + col]) = pack_bf16(p.scale * cq[n][2], p.scale * cq[n][3]);
+      *reinterpret_cast<float2*>(&s.Akk[ta * AS + col]) = make_float2(ck[n][0], ck[n][1]);
+      *reinterpret_cast<float2*>(&s.Akk[tb * AS + col]) = make_float2(ck[n][2], ck[n][3]);
+    }
   }
   __syncthreads();
 
@@ -320,6 +330,7 @@ __global__ void __launch_bounds__(256, 2) kda_chunk_prepare_kernel(const PrepPar
       *reinterpret_cast<float4*>(&s.Akk[r * AS + pc * 8 + 4]) = a1;
       *reinterpret_cast<uint4*>(gA + off) = *reinterpret_cast<const uint4*>(&s.Aqk[r * TS + pc * 8]);
     }
+    KDA_DBG_CLOCK(p.dbg, 25);
     unsigned char* gQG = p.QG + tile * TILE_TK;
     unsigned char* gKG = p.KG + tile * TILE_TK;
     for (int i = tid; i < C * 16; i += 256) {
@@ -333,27 +344,34 @@ __global__ void __launch_bounds__(256, 2) kda_chunk_prepare_kernel(const PrepPar
       const float g8[8] = {Ga.x, Ga.y, Ga.z, Ga.w, Gb.x, Gb.y, Gb.z, Gb.w};
       const float l8[8] = {La.x, La.y, La.z, La.w, Lb.x, Lb.y, Lb.z, Lb.w};
       const uint32_t qw[4] = {qr.x, qr.y, qr.z, qr.w}, kw[4] = {kr.x, kr.y, kr.z, kr.w};
-      uint32_t oq[4], ok[4];
+      uint32_t oq[4], ok[4], og[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const float2 qq = unpack_bf16(qw[e]), kk = unpack_bf16(kw[e]);
         const float e0 = ex2(g8[2 * e]), e1 = ex2(g8[2 * e + 1]);
         oq[e] = pack_bf16(p.scale * qq.x * e0, p.scale * qq.y * e1);
         ok[e] = pack_bf16(kk.x * ex2(l8[2 * e] - g8[2 * e]), kk.y * ex2(l8[2 * e + 1] - g8[2 * e + 1]));
+        og[e] = pack_bf16(kk.x * e0, kk.y * e1);
       }
       const uint32_t off = swz<256>(r, pc * 8);
       *reinterpret_cast<uint4*>(gQG + off) = make_uint4(oq[0], oq[1], oq[2], oq[3]);
       *reinterpret_cast<uint4*>(gKG + off) = make_uint4(ok[0], ok[1], ok[2], ok[3]);
+      // k * Gam takes the place of this thread's own q piece (no other thread reads it in this phase)
+      *reinterpret_cast<uint4*>(&s.q[r * QS + pc * 8]) = make_uint4(og[0], og[1], og[2], og[3]);
     }
+    KDA_DBG_CLOCK(p.dbg, 26);
     if (tid < KD) reinterpret_cast<float*>(p.GL + tile * TILE_GL)[tid] = ex2(s.G[(C - 1) * GS + tid]);
   }
-  __syncthreads();   // every read of s.q is done: its buffer becomes the scratch X, later k * Gam
+  __syncthreads();   // s.q now holds k * Gam; s.Aqk has been copied out and becomes the scratch X
   KDA_DBG_CLOCK(p.dbg, 21);
 
-  // ---- P4: Tm = (I + Akk)^-1, fp32.  16x16 diagonal blocks by forward substitution (one column per
-  // thread, in registers), then two levels of block merges  T21 = -T22 A21 T11.
+  // ---- P4: Tm = (I + Akk)^-1.  16x16 diagonal blocks by fp32 forward substitution (one column per thread,
+  // in registers); the two levels of block merges  T21 = -T22 A21 T11  run on tensor cores with every fp32
+  // operand split into bf16 hi + lo (three MMAs per product: about 16 bits of mantissa, better than TF32).
   {
-    float* sX = reinterpret_cast<float*>(s.q);
+    constexpr int XS = 36;                                   // floats per row of the scratch X
+    float* sX = reinterpret_cast<float*>(s.Aqk);
+    static_assert(32 * XS * 4 <= C * TS * 2, "X must fit the Aqk buffer");
     float x[16];
     if (tid < 64) {
       const int b = tid >> 4, cc = tid & 15;
@@ -374,85 +392,71 @@ __global__ void __launch_bounds__(256, 2) kda_chunk_prepare_kernel(const PrepPar
       for (int i = 0; i < 16; ++i) A[i * AS + cc] = x[i];
     }
     __syncthreads();
-    // level 1: pairs (rows 16..31 | cols 0..15) and (rows 48..63 | cols 32..47)
+    KDA_DBG_CLOCK(p.dbg, 27);
+    // c += A[ar.., ac..](16x16, stride AS, from Akk) * B[br.., bc..](16x8, row stride bs)
+    auto mma_split = [&](float (&c)[4], int ar, int ac, const float* Bm, int bs, int br, int bc) {
+      uint32_t ah[4], al[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 v2 = *reinterpret_cast<const float2*>(&s.Akk[(ar + gid + (e & 1) * 8) * AS + ac + tig * 2 + (e >> 1) * 8]);
+        ah[e] = pack_bf16(v2.x, v2.y);
+        const float2 hi = unpack_bf16(ah[e]);
+        al[e] = pack_bf16(v2.x - hi.x, v2.y - hi.y);
+      }
+      uint32_t bh[2], bl[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const float y0 = Bm[(br + tig * 2 + e * 8) * bs + bc + gid];
+        const float y1 = Bm[(br + tig * 2 + 1 + e * 8) * bs + bc + gid];
+        bh[e] = pack_bf16(y0, y1);
+        const float2 hi = unpack_bf16(bh[e]);
+        bl[e] = pack_bf16(y0 - hi.x, y1 - hi.y);
+      }
+      mma16816(c, ah, bh[0], bh[1]);
+      mma16816(c, ah, bl[0], bl[1]);
+      mma16816(c, al, bh[0], bh[1]);
+    };
+    // level 1: pairs (rows 16..31 | cols 0..15) and (rows 48..63 | cols 32..47); warps 0..3: (pair, 8 columns)
     {
-      const int pr = tid >> 7, e = tid & 127;            // 2 pairs x 128 threads, 2 outputs each
-      const int base = 32 * pr;
-      float* A21 = &s.Akk[(base + 16) * AS + base];
-      const float* T11 = &s.Akk[base * AS + base];
-      const float* T22 = &s.Akk[(base + 16) * AS + base + 16];
-      float* X = &sX[pr * 16 * 17];
-      float r[2];
-#pragma unroll
-      for (int o = 0; o < 2; ++o) {
-        const int idx = e * 2 + o, i = idx >> 4, jj = idx & 15;
-        float acc = 0.f;
-#pragma unroll
-        for (int m = 0; m < 16; ++m) acc += A21[i * AS + m] * T11[m * AS + jj];
-        r[o] = acc;
-      }
-#pragma unroll
-      for (int o = 0; o < 2; ++o) {
-        const int idx = e * 2 + o;
-        X[(idx >> 4) * 17 + (idx & 15)] = r[o];
+      const int pr = (warp >> 1) & 1, nt = warp & 1, base = 32 * pr;
+      float c1[4] = {0.f, 0.f, 0.f, 0.f};
+      if (warp < 4) {
+        mma_split(c1, base + 16, base, s.Akk, AS, base, base + nt * 8);                 // X = A21 T11
+        float* X = sX + pr * 16 * XS;
+        *reinterpret_cast<float2*>(&X[gid * XS + nt * 8 + tig * 2]) = make_float2(c1[0], c1[1]);
+        *reinterpret_cast<float2*>(&X[(gid + 8) * XS + nt * 8 + tig * 2]) = make_float2(c1[2], c1[3]);
       }
       __syncthreads();
-#pragma unroll
-      for (int o = 0; o < 2; ++o) {
-        const int idx = e * 2 + o, i = idx >> 4, jj = idx & 15;
-        float acc = 0.f;
-#pragma unroll
-        for (int m = 0; m < 16; ++m) acc += T22[i * AS + m] * X[m * 17 + jj];
-        r[o] = -acc;
-      }
-      __syncthreads();
-#pragma unroll
-      for (int o = 0; o < 2; ++o) {
-        const int idx = e * 2 + o;
-        A21[(idx >> 4) * AS + (idx & 15)] = r[o];
+      if (warp < 4) {
+        float c2[4] = {0.f, 0.f, 0.f, 0.f};
+        mma_split(c2, base + 16, base + 16, sX + pr * 16 * XS, XS, 0, nt * 8);          // T22 X
+        float* A21 = &s.Akk[(base + 16) * AS + base + nt * 8 + tig * 2];
+        *reinterpret_cast<float2*>(&A21[gid * AS]) = make_float2(-c2[0], -c2[1]);
+        *reinterpret_cast<float2*>(&A21[(gid + 8) * AS]) = make_float2(-c2[2], -c2[3]);
       }
       __syncthreads();
     }
-    // level 2: rows 32..63 | cols 0..31
+    // level 2: rows 32..63 | cols 0..31; warp = (16-row tile mt, 8-column tile nt)
     {
-      float* A21 = &s.Akk[32 * AS];
-      const float* T11 = &s.Akk[0];
-      const float* T22 = &s.Akk[32 * AS + 32];
-      float r[4];
-#pragma unroll
-      for (int o = 0; o < 4; ++o) {
-        const int idx = tid * 4 + o, i = idx >> 5, jj = idx & 31;
-        float acc = 0.f;
-#pragma unroll 8
-        for (int m = 0; m < 32; ++m) acc += A21[i * AS + m] * T11[m * AS + jj];
-        r[o] = acc;
-      }
-#pragma unroll
-      for (int o = 0; o < 4; ++o) {
-        const int idx = tid * 4 + o;
-        sX[(idx >> 5) * 33 + (idx & 31)] = r[o];
-      }
+      const int mt = warp >> 2, nt = warp & 3;
+      float c1[4] = {0.f, 0.f, 0.f, 0.f};
+      mma_split(c1, 32 + 16 * mt, 0, s.Akk, AS, 0, nt * 8);                             // X = A21 T11
+      mma_split(c1, 32 + 16 * mt, 16, s.Akk, AS, 16, nt * 8);
+      *reinterpret_cast<float2*>(&sX[(16 * mt + gid) * XS + nt * 8 + tig * 2]) = make_float2(c1[0], c1[1]);
+      *reinterpret_cast<float2*>(&sX[(16 * mt + gid + 8) * XS + nt * 8 + tig * 2]) = make_float2(c1[2], c1[3]);
       __syncthreads();
-#pragma unroll
-      for (int o = 0; o < 4; ++o) {
-        const int idx = tid * 4 + o, i = idx >> 5, jj = idx & 31;
-        float acc = 0.f;
-#pragma unroll 8
-        for (int m = 0; m < 32; ++m) acc += T22[i * AS + m] * sX[m * 33 + jj];
-        r[o] = -acc;
-      }
-      __syncthreads();
-#pragma unroll
-      for (int o = 0; o < 4; ++o) {
-        const int idx = tid * 4 + o;
-        A21[(idx >> 5) * AS + (idx & 31)] = r[o];
-      }
+      float c2[4] = {0.f, 0.f, 0.f, 0.f};
+      mma_split(c2, 32 + 16 * mt, 32, sX, XS, 0, nt * 8);                               // T22 X
+      mma_split(c2, 32 + 16 * mt, 48, sX, XS, 16, nt * 8);
+      float* A21 = &s.Akk[(32 + 16 * mt) * AS + nt * 8 + tig * 2];
+      *reinterpret_cast<float2*>(&A21[gid * AS]) = make_float2(-c2[0], -c2[1]);
+      *reinterpret_cast<float2*>(&A21[(gid + 8) * AS]) = make_float2(-c2[2], -c2[3]);
       __syncthreads();
     }
   }
 
   KDA_DBG_CLOCK(p.dbg, 22);
-  // ---- P5b: Tm (bf16) to global for the backward; kGam = k * exp2(G) (bf16) into the q buffer ----------
+  // ---- P5b: Tm (bf16) to global for the backward ---------------------------------------------------------
   if (p.TI) {
     unsigned char* gT = p.TI + tile * TILE_TT;
     for (int i = tid; i < C * 8; i += 256) {
@@ -462,16 +466,6 @@ __global__ void __launch_bounds__(256, 2) kda_chunk_prepare_kernel(const PrepPar
       *reinterpret_cast<uint4*>(gT + swz<128>(r, pc * 8)) =
           make_uint4(pack_bf16(t0.x, t0.y), pack_bf16(t0.z, t0.w), pack_bf16(t1.x, t1.y), pack_bf16(t1.z, t1.w));
     }
-  }
-  for (int i = tid; i < C * 16; i += 256) {
-    const int r = i >> 4, pc = i & 15;
-    const uint4 kr = *reinterpret_cast<const uint4*>(&s.k[r * QS + pc * 8]);
-    const float4 Ga = *reinterpret_cast<const float4*>(&s.G[r * GS + pc * 8]);
-    const float4 Gb = *reinterpret_cast<const float4*>(&s.G[r * GS + pc * 8 + 4]);
-    const float2 k0 = unpack_bf16(kr.x), k1 = unpack_bf16(kr.y), k2 = unpack_bf16(kr.z), k3 = unpack_bf16(kr.w);
-    *reinterpret_cast<uint4*>(&s.q[r * QS + pc * 8]) =
-        make_uint4(pack_bf16(k0.x * ex2(Ga.x), k0.y * ex2(Ga.y)), pack_bf16(k1.x * ex2(Ga.z), k1.y * ex2(Ga.w)),
-                   pack_bf16(k2.x * ex2(Gb.x), k2.y * ex2(Gb.y)), pack_bf16(k3.x * ex2(Gb.z), k3.y * ex2(Gb.w)));
   }
   __syncthreads();   // G is dead from here on: its buffer stages the UT and W tiles
   KDA_DBG_CLOCK(p.dbg, 23);
