@@ -76,7 +76,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -159,7 +159,7 @@ def run_reference(args, rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="train_bf16", choices=sorted(WORKLOADS))
@@ -239,13 +239,13 @@ def main():
         launches_per_step = 3
 
     # ---------------- kernel-resident timing ----------------
-    for _ in range(args.warmup):
-        step()
-    barrier()
     sampler = ClockSampler(local_rank if os.environ.get("CUDA_VISIBLE_DEVICES") is None else
                            int(os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local_rank]))
     if rank == 0:
-        sampler.start()
+        sampler.start()          # started before the warm-up: nvidia-smi needs a moment to deliver samples
+    for _ in range(args.warmup):
+        step()
+    barrier()
     _lib.profile_enable(True)
     _lib.profile_read(reset=True)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

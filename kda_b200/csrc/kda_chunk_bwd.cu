@@ -286,7 +286,6 @@ struct MainSmem {
     float hdh[4][KD];       // partial sums over v of h * dh' (phase A)
   };
   float dgl[KD];            // extra gradient of G at the chunk's last row
-  float carry[KD];          // cross-half carry of the reverse cumsum
   float2 Ad[4][16][16];     // diagonal 16x16 blocks of (dAqk, beta dAkk), fp32
   unsigned char TI[TILE_TT];
   unsigned char RKK[TILE_TT];
@@ -876,18 +875,25 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_kernel(const MainPa
   }
 
   // =========================== phase D: diagonal 16x16 blocks pairwise + epilogue =======================
-  // One thread per key column and half chunk (two 16-row blocks).  The decay between rows of a block is the
-  // running product of the per-row factors lam_s = exp2(G_s - G_{s-1}) <= 1 (range-safe, no exp per pair).
+  // One thread per PAIR of key columns and 16-row block, all arithmetic in packed fp32x2 (sm_100 FFMA2).
+  // The decay between rows of a block is the running product of the per-row factors
+  // lam_s = exp2(G_s - G_{s-1}) <= 1 (range-safe, no exp per pair).
   // dG = q dq + k (dk+ - dk-), dg = reverse cumsum over the chunk, final dq / dk / dg.
   {
-    const int kk = tid & 127, half = tid >> 7;
-    float cq[32], cp[32], cn[32];
+    const int kp = tid & 63, b = tid >> 6, kk = 2 * kp;
+    float4* sAd4 = reinterpret_cast<float4*>(s.TI);          // (a1, a1, a2, a2) per (block, t, j): TI, RKK are dead
+    static_assert(4 * 16 * 16 * sizeof(float4) <= 2 * TILE_TT, "duplicated diagonal blocks must fit TI + RKK");
+    for (int i = tid; i < 1024; i += 256) {
+      const float2 a = (&s.Ad[0][0][0])[i];
+      sAd4[i] = make_float4(a.x, a.x, a.y, a.y);
+    }
+    float2 cq[16], cp[16], cn[16];
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      const int t = half * 32 + i;
-      cq[i] = stq[t * FS + kk];
-      cp[i] = stp[t * FS + kk];
-      cn[i] = stn[t * FS + kk];
+    for (int i = 0; i < 16; ++i) {
+      const int t = b * 16 + i;
+      cq[i] = *reinterpret_cast<const float2*>(&stq[t * FS + kk]);
+      cp[i] = *reinterpret_cast<const float2*>(&stp[t * FS + kk]);
+      cn[i] = *reinterpret_cast<const float2*>(&stn[t * FS + kk]);
     }
     fence_proxy_async();
     __syncthreads();   // (8) the staging regions are free again: fetch the next tile's phase-A operands
@@ -896,61 +902,71 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_kernel(const MainPa
       fetch_do(next_idx);
     }
     KDA_DBG_CLOCK(dbg, 10);
-    float dGv[32];
+    float2 lam[16], qv[16], kv[16];
 #pragma unroll
-    for (int bb = 0; bb < 2; ++bb) {
-      const int b = half * 2 + bb;
-      float lam[16], qv[16], kv[16];
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const int t = b * 16 + i;
-        const float Gt = s.G[t * GS + kk];
-        const float Gp = (i > 0) ? s.G[(t - 1) * GS + kk] : Gt;
-        lam[i] = ex2(Gt - Gp);
-        qv[i] = __bfloat162float(s.q[t * QS + kk]);
-        kv[i] = __bfloat162float(s.k[t * QS + kk]);
-      }
-#pragma unroll
-      for (int t = 0; t < 16; ++t) {
-        float D = 1.f;
-#pragma unroll
-        for (int j = t; j >= 0; --j) {
-          const float2 a = s.Ad[b][t][j];
-          const float sa = a.x;
-          const float kd = kv[j] * D;
-          cq[bb * 16 + t] = fmaf(sa, kd, cq[bb * 16 + t]);
-          cp[bb * 16 + t] = fmaf(a.y, kd, cp[bb * 16 + t]);
-          cn[bb * 16 + j] = fmaf(D, sa * qv[t] + a.y * kv[t], cn[bb * 16 + j]);
-          D *= lam[j];      // decay from row j-1 to row t
-        }
-      }
-      KDA_DBG_CLOCK(dbg, 11 + 2 * bb);
-      // dq, dk replace this thread's own q, k elements in shared memory (nobody else reads them any more)
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const int t = b * 16 + i;
-        const int r = bb * 16 + i;
-        dGv[r] = qv[i] * cq[r] + kv[i] * (cp[r] - cn[r]);
-        s.q[t * QS + kk] = __float2bfloat16_rn(cq[r]);
-        s.k[t * QS + kk] = __float2bfloat16_rn(cp[r] + cn[r]);
-      }
-      KDA_DBG_CLOCK(dbg, 12 + 2 * bb);
+    for (int i = 0; i < 16; ++i) {
+      const int t = b * 16 + i;
+      const float2 Gt = *reinterpret_cast<const float2*>(&s.G[t * GS + kk]);
+      const float2 Gp = (i > 0) ? *reinterpret_cast<const float2*>(&s.G[(t - 1) * GS + kk]) : Gt;
+      lam[i] = make_float2(ex2(Gt.x - Gp.x), ex2(Gt.y - Gp.y));
+      qv[i] = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.q[t * QS + kk]));
+      kv[i] = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.k[t * QS + kk]));
     }
-    if (half == 1) dGv[31] += s.dgl[kk];
-    {
-      float run = 0.f;
 #pragma unroll
-      for (int i = 31; i >= 0; --i) {
-        run += dGv[i];
+    for (int t = 0; t < 16; ++t) {
+      float2 D = make_float2(1.f, 1.f);
+#pragma unroll
+      for (int j = t; j >= 0; --j) {
+        const float4 a = sAd4[(b * 16 + t) * 16 + j];
+        const float2 a1 = make_float2(a.x, a.y), a2 = make_float2(a.z, a.w);
+        const float2 kd = __fmul2_rn(kv[j], D);
+        cq[t] = __ffma2_rn(a1, kd, cq[t]);
+        cp[t] = __ffma2_rn(a2, kd, cp[t]);
+        const float2 tmp = __ffma2_rn(a2, kv[t], __fmul2_rn(a1, qv[t]));
+        cn[j] = __ffma2_rn(D, tmp, cn[j]);
+        D = __fmul2_rn(D, lam[j]);      // decay from row j-1 to row t
+      }
+    }
+    KDA_DBG_CLOCK(dbg, 11);
+    // dq, dk replace this thread's own q, k elements in shared memory (nobody else reads them any more)
+    float2 dGv[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int t = b * 16 + i;
+      const float2 dkk = make_float2(cp[i].x + cn[i].x, cp[i].y + cn[i].y);
+      dGv[i] = make_float2(qv[i].x * cq[i].x + kv[i].x * (cp[i].x - cn[i].x), qv[i].y * cq[i].y + kv[i].y * (cp[i].y - cn[i].y));
+      *reinterpret_cast<uint32_t*>(&s.q[t * QS + kk]) = pack_bf16(cq[i].x, cq[i].y);
+      *reinterpret_cast<uint32_t*>(&s.k[t * QS + kk]) = pack_bf16(dkk.x, dkk.y);
+    }
+    if (b == 3) {
+      dGv[15].x += s.dgl[kk];
+      dGv[15].y += s.dgl[kk + 1];
+    }
+    float* carry = &s.red[0][0];          // [4][128]; the dbeta partials in it were consumed before sync (8)
+    {
+      float2 run = make_float2(0.f, 0.f);
+#pragma unroll
+      for (int i = 15; i >= 0; --i) {
+        run.x += dGv[i].x;
+        run.y += dGv[i].y;
         dGv[i] = run;
       }
-      if (half == 1) s.carry[kk] = run;
+      *reinterpret_cast<float2*>(&carry[b * KD + kk]) = run;
     }
     __syncthreads();
     {
-      const float add = half ? 0.f : s.carry[kk];
+      float2 add = make_float2(0.f, 0.f);
 #pragma unroll
-      for (int i = 0; i < 32; ++i) s.G[(half * 32 + i) * GS + kk] = dGv[i] + add;   // dg replaces G
+      for (int bb = 1; bb < 4; ++bb) {
+        if (bb > b) {
+          const float2 cb = *reinterpret_cast<const float2*>(&carry[bb * KD + kk]);
+          add.x += cb.x;
+          add.y += cb.y;
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 16; ++i)
+        *reinterpret_cast<float2*>(&s.G[(b * 16 + i) * GS + kk]) = make_float2(dGv[i].x + add.x, dGv[i].y + add.y);   // dg replaces G
     }
     __syncthreads();
     // coalesced 16-byte stores of dq, dk (bf16) and dg (fp32) rows
