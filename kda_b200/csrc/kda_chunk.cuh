@@ -8,7 +8,8 @@
 //   AQK, TI, RKK : [64 t][64 j]      128-byte rows      Aqk (lower incl. diagonal), Tm = (I + Akk)^-1, raw <k_t D, k_j>
 //   UT        : [128 v][64 t]        128-byte rows      u^T,  u = Tm (beta v)
 //   GL        : fp32 [128]                              Gam_last = exp(G_last)
-//   HS, DH    : [128 v][128 k]       256-byte rows      transposed state at chunk start / its gradient at chunk end
+//   HS, DH    : [128 v][128 k]       two [128 v][64 k] spans of 128-byte rows (vk_off): transposed state at chunk
+//                                    start / its gradient at chunk end; each span is a tcgen05 SW128 operand tile
 //   VNEWT, DVNEWT : [128 v][64 t]    128-byte rows      v_new^T and its gradient
 #pragma once
 
@@ -91,6 +92,9 @@ __device__ __forceinline__ ChunkInfo chunk_info(const int* seq_chunk_off, const 
   ci.len = rem < C ? static_cast<int>(rem) : C;
   return ci;
 }
+
+// byte offset of element (v, k) of a [128 v][128 k] state tile: span k/64, then the 128-byte-row swizzle
+__device__ __forceinline__ uint32_t vk_off(int v, int k) { return (static_cast<uint32_t>(k >> 6) << 14) + swz<128>(v, k & 63); }
 
 // ---- development aid: phase clocks of CTA (0,0), written when a buffer has been registered --------------
 extern long long* g_dbg_clocks;   // device pointer or NULL

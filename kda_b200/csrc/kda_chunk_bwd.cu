@@ -168,10 +168,10 @@ __global__ void __launch_bounds__(RS_THREADS, 1) kda_chunk_bwd_scan_kernel(const
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
         const int kk = ks * 16 + tig * 2;
-        *reinterpret_cast<uint32_t*>(g + swz<256>(v0 + gid, kk)) = dhA[ks][0];
-        *reinterpret_cast<uint32_t*>(g + swz<256>(v0 + gid + 8, kk)) = dhA[ks][1];
-        *reinterpret_cast<uint32_t*>(g + swz<256>(v0 + gid, kk + 8)) = dhA[ks][2];
-        *reinterpret_cast<uint32_t*>(g + swz<256>(v0 + gid + 8, kk + 8)) = dhA[ks][3];
+        *reinterpret_cast<uint32_t*>(g + vk_off(v0 + gid, kk)) = dhA[ks][0];
+        *reinterpret_cast<uint32_t*>(g + vk_off(v0 + gid + 8, kk)) = dhA[ks][1];
+        *reinterpret_cast<uint32_t*>(g + vk_off(v0 + gid, kk + 8)) = dhA[ks][2];
+        *reinterpret_cast<uint32_t*>(g + vk_off(v0 + gid + 8, kk + 8)) = dhA[ks][3];
       }
     }
     // dO^T as A fragments: A[m = v][k = t] from the slab stored [t][v]  (transposed ldmatrix)
@@ -412,8 +412,8 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_kernel(const MainPa
 #pragma unroll 1
   for (int ks = 0; ks < 8; ++ks) {
     uint32_t bh[4], bd[4];
-    ldsm_x4_t(bh, uHS + swz<256>(ks * 16 + trow, n0 + tcol));      // B[k=v][n=kk] = h[kk][v]
-    ldsm_x4_t(bd, uDH + swz<256>(ks * 16 + trow, n0 + tcol));      // B[k=v][n=kk] = dh'[kk][v]
+    ldsm_x4_t(bh, uHS + vk_off(ks * 16 + trow, n0 + tcol));      // B[k=v][n=kk] = h[kk][v]
+    ldsm_x4_t(bd, uDH + vk_off(ks * 16 + trow, n0 + tcol));      // B[k=v][n=kk] = dh'[kk][v]
 #pragma unroll
     for (int mt = 0; mt < 4; ++mt) {
       uint32_t a[4];
@@ -448,8 +448,8 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_kernel(const MainPa
     float ax = 0.f, ay = 0.f;
 #pragma unroll 4
     for (int vv = vq * 32; vv < vq * 32 + 32; ++vv) {
-      const float2 hh = unpack_bf16(*reinterpret_cast<const uint32_t*>(s.HS + swz<256>(vv, 2 * kp)));
-      const float2 dd = unpack_bf16(*reinterpret_cast<const uint32_t*>(s.DH + swz<256>(vv, 2 * kp)));
+      const float2 hh = unpack_bf16(*reinterpret_cast<const uint32_t*>(s.HS + vk_off(vv, 2 * kp)));
+      const float2 dd = unpack_bf16(*reinterpret_cast<const uint32_t*>(s.DH + vk_off(vv, 2 * kp)));
       ax += hh.x * dd.x;
       ay += hh.y * dd.y;
     }

@@ -653,10 +653,10 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1) kda_chunk_scan_kernel(const S
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
         const int kk = ks * 16 + tig * 2;
-        *reinterpret_cast<uint32_t*>(g + swz<256>(v0 + gid, kk)) = hA[ks][0];
-        *reinterpret_cast<uint32_t*>(g + swz<256>(v0 + gid + 8, kk)) = hA[ks][1];
-        *reinterpret_cast<uint32_t*>(g + swz<256>(v0 + gid, kk + 8)) = hA[ks][2];
-        *reinterpret_cast<uint32_t*>(g + swz<256>(v0 + gid + 8, kk + 8)) = hA[ks][3];
+        *reinterpret_cast<uint32_t*>(g + vk_off(v0 + gid, kk)) = hA[ks][0];
+        *reinterpret_cast<uint32_t*>(g + vk_off(v0 + gid + 8, kk)) = hA[ks][1];
+        *reinterpret_cast<uint32_t*>(g + vk_off(v0 + gid, kk + 8)) = hA[ks][2];
+        *reinterpret_cast<uint32_t*>(g + vk_off(v0 + gid + 8, kk + 8)) = hA[ks][3];
       }
     }
 
