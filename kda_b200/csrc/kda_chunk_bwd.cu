@@ -22,6 +22,7 @@
 #include <mutex>
 
 #include "kda_chunk.cuh"
+#include "kda_chunk_bwd.cuh"
 
 namespace kda {
 
@@ -301,20 +302,6 @@ static_assert(3 * C * FS * 4 <= C * QS * 2 + 2 * TILE_VK + 2 * TILE_VT, "staged 
 static_assert(sizeof(MainSmem) <= 227 * 1024, "MainSmem too large");
 static_assert(C * QS * 2 + C * TS * 2 <= TILE_VK, "aliasing of HS/DH regions");
 static_assert(C * TS * 2 <= TILE_VT && C * TS * 2 <= C * QS * 2, "aliasing of VN/dO regions");
-
-struct MainParams {
-  const __nv_bfloat16 *q, *k, *v, *d_o;
-  const float *g, *beta;
-  const int* cu;
-  const int *seq_chunk_off, *chunk_seq;
-  const unsigned char *TI, *RKK, *HS, *VNEWT, *DH, *DVNEWT;
-  __nv_bfloat16 *dv, *dq, *dk;
-  float *dbeta, *dg;
-  unsigned* status;
-  long long* dbg;
-  int N, H;
-  float scale;
-};
 
 __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_kernel(const MainParams p) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -1120,8 +1107,7 @@ extern "C" int kda_chunk_bwd(const kda_chunk_args* args, void* stream) {
   mp.dv = static_cast<__nv_bfloat16*>(a.dv); mp.dq = static_cast<__nv_bfloat16*>(a.dq); mp.dk = static_cast<__nv_bfloat16*>(a.dk);
   mp.dbeta = a.dbeta; mp.dg = a.dg; mp.status = w.status; mp.dbg = g_dbg_clocks;
   mp.N = a.N; mp.H = a.H; mp.scale = a.scale;
-  kda_chunk_bwd_main_kernel<<<main_grid(NTmax, a.H), 256, sizeof(MainSmem), st>>>(mp);
-  if ((e = cudaGetLastError()) != cudaSuccess) return static_cast<int>(e);
+  if ((e = launch_bwd_main_tc(mp, main_grid(NTmax, a.H), st)) != cudaSuccess) return static_cast<int>(e);
   prof_mark(prof, KDA_STAGE_BWD_MAIN, st);
 
   if (l2) {

@@ -1,0 +1,25 @@
+// Parameters shared by the per-chunk backward kernels.
+#pragma once
+
+#include "kda_chunk.cuh"
+
+namespace kda {
+
+struct MainParams {
+  const __nv_bfloat16 *q, *k, *v, *d_o;
+  const float *g, *beta;
+  const int* cu;
+  const int *seq_chunk_off, *chunk_seq;
+  const unsigned char *TI, *RKK, *HS, *VNEWT, *DH, *DVNEWT;
+  __nv_bfloat16 *dv, *dq, *dk;
+  float *dbeta, *dg;
+  unsigned* status;
+  long long* dbg;
+  int N, H;
+  float scale;
+};
+
+// tcgen05 / TMEM version of the per-chunk backward kernel (kda_chunk_bwd_tc.cu)
+cudaError_t launch_bwd_main_tc(const MainParams& p, int grid, cudaStream_t st);
+
+}  // namespace kda

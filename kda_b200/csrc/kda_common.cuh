@@ -128,6 +128,10 @@ __device__ __forceinline__ void cp_async16(void* dst_smem, const void* src_gmem,
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst_smem)), "l"(src_gmem), "r"(sz)
                : "memory");
 }
+__device__ __forceinline__ void cp_async4(void* dst_smem, const void* src_gmem, bool valid) {
+  const unsigned sz = valid ? 4u : 0u;
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(smem_u32(dst_smem)), "l"(src_gmem), "r"(sz) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
