@@ -29,6 +29,7 @@ namespace kda {
 namespace {
 
 constexpr uint32_t SPAN = 16384;    // bytes of one [128 rows][64] tile
+constexpr int NT = 512;             // threads per CTA: 16 warps = 4 TMEM lane quadrants x 4 column parts
 
 struct TcSmem {
   // ---- SW128 operand tiles; every offset is a multiple of 1024 -------------------------------------------------
@@ -44,11 +45,16 @@ struct TcSmem {
   __nv_bfloat16 q[C * KD];      // [64][128]; at the end dq
   __nv_bfloat16 k[C * KD];      // at the end dk
   float G[C * KD];              // log2-domain cumsum of g; at the end dg
-  float4 Ad[2][16][16];         // diagonal blocks: (a1[b], a1[b+2], a2[b], a2[b+2]), a1 = scale dAqk, a2 = beta dAkk
+  float2 Ad[4][16][16];         // diagonal blocks: (a1, a2) = (scale dAqk, beta dAkk)
   float beta[C];
-  float hdh[4][KD];             // partial sums over v of h dh'
-  float dbp[4][C];              // dbeta partial sums
-  float dglp[2][KD];            // partial sums over rows of k dk_end
+  float hdh[KD];                // sum over v of h dh'
+  union {
+    float hdh_part[8][KD];      // its partial sums (phase A only)
+    struct {
+      float dbp[8][C];          // dbeta partial sums (from phase B1 on)
+      float dglp[4][KD];        // partial sums over rows of k dk_end (phase D)
+    };
+  };
   float carry[4][KD];           // block totals of the reverse cumsum
   uint64_t barS, barB, barM;
   uint32_t tmem_slot;
@@ -82,11 +88,11 @@ __device__ __forceinline__ unsigned char* sw_piece(unsigned char* tile, int row,
 
 }  // namespace
 
-__global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_tc_kernel(const MainParams p) {
+__global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const MainParams p) {
   extern __shared__ unsigned char smem_raw[];
   TcSmem& s = *reinterpret_cast<TcSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int q4 = warp & 3, half = warp >> 2;          // TMEM lane quadrant of this warp; which half of the columns
+  const int q4 = warp & 3, part = warp >> 2;          // TMEM lane quadrant of this warp; which 16 of the 64 columns
   const long long total_tiles = static_cast<long long>(p.seq_chunk_off[p.N]) * p.H;
 
   // aliases inside the tile regions
@@ -127,7 +133,7 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_tc_kernel(const Mai
   auto fetch_do = [&](long long idx) {          // all threads: dO rows of tile idx as two K-major sub-tiles
     const int cc = static_cast<int>(idx / p.H), hh = static_cast<int>(idx % p.H);
     const ChunkInfo cn = chunk_info(p.seq_chunk_off, p.chunk_seq, p.cu, cc);
-    for (int i = tid; i < C * 16; i += 256) {
+    for (int i = tid; i < C * 16; i += NT) {
       const int r = i >> 4, pc = i & 15;
       const bool ok = r < cn.len;
       const size_t row = (static_cast<size_t>(cn.tok0 + (ok ? r : 0)) * p.H + hh) * KD + pc * 8;
@@ -149,14 +155,16 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_tc_kernel(const Mai
     const int len = ci.len;
     const size_t tile = static_cast<size_t>(idx);
     const long long next_idx = idx + gridDim.x;
+    long long* const dbg = (it == 2) ? p.dbg : nullptr;   // development aid: clocks of a steady-state tile
 
+    KDA_DBG_CLOCK(dbg, 0);
     // ---- second load group: Tm, raw kk (bulk); q, k, g, v, beta (async copies); lands behind phase A ------------
     if (tid == 0) {
       mbar_expect_tx(&s.barB, 2 * TILE_TT);
       bulk_g2s(s.TI, p.TI + tile * TILE_TT, TILE_TT, &s.barB);
       bulk_g2s(s.RKK, p.RKK + tile * TILE_TT, TILE_TT, &s.barB);
     }
-    for (int i = tid; i < C * 16; i += 256) {
+    for (int i = tid; i < C * 16; i += NT) {
       const int r = i >> 4, pc = i & 15;
       const bool ok = r < len;
       const size_t row = (static_cast<size_t>(ci.tok0 + (ok ? r : 0)) * p.H + h) * KD + pc * 8;
@@ -164,7 +172,7 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_tc_kernel(const Mai
       cp_async16(&s.k[r * KD + pc * 8], p.k + row, ok);
       cp_async16(sw_piece(s.V + (pc >> 3) * 8192, r, pc & 7), p.v + row, ok);
     }
-    for (int i = tid; i < C * 32; i += 256) {
+    for (int i = tid; i < C * 32; i += NT) {
       const int r = i >> 5, pc = i & 31;
       const bool ok = r < len;
       const size_t row = (static_cast<size_t>(ci.tok0 + (ok ? r : 0)) * p.H + h) * KD + pc * 4;
@@ -181,6 +189,7 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_tc_kernel(const Mai
     }
     umma::fence_after_sync();
 
+    KDA_DBG_CLOCK(dbg, 1);
     // =========================== phase A: state-dependent products ==================================================
     if (tid == 0 && alive) {
       const uint32_t aHS = smem_u32(s.HS), aDH = smem_u32(s.DH), aVN = smem_u32(s.VN), aDVN = smem_u32(s.DVN), aDO = smem_u32(s.dO);
@@ -188,54 +197,55 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_tc_kernel(const Mai
       constexpr uint32_t i2 = umma::instr_desc(128, 64, true, true, false, true);
       constexpr uint32_t i3 = umma::instr_desc(128, 64, true, true);
       constexpr uint32_t i4 = umma::instr_desc(64, 64, false, true);
+      // base descriptors once; a k-step advances an MN-major operand by two atoms (2048 B) and a K-major one by 32 B
+      const uint64_t dHS = umma::desc_mnmajor(aHS, 0, SPAN), dDHm = umma::desc_mnmajor(aDH, 0, SPAN);
+      const uint64_t dVNm = umma::desc_mnmajor(aVN, 0, SPAN), dDVNm = umma::desc_mnmajor(aDVN, 0, SPAN);
+      const uint64_t dDO0 = umma::desc_kmajor(aDO, 0), dDO1 = umma::desc_kmajor(aDO + 8192, 0);
 #pragma unroll
       for (int sK = 0; sK < 8; ++sK) {
-        const uint64_t dHS = umma::desc_mnmajor(aHS, sK, SPAN);
-        const uint64_t dDOk = umma::desc_kmajor(aDO + (sK >> 2) * 8192, sK & 3);
-        umma::mma_ss(tb + C_DQG, dHS, dDOk, i1, sK > 0);                                          // dqg^T = h dO^T
-        umma::mma_ss(tb + C_DW, dHS, umma::desc_mnmajor(aDVN, sK, SPAN), i2, sK > 0);              // dw^T = -h dv_new^T
-        umma::mma_ss(tb + C_DKG, umma::desc_mnmajor(aDH, sK, SPAN), umma::desc_mnmajor(aVN, sK, SPAN), i3, sK > 0);   // dkg^T
-        umma::mma_ss(tb + C_DAQ, dDOk, umma::desc_mnmajor(aVN, sK, SPAN), i4, sK > 0);             // dAqk = dO v_new^T
+        const uint64_t mn = static_cast<uint64_t>(sK) * 128u, dDOk = ((sK >> 2) ? dDO1 : dDO0) + static_cast<uint64_t>(sK & 3) * 2u;
+        umma::mma_ss(tb + C_DQG, dHS + mn, dDOk, i1, sK > 0);                 // dqg^T = h dO^T
+        umma::mma_ss(tb + C_DW, dHS + mn, dDVNm + mn, i2, sK > 0);            // dw^T = -h dv_new^T
+        umma::mma_ss(tb + C_DKG, dDHm + mn, dVNm + mn, i3, sK > 0);           // dkg^T = dh' v_new^T
+        umma::mma_ss(tb + C_DAQ, dDOk, dVNm + mn, i4, sK > 0);                // dAqk = dO v_new^T
       }
       umma::commit(&s.barM);
     }
+    KDA_DBG_CLOCK(dbg, 2);
     // ---- meanwhile: the second load group, G = cumsum(g) log2(e), sum_v h dh' ------------------------------------
     cp_async_wait<0>();
     __syncthreads();
     {
-      const int col = tid & 127, hf = tid >> 7;
-      float gv[32];
+      const int col = tid & 127, qr = tid >> 7;        // four quarters of 16 rows
+      float gv[16];
 #pragma unroll
-      for (int i = 0; i < 32; ++i) gv[i] = s.G[(hf * 32 + i) * KD + col];
+      for (int i = 0; i < 16; ++i) gv[i] = s.G[(qr * 16 + i) * KD + col];
       float run = 0.f;
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
+      for (int i = 0; i < 16; ++i) {
         run += gv[i];
         gv[i] = run;
       }
-      if (hf == 0) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) s.G[i * KD + col] = gv[i] * LOG2E;
-      }
+      s.carry[qr][col] = run;
       __syncthreads();
-      if (hf == 1) {
-        const float carry = s.G[31 * KD + col];
+      float pre = 0.f;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) s.G[(32 + i) * KD + col] = carry + gv[i] * LOG2E;
-      }
+      for (int b = 0; b < 3; ++b) pre += (b < qr) ? s.carry[b][col] : 0.f;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) s.G[(qr * 16 + i) * KD + col] = (pre + gv[i]) * LOG2E;
     }
     {
       const int kp = tid & 63, vq = tid >> 6;
       float ax = 0.f, ay = 0.f;
 #pragma unroll 4
-      for (int vv = vq * 32; vv < vq * 32 + 32; ++vv) {
+      for (int vv = vq * 16; vv < vq * 16 + 16; ++vv) {
         const float2 hh = unpack_bf16(*reinterpret_cast<const uint32_t*>(s.HS + vk_off(vv, 2 * kp)));
         const float2 dd = unpack_bf16(*reinterpret_cast<const uint32_t*>(s.DH + vk_off(vv, 2 * kp)));
         ax += hh.x * dd.x;
         ay += hh.y * dd.y;
       }
-      s.hdh[vq][2 * kp] = ax;
-      s.hdh[vq][2 * kp + 1] = ay;
+      s.hdh_part[vq][2 * kp] = ax;
+      s.hdh_part[vq][2 * kp + 1] = ay;
     }
     if (alive && !mbar_wait(&s.barB, it & 1)) {
       if (tid == 0) atomicOr(p.status, 32u);
@@ -246,32 +256,37 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_tc_kernel(const Mai
       alive = false;
     }
     ++mph;
-    alive = __syncthreads_and(alive);      // also: G complete, hdh complete, phase A products complete for everybody
+    alive = __syncthreads_and(alive);      // also: G complete, hdh partials complete, phase A products complete for everybody
     if (!alive) break;
     umma::fence_after_sync();
+    if (tid < KD)
+      s.hdh[tid] = s.hdh_part[0][tid] + s.hdh_part[1][tid] + s.hdh_part[2][tid] + s.hdh_part[3][tid] + s.hdh_part[4][tid] +
+                   s.hdh_part[5][tid] + s.hdh_part[6][tid] + s.hdh_part[7][tid];      // consumed long before dbp is written
 
+    KDA_DBG_CLOCK(dbg, 3);
     // ---- post-A: dw^T -> bf16 tile; dAqk -> masked bf16 tile + diagonal blocks; k Gam tile -------------------------
     {
-      float v[32];
-      tmem_ld32(tq + C_DW + 32 * half, v);
+      float v[16];
+      umma::tmem_ld16(tq + C_DW + 16 * part, v);
+      umma::tmem_ld_wait();
       const int kk = 32 * q4 + lane;
-#pragma unroll
-      for (int cix = 0; cix < 4; ++cix) *reinterpret_cast<uint4*>(sw_piece(sDWT, kk, 4 * half + cix)) = pack8(&v[8 * cix]);
-      tmem_ld32(tq + C_DAQ + 32 * half, v);            // M = 64: rows 16 q4 .. +15 live in lanes 0..15 of this quadrant
+      *reinterpret_cast<uint4*>(sw_piece(sDWT, kk, 2 * part)) = pack8(&v[0]);
+      *reinterpret_cast<uint4*>(sw_piece(sDWT, kk, 2 * part + 1)) = pack8(&v[8]);
+      umma::tmem_ld16(tq + C_DAQ + 16 * part, v);      // M = 64: rows 16 q4 .. +15 live in lanes 0..15 of this quadrant
+      umma::tmem_ld_wait();
       if (lane < 16) {
         const int t = 16 * q4 + lane;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = (32 * half + i <= t) ? v[i] : 0.f;
+        for (int i = 0; i < 16; ++i) v[i] = (16 * part + i <= t) ? v[i] : 0.f;
+        *reinterpret_cast<uint4*>(sw_piece(sDAQ, t, 2 * part)) = pack8(&v[0]);
+        *reinterpret_cast<uint4*>(sw_piece(sDAQ, t, 2 * part + 1)) = pack8(&v[8]);
+        if (part == q4) {                              // these 16 columns are the diagonal block of row block q4
 #pragma unroll
-        for (int cix = 0; cix < 4; ++cix) *reinterpret_cast<uint4*>(sw_piece(sDAQ, t, 4 * half + cix)) = pack8(&v[8 * cix]);
-        if ((q4 >> 1) == half) {                       // the diagonal block of row block q4 lies in this half of the columns
-          float* ad = reinterpret_cast<float*>(&s.Ad[q4 & 1][lane][0]);
-#pragma unroll
-          for (int cc = 0; cc < 16; ++cc) ad[cc * 4 + (q4 >> 1)] = p.scale * v[16 * (q4 & 1) + cc];
+          for (int cc = 0; cc < 16; ++cc) s.Ad[q4][lane][cc].x = p.scale * v[cc];
         }
       }
     }
-    for (int i = tid; i < C * 16; i += 256) {          // k Gam as two K-major sub-tiles [64 j][64 kk]
+    for (int i = tid; i < C * 16; i += NT) {          // k Gam as two K-major sub-tiles [64 j][64 kk]
       const int j = i >> 4, pc = i & 15;
       const uint4 kr = *reinterpret_cast<const uint4*>(&s.k[j * KD + pc * 8]);
       const float4 Ga = *reinterpret_cast<const float4*>(&s.G[j * KD + pc * 8]);
@@ -286,62 +301,71 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_tc_kernel(const Mai
     __syncthreads();
     umma::fence_after_sync();
 
+    KDA_DBG_CLOCK(dbg, 4);
     // =========================== phase B1 ===========================================================================
     if (tid == 0) {
       const uint32_t aDVN = smem_u32(s.DVN), aV = smem_u32(s.V), aDWT = smem_u32(sDWT), aKG = smem_u32(sKG), aTI = smem_u32(s.TI);
       constexpr uint32_t iT = umma::instr_desc(64, 64, true, false);
       constexpr uint32_t iTt = umma::instr_desc(64, 64, false, true);
       constexpr uint32_t iB = umma::instr_desc(128, 64, false, true);
+      const uint64_t dDuM = umma::desc_mnmajor(aDVN, 0, SPAN), dDwM = umma::desc_mnmajor(aDWT, 0, SPAN), dTiM = umma::desc_mnmajor(aTI, 0, SPAN);
+      const uint64_t dV0 = umma::desc_kmajor(aV, 0), dV1 = umma::desc_kmajor(aV + 8192, 0);
+      const uint64_t dKg0 = umma::desc_kmajor(aKG, 0), dKg1 = umma::desc_kmajor(aKG + 8192, 0);
+      const uint64_t dDuK = umma::desc_kmajor(aDVN, 0), dDwK = umma::desc_kmajor(aDWT, 0);
 #pragma unroll
       for (int sK = 0; sK < 8; ++sK) {
-        const uint64_t dDu = umma::desc_mnmajor(aDVN, sK, SPAN), dVk = umma::desc_kmajor(aV + (sK >> 2) * 8192, sK & 3);
-        umma::mma_ss(tb + C_DAQ, dDu, dVk, iT, sK > 0);       // dTm[t][j]   += sum_v du[t][v] v[j][v]
-        umma::mma_ss(tb + C_DTT, dVk, dDu, iTt, sK > 0);      // dTm^T[j][t] += the same
+        const uint64_t mn = static_cast<uint64_t>(sK) * 128u, dVk = ((sK >> 2) ? dV1 : dV0) + static_cast<uint64_t>(sK & 3) * 2u;
+        umma::mma_ss(tb + C_DAQ, dDuM + mn, dVk, iT, sK > 0);       // dTm[t][j]   += sum_v du[t][v] v[j][v]
+        umma::mma_ss(tb + C_DTT, dVk, dDuM + mn, iTt, sK > 0);      // dTm^T[j][t] += the same
       }
 #pragma unroll
       for (int sK = 0; sK < 8; ++sK) {
-        const uint64_t dDw = umma::desc_mnmajor(aDWT, sK, SPAN), dKg = umma::desc_kmajor(aKG + (sK >> 2) * 8192, sK & 3);
-        umma::mma_ss(tb + C_DAQ, dDw, dKg, iT, 1);            // += sum_kk dw[t][kk] kGam[j][kk]
-        umma::mma_ss(tb + C_DTT, dKg, dDw, iTt, 1);
+        const uint64_t mn = static_cast<uint64_t>(sK) * 128u, dKg = ((sK >> 2) ? dKg1 : dKg0) + static_cast<uint64_t>(sK & 3) * 2u;
+        umma::mma_ss(tb + C_DAQ, dDwM + mn, dKg, iT, 1);            // += sum_kk dw[t][kk] kGam[j][kk]
+        umma::mma_ss(tb + C_DTT, dKg, dDwM + mn, iTt, 1);
       }
 #pragma unroll
       for (int sK = 0; sK < 4; ++sK) {
-        const uint64_t dTi = umma::desc_mnmajor(aTI, sK, SPAN);
-        umma::mma_ss(tb + C_DBV, umma::desc_kmajor(aDVN, sK), dTi, iB, sK > 0);     // dbv^T[v][t] = sum_t' du[t'][v] Tm[t'][t]
-        umma::mma_ss(tb + C_DBK, umma::desc_kmajor(aDWT, sK), dTi, iB, sK > 0);     // dbk^T[kk][t] = sum_t' dw[t'][kk] Tm[t'][t]
+        const uint64_t dTi = dTiM + static_cast<uint64_t>(sK) * 128u;
+        umma::mma_ss(tb + C_DBV, dDuK + static_cast<uint64_t>(sK) * 2u, dTi, iB, sK > 0);     // dbv^T[v][t] = sum_t' du[t'][v] Tm[t'][t]
+        umma::mma_ss(tb + C_DBK, dDwK + static_cast<uint64_t>(sK) * 2u, dTi, iB, sK > 0);     // dbk^T[kk][t] = sum_t' dw[t'][kk] Tm[t'][t]
       }
       umma::commit(&s.barM);
     }
     if (!mbar_wait(&s.barM, mph & 1)) alive = false;
     ++mph;
     umma::fence_after_sync();
+    KDA_DBG_CLOCK(dbg, 5);
     if (alive) {
-      float v[32];
-      tmem_ld32(tq + C_DAQ + 32 * half, v);            // dTm rows (M = 64 layout): scale the columns by beta_j
+      float v[16];
+      umma::tmem_ld16(tq + C_DAQ + 16 * part, v);      // dTm rows (M = 64 layout): scale the columns by beta_j
+      umma::tmem_ld_wait();
       if (lane < 16) {
         const int t = 16 * q4 + lane;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] *= s.beta[32 * half + i];
-#pragma unroll
-        for (int cix = 0; cix < 4; ++cix) *reinterpret_cast<uint4*>(sw_piece(sDT, t, 4 * half + cix)) = pack8(&v[8 * cix]);
+        for (int i = 0; i < 16; ++i) v[i] *= s.beta[16 * part + i];
+        *reinterpret_cast<uint4*>(sw_piece(sDT, t, 2 * part)) = pack8(&v[0]);
+        *reinterpret_cast<uint4*>(sw_piece(sDT, t, 2 * part + 1)) = pack8(&v[8]);
       }
-      tmem_ld32(tq + C_DTT + 32 * half, v);            // dTm_raw^T rows j: dbeta_j += sum_t' Tm[t'][j] dTm_raw[t'][j]
+      umma::tmem_ld16(tq + C_DTT + 16 * part, v);      // dTm_raw^T rows j: dbeta_j += sum_t' Tm[t'][j] dTm_raw[t'][j]
+      umma::tmem_ld_wait();
       if (lane < 16) {
         const int j = 16 * q4 + lane;
         float acc = 0.f;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int t2 = 32 * half + i;
+        for (int i = 0; i < 16; ++i) {
+          const int t2 = 16 * part + i;
           acc += v[i] * __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(s.TI + umma::sw128(t2, j)));
         }
-        s.dbp[half][j] = acc;
+        s.dbp[part][j] = acc;
       }
-      tmem_ld32(tq + C_DBV + 32 * half, v);            // dbv^T rows v: dv[t][v] = beta_t dbv[t][v]
+      umma::tmem_ld16(tq + C_DBV + 16 * part, v);      // dbv^T rows v: dv[t][v] = beta_t dbv[t][v]
+      umma::tmem_ld_wait();
       {
         const int vcol = 32 * q4 + lane;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int t = 32 * half + i;
+        for (int i = 0; i < 16; ++i) {
+          const int t = 16 * part + i;
           if (t < len) p.dv[(static_cast<size_t>(ci.tok0 + t) * p.H + h) * VD + vcol] = __float2bfloat16_rn(s.beta[t] * v[i]);
         }
       }
@@ -355,24 +379,28 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_tc_kernel(const Mai
     }
     umma::fence_after_sync();
 
+    KDA_DBG_CLOCK(dbg, 6);
     // =========================== phase B2: X = dTm Tm^T ============================================================
     if (tid == 0) {
       const uint32_t aDT = smem_u32(sDT), aTI = smem_u32(s.TI);
       constexpr uint32_t iX = umma::instr_desc(64, 64, false, false);
 #pragma unroll
-      for (int sK = 0; sK < 4; ++sK) umma::mma_ss(tb + C_XY, umma::desc_kmajor(aDT, sK), umma::desc_kmajor(aTI, sK), iX, sK > 0);
+      const uint64_t dDt = umma::desc_kmajor(aDT, 0), dTiK = umma::desc_kmajor(aTI, 0);
+#pragma unroll
+      for (int sK = 0; sK < 4; ++sK) umma::mma_ss(tb + C_XY, dDt + static_cast<uint64_t>(sK) * 2u, dTiK + static_cast<uint64_t>(sK) * 2u, iX, sK > 0);
       umma::commit(&s.barM);
     }
     if (!mbar_wait(&s.barM, mph & 1)) alive = false;
     ++mph;
     umma::fence_after_sync();
     if (alive) {
-      float v[32];
-      tmem_ld32(tq + C_XY + 32 * half, v);
+      float v[16];
+      umma::tmem_ld16(tq + C_XY + 16 * part, v);
+      umma::tmem_ld_wait();
       if (lane < 16) {
         const int m = 16 * q4 + lane;
-#pragma unroll
-        for (int cix = 0; cix < 4; ++cix) *reinterpret_cast<uint4*>(sw_piece(sX, m, 4 * half + cix)) = pack8(&v[8 * cix]);
+        *reinterpret_cast<uint4*>(sw_piece(sX, m, 2 * part)) = pack8(&v[0]);
+        *reinterpret_cast<uint4*>(sw_piece(sX, m, 2 * part + 1)) = pack8(&v[8]);
       }
     }
     fence_proxy_async();
@@ -384,46 +412,50 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_tc_kernel(const Mai
     }
     umma::fence_after_sync();
 
+    KDA_DBG_CLOCK(dbg, 7);
     // =========================== phase B3: Y = Tm^T X,  dAkk = -tril(Y, -1) ==========================================
     if (tid == 0) {
       const uint32_t aX = smem_u32(sX), aTI = smem_u32(s.TI);
       constexpr uint32_t iY = umma::instr_desc(64, 64, true, true);
 #pragma unroll
+      const uint64_t dTiM = umma::desc_mnmajor(aTI, 0, SPAN), dXm = umma::desc_mnmajor(aX, 0, SPAN);
+#pragma unroll
       for (int sK = 0; sK < 4; ++sK)
-        umma::mma_ss(tb + C_XY, umma::desc_mnmajor(aTI, sK, SPAN), umma::desc_mnmajor(aX, sK, SPAN), iY, sK > 0);
+        umma::mma_ss(tb + C_XY, dTiM + static_cast<uint64_t>(sK) * 128u, dXm + static_cast<uint64_t>(sK) * 128u, iY, sK > 0);
       umma::commit(&s.barM);
     }
     if (!mbar_wait(&s.barM, mph & 1)) alive = false;
     ++mph;
     umma::fence_after_sync();
     if (alive) {
-      float v[32];
-      tmem_ld32(tq + C_XY + 32 * half, v);
+      float v[16];
+      umma::tmem_ld16(tq + C_XY + 16 * part, v);
+      umma::tmem_ld_wait();
       if (lane < 16) {
         const int i0 = 16 * q4 + lane;                 // row i of dAkk
         const float br = s.beta[i0];
         float pb = 0.f;
 #pragma unroll
-        for (int cix = 0; cix < 4; ++cix) {
-          const uint4 rw = *reinterpret_cast<const uint4*>(sw_piece(s.RKK, i0, 4 * half + cix));
+        for (int cix = 0; cix < 2; ++cix) {
+          const uint4 rw = *reinterpret_cast<const uint4*>(sw_piece(s.RKK, i0, 2 * part + cix));
           const uint32_t rws[4] = {rw.x, rw.y, rw.z, rw.w};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const float2 raw = unpack_bf16(rws[e]);
-            const int j = 32 * half + 8 * cix + 2 * e;
+            const int j = 16 * part + 8 * cix + 2 * e;
             const float x0 = (j < i0) ? -v[8 * cix + 2 * e] : 0.f;
             const float x1 = (j + 1 < i0) ? -v[8 * cix + 2 * e + 1] : 0.f;
             pb += x0 * raw.x + x1 * raw.y;
             v[8 * cix + 2 * e] = br * x0;
             v[8 * cix + 2 * e + 1] = br * x1;
           }
-          *reinterpret_cast<uint4*>(sw_piece(sDAK, i0, 4 * half + cix)) = pack8(&v[8 * cix]);
         }
-        s.dbp[2 + half][i0] = pb;
-        if ((q4 >> 1) == half) {
-          float* ad = reinterpret_cast<float*>(&s.Ad[q4 & 1][lane][0]);
+        *reinterpret_cast<uint4*>(sw_piece(sDAK, i0, 2 * part)) = pack8(&v[0]);
+        *reinterpret_cast<uint4*>(sw_piece(sDAK, i0, 2 * part + 1)) = pack8(&v[8]);
+        s.dbp[4 + part][i0] = pb;
+        if (part == q4) {
 #pragma unroll
-          for (int cc = 0; cc < 16; ++cc) ad[cc * 4 + 2 + (q4 >> 1)] = v[16 * (q4 & 1) + cc];
+          for (int cc = 0; cc < 16; ++cc) s.Ad[q4][lane][cc].y = v[cc];
         }
       }
     }
@@ -434,11 +466,12 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_tc_kernel(const Mai
       break;
     }
 
+    KDA_DBG_CLOCK(dbg, 8);
     // ---- operands of phase C -------------------------------------------------------------------------------------------
     // kR_I[j][kk] = k_j 2^(G_r - G_j),  r = 16 I,  j < 16 I            rows stacked: I=1 -> 0..15, I=2 -> 16..47, I=3 -> 48..95
     // qL_J[t][kk] = scale q_t 2^(G_t - G_e), kL_J = k_t 2^(G_t - G_e), e = 16 J + 15, t >= 16 (J+1)
     //                                                                   rows stacked: J=0 -> 0..47, J=1 -> 48..79, J=2 -> 80..95
-    for (int i = tid; i < 96 * 16; i += 256) {
+    for (int i = tid; i < 96 * 16; i += NT) {
       const int R = i >> 4, pc = i & 15;
       {
         const int I = (R < 16) ? 1 : (R < 48 ? 2 : 3);
@@ -482,30 +515,36 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_tc_kernel(const Mai
     __syncthreads();
     umma::fence_after_sync();
 
+    KDA_DBG_CLOCK(dbg, 9);
     // =========================== phase C: off-diagonal blocks of the intra-chunk terms ==============================
     if (tid == 0) {
       const uint32_t aKR = smem_u32(sKR0), aQL = smem_u32(sQL0), aKL = smem_u32(sKL0), aDAQ = smem_u32(sDAQ), aDAK = smem_u32(sDAK);
       const uint32_t lKR = smem_u32(sKR1) - aKR, lQL = smem_u32(sQL1) - aQL, lKL = smem_u32(sKL1) - aKL;
       constexpr uint32_t iC1 = umma::instr_desc(128, 16, true, false);
       constexpr uint32_t iC2 = umma::instr_desc(128, 16, true, true);
+      const uint64_t dKr = umma::smem_desc(aKR, lKR, umma::ATOM_BYTES), dQl = umma::smem_desc(aQL, lQL, umma::ATOM_BYTES);
+      const uint64_t dKl = umma::smem_desc(aKL, lKL, umma::ATOM_BYTES);
+      const uint64_t dAq = umma::smem_desc(aDAQ, 16, umma::ATOM_BYTES), dAk = umma::smem_desc(aDAK, 16, umma::ATOM_BYTES);
 #pragma unroll
       for (int I = 1; I < 4; ++I) {
         const int rb = (I == 1) ? 0 : (I == 2 ? 16 : 48);
+#pragma unroll
         for (int sK = 0; sK < I; ++sK) {
-          const uint64_t dA = umma::smem_desc(aKR + (rb + 16 * sK) * 128, lKR, umma::ATOM_BYTES);     // A[kk][j] = kR_I[j][kk]
-          umma::mma_ss(tb + C_CQ + 16 * I, dA, umma::smem_desc(aDAQ + 16 * I * 128 + sK * 32, 16, umma::ATOM_BYTES), iC1, sK > 0);
-          umma::mma_ss(tb + C_CP + 16 * I, dA, umma::smem_desc(aDAK + 16 * I * 128 + sK * 32, 16, umma::ATOM_BYTES), iC1, sK > 0);
+          const uint64_t dA = dKr + static_cast<uint64_t>((rb + 16 * sK) * 8);                 // A[kk][j] = kR_I[j][kk]: row offset in 16-byte units
+          const uint64_t bo = static_cast<uint64_t>(16 * I * 8 + sK * 2);                      // B[t][j]: rows 16 I.., k-step sK
+          umma::mma_ss(tb + C_CQ + 16 * I, dA, dAq + bo, iC1, sK > 0);
+          umma::mma_ss(tb + C_CP + 16 * I, dA, dAk + bo, iC1, sK > 0);
         }
       }
 #pragma unroll
       for (int J = 0; J < 3; ++J) {
         const int rb = (J == 0) ? 0 : (J == 1 ? 48 : 80);
+#pragma unroll
         for (int sK = 0; sK < 3 - J; ++sK) {
-          const uint32_t boff = (16 * (J + 1) + 16 * sK) * 128 + 32 * J;                               // B[j][t] = dA[t][j]
-          umma::mma_ss(tb + C_CN + 16 * J, umma::smem_desc(aQL + (rb + 16 * sK) * 128, lQL, umma::ATOM_BYTES),
-                       umma::smem_desc(aDAQ + boff, 16, umma::ATOM_BYTES), iC2, sK > 0);
-          umma::mma_ss(tb + C_CN + 16 * J, umma::smem_desc(aKL + (rb + 16 * sK) * 128, lKL, umma::ATOM_BYTES),
-                       umma::smem_desc(aDAK + boff, 16, umma::ATOM_BYTES), iC2, 1);
+          const uint64_t ao = static_cast<uint64_t>((rb + 16 * sK) * 8);
+          const uint64_t bo = static_cast<uint64_t>((16 * (J + 1) + 16 * sK) * 8 + 2 * J);     // B[j][t] = dA[t][j]: rows t, columns 16 J..
+          umma::mma_ss(tb + C_CN + 16 * J, dQl + ao, dAq + bo, iC2, sK > 0);
+          umma::mma_ss(tb + C_CN + 16 * J, dKl + ao, dAk + bo, iC2, 1);
         }
       }
       umma::commit(&s.barM);
@@ -518,25 +557,39 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_tc_kernel(const Mai
       break;
     }
     umma::fence_after_sync();
+    KDA_DBG_CLOCK(dbg, 10);
     // every shared-memory operand tile is dead now: fetch the next tile's phase-A operands behind phase D
     if (next_idx < total_tiles) {
       if (tid == 0) fetch_state(next_idx);
       fetch_do(next_idx);
     }
-    if (tid < len) p.dbeta[static_cast<size_t>(ci.tok0 + tid) * p.H + h] = s.dbp[0][tid] + s.dbp[1][tid] + s.dbp[2][tid] + s.dbp[3][tid];
+    if (tid < len)
+      p.dbeta[static_cast<size_t>(ci.tok0 + tid) * p.H + h] = s.dbp[0][tid] + s.dbp[1][tid] + s.dbp[2][tid] + s.dbp[3][tid] +
+                                                             s.dbp[4][tid] + s.dbp[5][tid] + s.dbp[6][tid] + s.dbp[7][tid];
 
-    // =========================== phase D: one thread per key column and pair of 16-row blocks (half, half+2) =======
+    KDA_DBG_CLOCK(dbg, 11);
+    // =========================== phase D: one thread per key column and 16-row block ================================
     {
-      const int kk = 32 * q4 + lane;
-      float2 cq[16], cp[16], cn[16], lam[16], qv[16], kv[16];
-      float dglp = 0.f;
-#pragma unroll
-      for (int hb = 0; hb < 2; ++hb) {                 // component .x: block `half`, component .y: block `half + 2`
-        const int blk = half + 2 * hb, t0 = 16 * blk;
+      const int kk = 32 * q4 + lane, blk = part, t0 = 16 * blk;
+      float cq[16], cp[16], cn[16], lam[16], qv[16], kv[16];
+      {
         float Gc[16], a[16], b[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) Gc[i] = s.G[(t0 + i) * KD + kk];
         const float Glast = s.G[(C - 1) * KD + kk];
+        // dk-: dkg 2^(G_last - G) + 2^(G_e - G) Cn ;  sum of k dk_end feeds dG at the chunk's last row
+        umma::tmem_ld16(tq + C_DKG + t0, a);
+        umma::tmem_ld16(tq + C_CN + t0, b);
+        umma::tmem_ld_wait();
+        float dglp = 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          kv[i] = __bfloat162float(s.k[(t0 + i) * KD + kk]);
+          const float dke = a[i] * ex2(Glast - Gc[i]);
+          dglp = fmaf(kv[i], dke, dglp);
+          cn[i] = (blk < 3) ? fmaf(ex2(Gc[15] - Gc[i]), b[i], dke) : dke;
+        }
+        s.dglp[blk][kk] = dglp;
         // dq: scale (Gam dqg + L Cq)
         umma::tmem_ld16(tq + C_DQG + t0, a);
         umma::tmem_ld16(tq + C_CQ + t0, b);
@@ -545,7 +598,7 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_tc_kernel(const Mai
         for (int i = 0; i < 16; ++i) {
           float x = ex2(Gc[i]) * a[i];
           if (blk > 0) x = fmaf(ex2(Gc[i] - Gc[0]), b[i], x);
-          (hb ? cq[i].y : cq[i].x) = p.scale * x;
+          cq[i] = p.scale * x;
         }
         // dk+: Gam beta dbk + L Cp
         umma::tmem_ld16(tq + C_DBK + t0, a);
@@ -555,86 +608,59 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_tc_kernel(const Mai
         for (int i = 0; i < 16; ++i) {
           float x = ex2(Gc[i]) * s.beta[t0 + i] * a[i];
           if (blk > 0) x = fmaf(ex2(Gc[i] - Gc[0]), b[i], x);
-          (hb ? cp[i].y : cp[i].x) = x;
-        }
-        // dk-: dkg 2^(G_last - G) + 2^(G_e - G) Cn ;  sum of k dk_end feeds dG at the chunk's last row
-        umma::tmem_ld16(tq + C_DKG + t0, a);
-        umma::tmem_ld16(tq + C_CN + t0, b);
-        umma::tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float2 kq = make_float2(__bfloat162float(s.q[(t0 + i) * KD + kk]), __bfloat162float(s.k[(t0 + i) * KD + kk]));
-          const float dke = a[i] * ex2(Glast - Gc[i]);
-          dglp = fmaf(kq.y, dke, dglp);
-          float x = dke;
-          if (blk < 3) x = fmaf(ex2(Gc[15] - Gc[i]), b[i], x);
-          (hb ? cn[i].y : cn[i].x) = x;
-          (hb ? qv[i].y : qv[i].x) = kq.x;
-          (hb ? kv[i].y : kv[i].x) = kq.y;
-          (hb ? lam[i].y : lam[i].x) = (i > 0) ? ex2(Gc[i] - Gc[i - 1]) : 1.f;
+          cp[i] = x;
+          qv[i] = __bfloat162float(s.q[(t0 + i) * KD + kk]);
+          lam[i] = (i > 0) ? ex2(Gc[i] - Gc[i - 1]) : 1.f;
         }
       }
-      s.dglp[half][kk] = dglp;
-      // diagonal blocks, pairwise; D = running product of lam (range-safe)
+      KDA_DBG_CLOCK(dbg, 12);
+      // diagonal block, pairwise; D = running product of lam (range-safe)
 #pragma unroll
       for (int t = 0; t < 16; ++t) {
-        float2 D = make_float2(1.f, 1.f);
+        float D = 1.f;
 #pragma unroll
         for (int j = t; j >= 0; --j) {
-          const float4 a = s.Ad[half][t][j];
-          const float2 a1 = make_float2(a.x, a.y), a2 = make_float2(a.z, a.w);
-          const float2 kd = __fmul2_rn(kv[j], D);
-          cq[t] = __ffma2_rn(a1, kd, cq[t]);
-          cp[t] = __ffma2_rn(a2, kd, cp[t]);
-          const float2 tmp = __ffma2_rn(a2, kv[t], __fmul2_rn(a1, qv[t]));
-          cn[j] = __ffma2_rn(D, tmp, cn[j]);
-          D = __fmul2_rn(D, lam[j]);
+          const float2 a = s.Ad[blk][t][j];
+          const float kd = kv[j] * D;
+          cq[t] = fmaf(a.x, kd, cq[t]);
+          cp[t] = fmaf(a.y, kd, cp[t]);
+          cn[j] = fmaf(D, fmaf(a.y, kv[t], a.x * qv[t]), cn[j]);
+          D *= lam[j];
         }
       }
+      KDA_DBG_CLOCK(dbg, 13);
       // dG, dq, dk (in place of q, k)
-      float2 dGv[16];
+      float dGv[16];
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
-        dGv[i] = make_float2(qv[i].x * cq[i].x + kv[i].x * (cp[i].x - cn[i].x), qv[i].y * cq[i].y + kv[i].y * (cp[i].y - cn[i].y));
-        const int ta = 16 * half + i, tb2 = 16 * (half + 2) + i;
-        s.q[ta * KD + kk] = __float2bfloat16_rn(cq[i].x);
-        s.q[tb2 * KD + kk] = __float2bfloat16_rn(cq[i].y);
-        s.k[ta * KD + kk] = __float2bfloat16_rn(cp[i].x + cn[i].x);
-        s.k[tb2 * KD + kk] = __float2bfloat16_rn(cp[i].y + cn[i].y);
+        dGv[i] = qv[i] * cq[i] + kv[i] * (cp[i] - cn[i]);
+        s.q[(t0 + i) * KD + kk] = __float2bfloat16_rn(cq[i]);
+        s.k[(t0 + i) * KD + kk] = __float2bfloat16_rn(cp[i] + cn[i]);
       }
       __syncthreads();       // dglp complete
-      if (half == 1)         // this thread owns block 3 (.y): the chunk's last row carries the chunk-end terms
-        dGv[15].y += s.dglp[0][kk] + s.dglp[1][kk] +
-                     ex2(s.G[(C - 1) * KD + kk]) * (s.hdh[0][kk] + s.hdh[1][kk] + s.hdh[2][kk] + s.hdh[3][kk]);
+      if (blk == 3)          // the chunk's last row carries the chunk-end terms
+        dGv[15] += s.dglp[0][kk] + s.dglp[1][kk] + s.dglp[2][kk] + s.dglp[3][kk] +
+                   ex2(s.G[(C - 1) * KD + kk]) * s.hdh[kk];
       {
-        float2 run = make_float2(0.f, 0.f);
+        float run = 0.f;
 #pragma unroll
         for (int i = 15; i >= 0; --i) {
-          run.x += dGv[i].x;
-          run.y += dGv[i].y;
+          run += dGv[i];
           dGv[i] = run;
         }
-        s.carry[half][kk] = run.x;
-        s.carry[half + 2][kk] = run.y;
+        s.carry[blk][kk] = run;
       }
       __syncthreads();
       {
-        float addx = 0.f, addy = 0.f;        // totals of the later blocks
+        float add = 0.f;             // totals of the later blocks
 #pragma unroll
-        for (int bb = 1; bb < 4; ++bb) {
-          const float cb = s.carry[bb][kk];
-          if (bb > half) addx += cb;
-          if (bb > half + 2) addy += cb;
-        }
+        for (int bb = 1; bb < 4; ++bb) add += (bb > blk) ? s.carry[bb][kk] : 0.f;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          s.G[(16 * half + i) * KD + kk] = dGv[i].x + addx;
-          s.G[(16 * (half + 2) + i) * KD + kk] = dGv[i].y + addy;
-        }
+        for (int i = 0; i < 16; ++i) s.G[(t0 + i) * KD + kk] = dGv[i] + add;
       }
       umma::fence_before_sync();
       __syncthreads();
-      for (int i = tid; i < C * 16; i += 256) {
+      for (int i = tid; i < C * 16; i += NT) {
         const int r = i >> 4, pc = i & 15;
         if (r < len) {
           const size_t row = (static_cast<size_t>(ci.tok0 + r) * p.H + h) * KD + pc * 8;
@@ -642,7 +668,7 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_tc_kernel(const Mai
           *reinterpret_cast<uint4*>(p.dk + row) = *reinterpret_cast<const uint4*>(&s.k[r * KD + pc * 8]);
         }
       }
-      for (int i = tid; i < C * 32; i += 256) {
+      for (int i = tid; i < C * 32; i += NT) {
         const int r = i >> 5, pc = i & 31;
         if (r < len) {
           const size_t row = (static_cast<size_t>(ci.tok0 + r) * p.H + h) * KD + pc * 4;
@@ -650,6 +676,7 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_bwd_main_tc_kernel(const Mai
         }
       }
     }
+    KDA_DBG_CLOCK(dbg, 14);
     __syncthreads();   // q, k, G, beta, Ad, ... may be overwritten by the next tile
   }
 
@@ -668,7 +695,7 @@ cudaError_t launch_bwd_main_tc(const MainParams& p, int grid, cudaStream_t st) {
     attr_err = cudaFuncSetAttribute(kda_chunk_bwd_main_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   });
   if (attr_err != cudaSuccess) return attr_err;
-  kda_chunk_bwd_main_tc_kernel<<<grid, 256, smem, st>>>(p);
+  kda_chunk_bwd_main_tc_kernel<<<grid, NT, smem, st>>>(p);
   return cudaGetLastError();
 }
 
