@@ -266,9 +266,15 @@ def main():
     e2e = None
     if not args.no_e2e:
         out_host = None
+        pipelined = w.backward and cu is None and args.workload != "decode"
 
         def e2e_step():
             nonlocal out_host
+            if pipelined:
+                # public host-resident API: batch slices pipelined over copy-in / compute / copy-out streams
+                from kda_b200.host import chunk_kda_fwd_bwd_host
+                out_host = chunk_kda_fwd_bwd_host(pinned, out_host)
+                return
             x = {n: pinned[n].to(dev, non_blocking=True) for n in names}
             outs = step(x)
             outs = [t for t in outs if t is not None]
@@ -286,9 +292,10 @@ def main():
         barrier()
         ms_e2e = maxms(e0.elapsed_time(e1)) / n_e2e
         h2d = sum(pinned[n].numel() * pinned[n].element_size() for n in names)
-        d2h = sum(t.numel() * t.element_size() for t in out_host)
+        d2h = sum(t.numel() * t.element_size() for t in (out_host.values() if isinstance(out_host, dict) else out_host))
         e2e = {"value": world * tokens / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
-               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": n_e2e}
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": n_e2e,
+               "api": "kda_b200.host.chunk_kda_fwd_bwd_host (batch slices pipelined over 3 streams)" if pipelined else "kda_b200.chunk_kda"}
 
     if rank != 0:
         if world > 1:
