@@ -52,7 +52,7 @@ KERNEL_WORK = {
     "scan": (6 * K_ * V_ + 2 * C_ * V_, 4 * _TK + _TT + 8 + 2 * V_ + _VK + _TK),
     "bwd_scan": (6 * K_ * V_ + 2 * C_ * V_, 3 * _TK + _TT + 8 + 2 * V_ + _VK + _TK),
     "bwd_main": (6 * K_ * V_ + 12 * C_ * K_ + 6 * C_ * V_ + 4 * C_ * C_,
-                 _IN + 2 * V_ + 2 * _TT + 2 * _VK + 2 * _TK + (2 * K_ + 2 * K_ + 2 * V_ + 4 * K_ + 4)),
+                 _IN + 2 * V_ + 2 * _TT + 2 * _VK + 2 * _TK + (2 * K_ + 2 * K_ + 2 * V_ + 4 * K_ + 4)),   # = 4,616 B
 }
 
 
