@@ -393,6 +393,11 @@ extern "C" int kda_chunk_bwd(const kda_chunk_args* args, void* stream) {
   mp.TI = w.TI; mp.RKK = w.RKK; mp.HS = w.HS; mp.VNEWT = w.VNEWT; mp.DH = w.DH; mp.DVNEWT = w.DVNEWT;
   mp.dv = static_cast<__nv_bfloat16*>(a.dv); mp.dq = static_cast<__nv_bfloat16*>(a.dq); mp.dk = static_cast<__nv_bfloat16*>(a.dk);
   mp.dbeta = a.dbeta; mp.dg = a.dg; mp.status = w.status; mp.dbg = g_dbg_clocks;
+  if (make_rows_tmap(&mp.tm_q, q, false, a.tokens, a.H, KD, KD, C, false) || make_rows_tmap(&mp.tm_k, k, false, a.tokens, a.H, KD, KD, C, false) ||
+      make_rows_tmap(&mp.tm_g, a.g, true, a.tokens, a.H, KD, KD, C, false) ||
+      make_rows_tmap(&mp.tm_v, a.v, false, a.tokens, a.H, VD, 64, C, true) ||
+      make_rows_tmap(&mp.tm_do, a.d_o, false, a.tokens, a.H, VD, 64, C, true))
+    return KDA_E_DEVICE;
   mp.N = a.N; mp.H = a.H; mp.scale = a.scale;
   if ((e = launch_bwd_main_tc(mp, main_grid(NTmax, a.H), st)) != cudaSuccess) return static_cast<int>(e);
   prof_mark(prof, KDA_STAGE_BWD_MAIN, st);

@@ -2,6 +2,7 @@
 #pragma once
 
 #include "kda_chunk.cuh"
+#include "kda_tma.cuh"
 
 namespace kda {
 
@@ -17,6 +18,9 @@ struct MainParams {
   long long* dbg;
   int N, H;
   float scale;
+  // tiled-load maps of the [tokens, H, 128] operator tensors (64-token boxes of one head)
+  alignas(64) CUtensorMap tm_q, tm_k, tm_g;   // plain row-major boxes [64][128]
+  alignas(64) CUtensorMap tm_v, tm_do;        // 64-column boxes in the 128-byte-swizzled operand layout
 };
 
 // tcgen05 / TMEM version of the per-chunk backward kernel (kda_chunk_bwd_tc.cu)

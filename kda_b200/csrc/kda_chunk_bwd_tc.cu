@@ -88,7 +88,7 @@ __device__ __forceinline__ unsigned char* sw_piece(unsigned char* tile, int row,
 
 }  // namespace
 
-__global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const MainParams p) {
+__global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __grid_constant__ MainParams p) {
   extern __shared__ unsigned char smem_raw[];
   TcSmem& s = *reinterpret_cast<TcSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -122,29 +122,24 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const Mai
   const uint32_t tb = s.tmem_slot;
   const uint32_t tq = tb + (static_cast<uint32_t>(32 * q4) << 16);     // this warp's lanes
 
-  auto fetch_state = [&](long long idx) {      // thread 0: HS, DH, v_new^T, dv_new^T of tile idx
+  // thread 0: the phase-A operands of tile idx -- state tiles by bulk copy, dO by two tiled loads (64 value columns each)
+  auto fetch_state = [&](long long idx) {
     const size_t tl = static_cast<size_t>(idx);
-    mbar_expect_tx(&s.barS, 2 * TILE_VK + 2 * TILE_VT);
+    const int cc = static_cast<int>(idx / p.H), hh = static_cast<int>(idx % p.H);
+    const ChunkInfo cn = chunk_info(p.seq_chunk_off, p.chunk_seq, p.cu, cc);
+    mbar_expect_tx(&s.barS, 2 * TILE_VK + 2 * TILE_VT + TILE_TK);
     bulk_g2s(s.HS, p.HS + tl * TILE_VK, TILE_VK, &s.barS);
     bulk_g2s(s.DH, p.DH + tl * TILE_VK, TILE_VK, &s.barS);
     bulk_g2s(s.VN, p.VNEWT + tl * TILE_VT, TILE_VT, &s.barS);
     bulk_g2s(s.DVN, p.DVNEWT + tl * TILE_VT, TILE_VT, &s.barS);
+    tma_load_rows(s.dO, &p.tm_do, 0, hh, static_cast<int>(cn.tok0), &s.barS);
+    tma_load_rows(s.dO + 8192, &p.tm_do, 64, hh, static_cast<int>(cn.tok0), &s.barS);
   };
-  auto fetch_do = [&](long long idx) {          // all threads: dO rows of tile idx as two K-major sub-tiles
-    const int cc = static_cast<int>(idx / p.H), hh = static_cast<int>(idx % p.H);
-    const ChunkInfo cn = chunk_info(p.seq_chunk_off, p.chunk_seq, p.cu, cc);
-    for (int i = tid; i < C * 16; i += NT) {
-      const int r = i >> 4, pc = i & 15;
-      const bool ok = r < cn.len;
-      const size_t row = (static_cast<size_t>(cn.tok0 + (ok ? r : 0)) * p.H + hh) * KD + pc * 8;
-      cp_async16(sw_piece(s.dO + (pc >> 3) * 8192, r, pc & 7), p.d_o + row, ok);
-    }
-    cp_async_commit();
+  // rows of a partial chunk beyond its length hold the next sequence's tokens after a tiled load: clear them
+  auto zero_rows_sw = [&](unsigned char* tile, int len) {          // [64][64] bf16 sub-tile, 128-byte rows
+    for (int i = len * 8 + tid; i < C * 8; i += NT) *reinterpret_cast<uint4*>(tile + i * 16) = make_uint4(0u, 0u, 0u, 0u);
   };
-  if (static_cast<long long>(blockIdx.x) < total_tiles) {
-    if (tid == 0) fetch_state(blockIdx.x);
-    fetch_do(blockIdx.x);
-  }
+  if (static_cast<long long>(blockIdx.x) < total_tiles && tid == 0) fetch_state(blockIdx.x);
 
   uint32_t mph = 0;      // phase counter of barM
   bool alive = true;
@@ -160,32 +155,27 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const Mai
     KDA_DBG_CLOCK(dbg, 0);
     // ---- second load group: Tm, raw kk (bulk); q, k, g, v, beta (async copies); lands behind phase A ------------
     if (tid == 0) {
-      mbar_expect_tx(&s.barB, 2 * TILE_TT);
+      mbar_expect_tx(&s.barB, 2 * TILE_TT + 3 * TILE_TK + C * KD * 4);
       bulk_g2s(s.TI, p.TI + tile * TILE_TT, TILE_TT, &s.barB);
       bulk_g2s(s.RKK, p.RKK + tile * TILE_TT, TILE_TT, &s.barB);
-    }
-    for (int i = tid; i < C * 16; i += NT) {
-      const int r = i >> 4, pc = i & 15;
-      const bool ok = r < len;
-      const size_t row = (static_cast<size_t>(ci.tok0 + (ok ? r : 0)) * p.H + h) * KD + pc * 8;
-      cp_async16(&s.q[r * KD + pc * 8], p.q + row, ok);
-      cp_async16(&s.k[r * KD + pc * 8], p.k + row, ok);
-      cp_async16(sw_piece(s.V + (pc >> 3) * 8192, r, pc & 7), p.v + row, ok);
-    }
-    for (int i = tid; i < C * 32; i += NT) {
-      const int r = i >> 5, pc = i & 31;
-      const bool ok = r < len;
-      const size_t row = (static_cast<size_t>(ci.tok0 + (ok ? r : 0)) * p.H + h) * KD + pc * 4;
-      cp_async16(&s.G[r * KD + pc * 4], p.g + row, ok);
+      const int tk = static_cast<int>(ci.tok0);
+      tma_load_rows(s.q, &p.tm_q, 0, h, tk, &s.barB);
+      tma_load_rows(s.k, &p.tm_k, 0, h, tk, &s.barB);
+      tma_load_rows(s.G, &p.tm_g, 0, h, tk, &s.barB);
+      tma_load_rows(s.V, &p.tm_v, 0, h, tk, &s.barB);
+      tma_load_rows(s.V + 8192, &p.tm_v, 64, h, tk, &s.barB);
     }
     if (tid < C) cp_async4(&s.beta[tid], p.beta + static_cast<size_t>(ci.tok0 + (tid < len ? tid : 0)) * p.H + h, tid < len);
     cp_async_commit();
-    cp_async_wait<1>();          // this tile's dO (issued one tile ago, or in the prologue)
-    fence_proxy_async();         // async-copy writes -> tensor-core (async proxy) reads
-    __syncthreads();
     if (!mbar_wait(&s.barS, it & 1)) {
       if (tid == 0) atomicOr(p.status, 32u);
       alive = false;
+    }
+    if (len < C) {                 // uniform over the CTA
+      zero_rows_sw(s.dO, len);
+      zero_rows_sw(s.dO + 8192, len);
+      fence_proxy_async();
+      __syncthreads();
     }
     umma::fence_after_sync();
 
@@ -214,6 +204,21 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const Mai
     KDA_DBG_CLOCK(dbg, 2);
     // ---- meanwhile: the second load group, G = cumsum(g) log2(e), sum_v h dh' ------------------------------------
     cp_async_wait<0>();
+    if (alive && !mbar_wait(&s.barB, it & 1)) {
+      if (tid == 0) atomicOr(p.status, 32u);
+      alive = false;
+    }
+    if (len < C) {
+      for (int i = len * 16 + tid; i < C * 16; i += NT) {
+        reinterpret_cast<uint4*>(s.q)[i] = make_uint4(0u, 0u, 0u, 0u);
+        reinterpret_cast<uint4*>(s.k)[i] = make_uint4(0u, 0u, 0u, 0u);
+        reinterpret_cast<uint4*>(s.G)[2 * i] = make_uint4(0u, 0u, 0u, 0u);
+        reinterpret_cast<uint4*>(s.G)[2 * i + 1] = make_uint4(0u, 0u, 0u, 0u);
+      }
+      zero_rows_sw(s.V, len);
+      zero_rows_sw(s.V + 8192, len);
+      fence_proxy_async();
+    }
     __syncthreads();
     {
       const int col = tid & 127, qr = tid >> 7;        // four quarters of 16 rows
@@ -246,10 +251,6 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const Mai
       }
       s.hdh_part[vq][2 * kp] = ax;
       s.hdh_part[vq][2 * kp + 1] = ay;
-    }
-    if (alive && !mbar_wait(&s.barB, it & 1)) {
-      if (tid == 0) atomicOr(p.status, 32u);
-      alive = false;
     }
     if (alive && !mbar_wait(&s.barM, mph & 1)) {
       if (tid == 0) atomicOr(p.status, 64u);
@@ -559,10 +560,7 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const Mai
     umma::fence_after_sync();
     KDA_DBG_CLOCK(dbg, 10);
     // every shared-memory operand tile is dead now: fetch the next tile's phase-A operands behind phase D
-    if (next_idx < total_tiles) {
-      if (tid == 0) fetch_state(next_idx);
-      fetch_do(next_idx);
-    }
+    if (next_idx < total_tiles && tid == 0) fetch_state(next_idx);
     if (tid < len)
       p.dbeta[static_cast<size_t>(ci.tok0 + tid) * p.H + h] = s.dbp[0][tid] + s.dbp[1][tid] + s.dbp[2][tid] + s.dbp[3][tid] +
                                                              s.dbp[4][tid] + s.dbp[5][tid] + s.dbp[6][tid] + s.dbp[7][tid];
