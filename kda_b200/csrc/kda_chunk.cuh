@@ -4,7 +4,8 @@
 // global memory and already holds the XOR-swizzled image the consumer wants in shared memory, so a
 // consumer fetches a tile with one 1-D bulk (TMA) copy and reads it with ldmatrix without bank
 // conflicts.  Tile index = chunk * H + head.  Formats (bf16 unless noted):
-//   W, QG, KG : [64 tokens][128 k]   256-byte rows      w = Tm (beta k Gam), qg = scale q Gam, kg = k exp(G_last - G)
+//   W, QG, KG : [64 tokens][128 k]   two [64 t][64 k] sub-tiles of 128-byte rows (tk_off)
+//                                    w = Tm (beta k Gam), qg = scale q Gam, kg = k exp(G_last - G)
 //   AQK, TI, RKK : [64 t][64 j]      128-byte rows      Aqk (lower incl. diagonal), Tm = (I + Akk)^-1, raw <k_t D, k_j>
 //   UT        : [128 v][64 t]        128-byte rows      u^T,  u = Tm (beta v)
 //   GL        : fp32 [128]                              Gam_last = exp(G_last)
@@ -95,6 +96,9 @@ __device__ __forceinline__ ChunkInfo chunk_info(const int* seq_chunk_off, const 
 
 // byte offset of element (v, k) of a [128 v][128 k] state tile: span k/64, then the 128-byte-row swizzle
 __device__ __forceinline__ uint32_t vk_off(int v, int k) { return (static_cast<uint32_t>(k >> 6) << 14) + swz<128>(v, k & 63); }
+
+// byte offset of element (t, k) of a [64 t][128 k] tile: sub-tile k/64, then the 128-byte-row swizzle
+__device__ __forceinline__ uint32_t tk_off(int t, int k) { return (static_cast<uint32_t>(k >> 6) << 13) + swz<128>(t, k & 63); }
 
 // ---- development aid: phase clocks of CTA (0,0), written when a buffer has been registered --------------
 extern long long* g_dbg_clocks;   // device pointer or NULL

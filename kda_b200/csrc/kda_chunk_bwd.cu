@@ -203,7 +203,7 @@ __global__ void __launch_bounds__(RS_THREADS, 1) kda_chunk_bwd_scan_kernel(const
 #pragma unroll
       for (int np = 0; np < 4; ++np) {
         uint32_t b[4];
-        ldsm_x4(b, kbase + swz<256>(np * 16 + brow, ks * 16 + bcol));       // B[k=kk][n=j] = kg[j][kk]
+        ldsm_x4(b, kbase + tk_off(np * 16 + brow, ks * 16 + bcol));       // B[k=kk][n=j] = kg[j][kk]
         mma16816(dvn[2 * np], dhA[ks], b[0], b[1]);
         mma16816(dvn[2 * np + 1], dhA[ks], b[2], b[3]);
       }
@@ -241,10 +241,10 @@ __global__ void __launch_bounds__(RS_THREADS, 1) kda_chunk_bwd_scan_kernel(const
 #pragma unroll
       for (int np = 0; np < 8; ++np) {
         uint32_t b[4];
-        ldsm_x4_t(b, qbase + swz<256>(ks * 16 + trow, np * 16 + tcol));     // B[k=t][n=kk] = qg[t][kk]
+        ldsm_x4_t(b, qbase + tk_off(ks * 16 + trow, np * 16 + tcol));     // B[k=t][n=kk] = qg[t][kk]
         mma16816(dhT[2 * np], doA[ks], b[0], b[1]);
         mma16816(dhT[2 * np + 1], doA[ks], b[2], b[3]);
-        ldsm_x4_t(b, wbase + swz<256>(ks * 16 + trow, np * 16 + tcol));     // B[k=j][n=kk] = w[j][kk]
+        ldsm_x4_t(b, wbase + tk_off(ks * 16 + trow, np * 16 + tcol));     // B[k=j][n=kk] = w[j][kk]
         mma16816(dhT[2 * np], dneg, b[0], b[1]);
         mma16816(dhT[2 * np + 1], dneg, b[2], b[3]);
       }

@@ -353,7 +353,7 @@ __global__ void __launch_bounds__(256, 2) kda_chunk_prepare_kernel(const PrepPar
         ok[e] = pack_bf16(kk.x * ex2(l8[2 * e] - g8[2 * e]), kk.y * ex2(l8[2 * e + 1] - g8[2 * e + 1]));
         og[e] = pack_bf16(kk.x * e0, kk.y * e1);
       }
-      const uint32_t off = swz<256>(r, pc * 8);
+      const uint32_t off = tk_off(r, pc * 8);
       *reinterpret_cast<uint4*>(gQG + off) = make_uint4(oq[0], oq[1], oq[2], oq[3]);
       *reinterpret_cast<uint4*>(gKG + off) = make_uint4(ok[0], ok[1], ok[2], ok[3]);
       // k * Gam takes the place of this thread's own q piece (no other thread reads it in this phase)
@@ -514,8 +514,8 @@ __global__ void __launch_bounds__(256, 2) kda_chunk_prepare_kernel(const PrepPar
       for (int n = 0; n < 8; ++n) {
         const int col = nh * 64 + n * 8 + tig * 2;
         if (which) {   // W tile [t][k]
-          *reinterpret_cast<uint32_t*>(stW + swz<256>(ta, col)) = pack_bf16(acc[n][0], acc[n][1]);
-          *reinterpret_cast<uint32_t*>(stW + swz<256>(tb, col)) = pack_bf16(acc[n][2], acc[n][3]);
+          *reinterpret_cast<uint32_t*>(stW + tk_off(ta, col)) = pack_bf16(acc[n][0], acc[n][1]);
+          *reinterpret_cast<uint32_t*>(stW + tk_off(tb, col)) = pack_bf16(acc[n][2], acc[n][3]);
         } else {       // UT tile [v][t]
           *reinterpret_cast<__nv_bfloat16*>(stUT + swz<128>(col, ta)) = __float2bfloat16_rn(acc[n][0]);
           *reinterpret_cast<__nv_bfloat16*>(stUT + swz<128>(col + 1, ta)) = __float2bfloat16_rn(acc[n][1]);
@@ -682,10 +682,10 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1) kda_chunk_scan_kernel(const S
 #pragma unroll
       for (int np = 0; np < 4; ++np) {
         uint32_t b[4];
-        ldsm_x4(b, wbase + swz<256>(np * 16 + brow, ks * 16 + bcol));
+        ldsm_x4(b, wbase + tk_off(np * 16 + brow, ks * 16 + bcol));
         mma16816(vn[2 * np], hneg, b[0], b[1]);
         mma16816(vn[2 * np + 1], hneg, b[2], b[3]);
-        ldsm_x4(b, qbase + swz<256>(np * 16 + brow, ks * 16 + bcol));
+        ldsm_x4(b, qbase + tk_off(np * 16 + brow, ks * 16 + bcol));
         mma16816(oT[2 * np], hA[ks], b[0], b[1]);
         mma16816(oT[2 * np + 1], hA[ks], b[2], b[3]);
       }
@@ -735,7 +735,7 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1) kda_chunk_scan_kernel(const S
 #pragma unroll
       for (int np = 0; np < 8; ++np) {
         uint32_t b[4];
-        ldsm_x4_t(b, kbase + swz<256>(ks * 16 + trow, np * 16 + tcol));
+        ldsm_x4_t(b, kbase + tk_off(ks * 16 + trow, np * 16 + tcol));
         mma16816(hT[2 * np], vA[ks], b[0], b[1]);
         mma16816(hT[2 * np + 1], vA[ks], b[2], b[3]);
       }
