@@ -4,13 +4,13 @@
 //                            so that variable-length calls need no device->host copy.
 //  kda_chunk_prepare_kernel  one CTA per (chunk, head): everything that does not depend on the state:
 //                            G = cumsum(g), Aqk, Akk, Tm = (I+Akk)^-1, w, u, qg, kg  -> tiles in the workspace.
-//  kda_chunk_scan_kernel     one CTA per (sequence, head): walks the chunks in order with the fp32 state in
-//                            registers (transposed, one warp per 16 value columns, all 128 key columns),
-//                            operand tiles streamed through a 3-stage TMA bulk-copy pipeline issued by
-//                            one lane.   v_new = u - w h;  o = qg h + Aqk v_new;  h = Diag(Gam_last) h + kg^T v_new.
+//  kda_chunk_scan_tc_kernel  (kda_chunk_scan_tc.cu) one CTA per (sequence, head): walks the chunks in order with
+//                            the fp32 state in tensor memory, products on tcgen05.
+//                            v_new = u - w h;  o = qg h + Aqk v_new;  h = Diag(Gam_last) h + kg^T v_new.
 #include <mutex>
 
 #include "kda_chunk.cuh"
+#include "kda_scan.cuh"
 
 namespace kda {
 
@@ -536,251 +536,6 @@ __global__ void __launch_bounds__(256, 2) kda_chunk_prepare_kernel(const PrepPar
   }
 }
 
-// =================================================================================================
-// state scan (forward)
-// =================================================================================================
-constexpr int SCAN_STAGES = 3;
-constexpr int SCAN_CWARPS = 8;                       // compute warps: 16 value columns each
-constexpr int SCAN_THREADS = SCAN_CWARPS * 32;
-
-struct ScanStage {
-  unsigned char W[TILE_TK], QG[TILE_TK], KG[TILE_TK], AQK[TILE_TT], UT[TILE_VT];
-  float GL[KD];
-};
-constexpr unsigned SCAN_STAGE_TX = 3 * TILE_TK + TILE_TT + TILE_VT + TILE_GL;
-
-struct ScanSmem {
-  ScanStage st[SCAN_STAGES];
-  uint64_t full[SCAN_STAGES], empty[SCAN_STAGES];
-};
-
-struct ScanParams {
-  const int* cu;
-  const int *seq_chunk_off, *chunk_seq;
-  const unsigned char *W, *UT, *KG, *QG, *AQK, *GL;
-  unsigned char *HS, *VNEWT;    // NULL unless saving for backward
-  const float* h0;
-  float* ht;
-  __nv_bfloat16* o;
-  unsigned* status;
-  int N, H;
-};
-
-__global__ void __launch_bounds__(SCAN_THREADS, 1) kda_chunk_scan_kernel(const ScanParams p) {
-  extern __shared__ __align__(128) unsigned char smem_raw[];
-  ScanSmem& s = *reinterpret_cast<ScanSmem*>(smem_raw);
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gid = lane >> 2, tig = lane & 3;
-  const int seq = blockIdx.x / p.H, h = blockIdx.x % p.H;
-  const int c_begin = p.seq_chunk_off[seq], c_end = p.seq_chunk_off[seq + 1];
-  const int nchunks = c_end - c_begin;
-
-  if (tid == 0) {
-    for (int i = 0; i < SCAN_STAGES; ++i) {
-      mbar_init(&s.full[i], 1);
-      mbar_init(&s.empty[i], SCAN_CWARPS);
-    }
-    fence_mbar_init();
-  }
-  __syncthreads();
-
-  // Warp 0's lane 0 doubles as the producer: it streams the tiles of chunk i+2 while chunk i is computed.
-  auto issue = [&](int i) -> bool {
-    const int stg = i % SCAN_STAGES;
-    if (i >= SCAN_STAGES) {
-      if (!mbar_wait(&s.empty[stg], ((i / SCAN_STAGES) & 1) ^ 1)) return false;
-    }
-    const size_t tile = static_cast<size_t>(c_begin + i) * p.H + h;
-    ScanStage& d = s.st[stg];
-    mbar_expect_tx(&s.full[stg], SCAN_STAGE_TX);
-    bulk_g2s(d.W, p.W + tile * TILE_TK, TILE_TK, &s.full[stg]);
-    bulk_g2s(d.QG, p.QG + tile * TILE_TK, TILE_TK, &s.full[stg]);
-    bulk_g2s(d.KG, p.KG + tile * TILE_TK, TILE_TK, &s.full[stg]);
-    bulk_g2s(d.AQK, p.AQK + tile * TILE_TT, TILE_TT, &s.full[stg]);
-    bulk_g2s(d.UT, p.UT + tile * TILE_VT, TILE_VT, &s.full[stg]);
-    bulk_g2s(d.GL, p.GL + tile * TILE_GL, TILE_GL, &s.full[stg]);
-    return true;
-  };
-  if (tid == 0) {
-    for (int i = 0; i < SCAN_STAGES - 1 && i < nchunks; ++i) issue(i);
-  }
-
-  // --------------------------------- compute warps ------------------------------------------------
-  const int v0 = warp * 16;
-  float hT[16][4];   // transposed state: rows v0+gid (+8), columns nt*8 + 2 tig (+1)
-  {
-    const size_t sb = (static_cast<size_t>(seq) * p.H + h) * KD * VD;
-#pragma unroll
-    for (int nt = 0; nt < 16; ++nt) {
-      const int kk = nt * 8 + tig * 2;
-      if (p.h0) {
-        hT[nt][0] = __ldg(p.h0 + sb + static_cast<size_t>(kk) * VD + v0 + gid);
-        hT[nt][1] = __ldg(p.h0 + sb + static_cast<size_t>(kk + 1) * VD + v0 + gid);
-        hT[nt][2] = __ldg(p.h0 + sb + static_cast<size_t>(kk) * VD + v0 + gid + 8);
-        hT[nt][3] = __ldg(p.h0 + sb + static_cast<size_t>(kk + 1) * VD + v0 + gid + 8);
-      } else {
-        hT[nt][0] = hT[nt][1] = hT[nt][2] = hT[nt][3] = 0.f;
-      }
-    }
-  }
-
-  bool failed = false;
-  for (int i = 0; i < nchunks; ++i) {
-    const int stg = i % SCAN_STAGES;
-    const int c = c_begin + i;
-    if (tid == 0 && i + SCAN_STAGES - 1 < nchunks) {
-      if (!issue(i + SCAN_STAGES - 1)) atomicOr(p.status, 1u);   // consumers then time out on `full` and leave too
-    }
-    __syncwarp();
-    if (!mbar_wait(&s.full[stg], (i / SCAN_STAGES) & 1)) {
-      failed = true;
-      break;
-    }
-    const ScanStage& d = s.st[stg];
-    const ChunkInfo ci = chunk_info(p.seq_chunk_off, p.chunk_seq, p.cu, c);
-    const size_t tile = static_cast<size_t>(c) * p.H + h;
-
-    // bf16 copy of the state as A fragments (and the saved chunk-start state)
-    uint32_t hA[8][4];
-#pragma unroll
-    for (int ks = 0; ks < 8; ++ks) {
-      hA[ks][0] = pack_bf16(hT[2 * ks][0], hT[2 * ks][1]);
-      hA[ks][1] = pack_bf16(hT[2 * ks][2], hT[2 * ks][3]);
-      hA[ks][2] = pack_bf16(hT[2 * ks + 1][0], hT[2 * ks + 1][1]);
-      hA[ks][3] = pack_bf16(hT[2 * ks + 1][2], hT[2 * ks + 1][3]);
-    }
-    if (p.HS) {
-      unsigned char* g = p.HS + tile * TILE_VK;
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
-        const int kk = ks * 16 + tig * 2;
-        *reinterpret_cast<uint32_t*>(g + vk_off(v0 + gid, kk)) = hA[ks][0];
-        *reinterpret_cast<uint32_t*>(g + vk_off(v0 + gid + 8, kk)) = hA[ks][1];
-        *reinterpret_cast<uint32_t*>(g + vk_off(v0 + gid, kk + 8)) = hA[ks][2];
-        *reinterpret_cast<uint32_t*>(g + vk_off(v0 + gid + 8, kk + 8)) = hA[ks][3];
-      }
-    }
-
-    // v_new^T = u^T - h^T w^T        (rows: value columns of this warp; columns: tokens)
-    float vn[8][4];
-#pragma unroll
-    for (int nt = 0; nt < 8; ++nt) {
-      const int t = nt * 8 + tig * 2;
-      const float2 ua = unpack_bf16(*reinterpret_cast<const uint32_t*>(d.UT + swz<128>(v0 + gid, t)));
-      const float2 ub = unpack_bf16(*reinterpret_cast<const uint32_t*>(d.UT + swz<128>(v0 + gid + 8, t)));
-      vn[nt][0] = ua.x; vn[nt][1] = ua.y; vn[nt][2] = ub.x; vn[nt][3] = ub.y;
-    }
-    float oT[8][4];
-#pragma unroll
-    for (int nt = 0; nt < 8; ++nt) oT[nt][0] = oT[nt][1] = oT[nt][2] = oT[nt][3] = 0.f;
-    const uint32_t wbase = smem_u32(d.W), qbase = smem_u32(d.QG);
-    const int brow = (lane & 7) + ((lane >> 4) << 3), bcol = ((lane >> 3) & 1) << 3;   // non-transposed B tiles
-#pragma unroll
-    for (int ks = 0; ks < 8; ++ks) {
-      uint32_t hneg[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e) hneg[e] = hA[ks][e] ^ 0x80008000u;
-#pragma unroll
-      for (int np = 0; np < 4; ++np) {
-        uint32_t b[4];
-        ldsm_x4(b, wbase + tk_off(np * 16 + brow, ks * 16 + bcol));
-        mma16816(vn[2 * np], hneg, b[0], b[1]);
-        mma16816(vn[2 * np + 1], hneg, b[2], b[3]);
-        ldsm_x4(b, qbase + tk_off(np * 16 + brow, ks * 16 + bcol));
-        mma16816(oT[2 * np], hA[ks], b[0], b[1]);
-        mma16816(oT[2 * np + 1], hA[ks], b[2], b[3]);
-      }
-    }
-    // v_new as A fragments (and the saved copy)
-    uint32_t vA[4][4];
-#pragma unroll
-    for (int ks = 0; ks < 4; ++ks) {
-      vA[ks][0] = pack_bf16(vn[2 * ks][0], vn[2 * ks][1]);
-      vA[ks][1] = pack_bf16(vn[2 * ks][2], vn[2 * ks][3]);
-      vA[ks][2] = pack_bf16(vn[2 * ks + 1][0], vn[2 * ks + 1][1]);
-      vA[ks][3] = pack_bf16(vn[2 * ks + 1][2], vn[2 * ks + 1][3]);
-    }
-    if (p.VNEWT) {
-      unsigned char* g = p.VNEWT + tile * TILE_VT;
-#pragma unroll
-      for (int ks = 0; ks < 4; ++ks) {
-        const int t = ks * 16 + tig * 2;
-        *reinterpret_cast<uint32_t*>(g + swz<128>(v0 + gid, t)) = vA[ks][0];
-        *reinterpret_cast<uint32_t*>(g + swz<128>(v0 + gid + 8, t)) = vA[ks][1];
-        *reinterpret_cast<uint32_t*>(g + swz<128>(v0 + gid, t + 8)) = vA[ks][2];
-        *reinterpret_cast<uint32_t*>(g + swz<128>(v0 + gid + 8, t + 8)) = vA[ks][3];
-      }
-    }
-    // o^T += v_new^T Aqk^T
-    const uint32_t abase = smem_u32(d.AQK);
-#pragma unroll
-    for (int ks = 0; ks < 4; ++ks) {
-#pragma unroll
-      for (int np = 0; np < 4; ++np) {
-        uint32_t b[4];
-        ldsm_x4(b, abase + swz<128>(np * 16 + brow, ks * 16 + bcol));
-        mma16816(oT[2 * np], vA[ks], b[0], b[1]);
-        mma16816(oT[2 * np + 1], vA[ks], b[2], b[3]);
-      }
-    }
-    // h^T = h^T Diag(Gam_last) + v_new^T kg
-#pragma unroll
-    for (int nt = 0; nt < 16; ++nt) {
-      const float2 gl = *reinterpret_cast<const float2*>(&d.GL[nt * 8 + tig * 2]);
-      hT[nt][0] *= gl.x; hT[nt][1] *= gl.y; hT[nt][2] *= gl.x; hT[nt][3] *= gl.y;
-    }
-    const uint32_t kbase = smem_u32(d.KG);
-    const int trow = (lane & 7) + (((lane >> 3) & 1) << 3), tcol = (lane >> 4) << 3;   // transposed B tiles
-#pragma unroll
-    for (int ks = 0; ks < 4; ++ks) {
-#pragma unroll
-      for (int np = 0; np < 8; ++np) {
-        uint32_t b[4];
-        ldsm_x4_t(b, kbase + tk_off(ks * 16 + trow, np * 16 + tcol));
-        mma16816(hT[2 * np], vA[ks], b[0], b[1]);
-        mma16816(hT[2 * np + 1], vA[ks], b[2], b[3]);
-      }
-    }
-    // o: stage this warp's [64 t][16 v] slab in its own (now dead) rows of the UT tile, then 16-byte stores
-    {
-      __syncwarp();
-      __nv_bfloat16* slab = reinterpret_cast<__nv_bfloat16*>(const_cast<unsigned char*>(d.UT) + static_cast<size_t>(v0) * (C * 2));
-#pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
-        const int t = nt * 8 + tig * 2;
-        slab[t * 16 + gid] = __float2bfloat16_rn(oT[nt][0]);
-        slab[(t + 1) * 16 + gid] = __float2bfloat16_rn(oT[nt][1]);
-        slab[t * 16 + gid + 8] = __float2bfloat16_rn(oT[nt][2]);
-        slab[(t + 1) * 16 + gid + 8] = __float2bfloat16_rn(oT[nt][3]);
-      }
-      __syncwarp();
-#pragma unroll
-      for (int it = 0; it < 4; ++it) {
-        const int pc = lane + 32 * it, t = pc >> 1, half = pc & 1;
-        if (t < ci.len) {
-          const uint4 val = *reinterpret_cast<const uint4*>(&slab[t * 16 + half * 8]);
-          *reinterpret_cast<uint4*>(p.o + (static_cast<size_t>(ci.tok0 + t) * p.H + h) * VD + v0 + half * 8) = val;
-        }
-      }
-      __syncwarp();
-    }
-    fence_proxy_async();   // this warp's generic-proxy writes to the stage precede the next bulk copy into it
-    if (lane == 0) mbar_arrive(&s.empty[stg]);
-  }
-  if (failed && lane == 0) atomicOr(p.status, 2u);
-
-  if (p.ht && !failed) {
-    const size_t sb = (static_cast<size_t>(seq) * p.H + h) * KD * VD;
-#pragma unroll
-    for (int nt = 0; nt < 16; ++nt) {
-      const int kk = nt * 8 + tig * 2;
-      p.ht[sb + static_cast<size_t>(kk) * VD + v0 + gid] = hT[nt][0];
-      p.ht[sb + static_cast<size_t>(kk + 1) * VD + v0 + gid] = hT[nt][1];
-      p.ht[sb + static_cast<size_t>(kk) * VD + v0 + gid + 8] = hT[nt][2];
-      p.ht[sb + static_cast<size_t>(kk + 1) * VD + v0 + gid + 8] = hT[nt][3];
-    }
-  }
-}
-
 static std::once_flag g_attr_once;
 static cudaError_t g_attr_err = cudaSuccess;
 
@@ -788,9 +543,6 @@ static cudaError_t set_attrs() {
   std::call_once(g_attr_once, [] {
     cudaError_t e = cudaFuncSetAttribute(kda_chunk_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(sizeof(PrepSmem)));
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(kda_chunk_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               static_cast<int>(sizeof(ScanSmem)));
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(kda_chunk_prepare_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
                                cudaSharedmemCarveoutMaxShared);
@@ -877,8 +629,7 @@ extern "C" int kda_chunk_fwd(const kda_chunk_args* args, void* stream) {
   sp.HS = save ? w.HS : nullptr; sp.VNEWT = save ? w.VNEWT : nullptr;
   sp.h0 = a.h0; sp.ht = a.ht; sp.o = static_cast<__nv_bfloat16*>(a.o); sp.status = w.status;
   sp.N = a.N; sp.H = a.H;
-  kda_chunk_scan_kernel<<<a.N * a.H, SCAN_THREADS, sizeof(ScanSmem), st>>>(sp);
-  if ((e = cudaGetLastError()) != cudaSuccess) return static_cast<int>(e);
+  if ((e = launch_scan_tc(sp, a.N * a.H, st)) != cudaSuccess) return static_cast<int>(e);
   prof_mark(prof, KDA_STAGE_SCAN, st);
   return KDA_OK;
 }
