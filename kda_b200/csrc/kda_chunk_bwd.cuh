@@ -23,6 +23,21 @@ struct MainParams {
   alignas(64) CUtensorMap tm_v, tm_do;        // 64-column boxes in the 128-byte-swizzled operand layout
 };
 
+struct RScanParams {
+  const int* cu;
+  const int *seq_chunk_off, *chunk_seq;
+  const unsigned char *W, *KG, *QG, *AQK, *GL;
+  unsigned char *DH, *DVNEWT;
+  const __nv_bfloat16* d_o;
+  const float* d_ht;
+  float* dh0;
+  unsigned* status;
+  int N, H;
+  alignas(64) CUtensorMap tm_do;   // 64-column boxes of dO in the 128-byte-swizzled operand layout
+};
+
+cudaError_t launch_bwd_scan_tc(const RScanParams& p, int blocks, cudaStream_t st);
+
 // tcgen05 / TMEM version of the per-chunk backward kernel (kda_chunk_bwd_tc.cu)
 cudaError_t launch_bwd_main_tc(const MainParams& p, int grid, cudaStream_t st);
 
