@@ -33,19 +33,19 @@ constexpr int NT = 512;             // threads per CTA: 16 warps = 4 TMEM lane q
 
 struct TcSmem {
   // ---- SW128 operand tiles; every offset is a multiple of 1024 -------------------------------------------------
-  unsigned char HS[TILE_VK];    // A.  later: KG = k Gam [64 j][128 kk] (16K) | DWT = dw^T [128 kk][64 t] (16K);  C: kL span 0 (12K)
+  unsigned char HS[TILE_VK];    // A.  later: KG = k Gam [64 j][128 kk] (16K) | DWT = dw^T [128 kk][64 t] (16K);  C: kL span 0 | kL span 1 (12K each)
   unsigned char DH[TILE_VK];    // A.  later: DT (8K) | X (8K) | DAQ (8K) | DAK (8K)
   unsigned char VN[TILE_VT];    // A.  C: kR span 0 (12K)
   unsigned char DVN[TILE_VT];   // A, B1.  C: qL span 0 (12K)
   unsigned char dO[TILE_TK];    // A (two [64 t][64 v] sub-tiles).  C: kR span 1
-  unsigned char V[TILE_TK];     // B1 (two [64 j][64 v] sub-tiles).  C: qL span 1
-  unsigned char TI[TILE_TT];    // B1..B3.  C (with RKK): kL span 1 (12K)
+  unsigned char V[TILE_TK];     // B1 (two [64 j][64 v] sub-tiles).  C: qL span 1.  D: dq staging [64][128]
+  unsigned char TI[TILE_TT];    // B1..B3.  D (with RKK): dk staging [64][128]
   unsigned char RKK[TILE_TT];   // post-B3
   // ---- plain arrays -----------------------------------------------------------------------------------------------
-  __nv_bfloat16 q[C * KD];      // [64][128]; at the end dq
-  __nv_bfloat16 k[C * KD];      // at the end dk
-  float G[C * KD];              // log2-domain cumsum of g; at the end dg
-  float2 Ad[4][16][16];         // diagonal blocks: (a1, a2) = (scale dAqk, beta dAkk)
+  __nv_bfloat16 q[C * KD];      // [64][128]   (q, k, g of the NEXT tile arrive here during phase D)
+  __nv_bfloat16 k[C * KD];
+  float G[C * KD];              // log2-domain cumsum of g
+  float2 Ad[4][16][17];         // diagonal blocks: (a1, a2) = (scale dAqk, beta dAkk); rows padded against bank conflicts
   float beta[C];
   float hdh[KD];                // sum over v of h dh'
   union {
@@ -56,7 +56,9 @@ struct TcSmem {
     };
   };
   float carry[4][KD];           // block totals of the reverse cumsum
-  uint64_t barS, barB, barM;
+  uint64_t barS, barQ, barB, barM;
+  long long ci_tok0[2];         // first token and length of the chunk of the current / next tile (written by thread 0)
+  int ci_len[2];
   uint32_t tmem_slot;
 };
 static_assert(sizeof(TcSmem) + 1024 <= 227 * 1024, "TcSmem too large");
@@ -107,26 +109,17 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __g
   unsigned char* const sQL0 = s.DVN;
   unsigned char* const sQL1 = s.V;
   unsigned char* const sKL0 = s.HS;
-  unsigned char* const sKL1 = s.TI;
-
-  if (tid == 0) {
-    mbar_init(&s.barS, 1);
-    mbar_init(&s.barB, 1);
-    mbar_init(&s.barM, 1);
-    fence_mbar_init();
-  }
-  if (warp == 0) umma::tmem_alloc(&s.tmem_slot, 512);
-  umma::fence_before_sync();
-  __syncthreads();
-  umma::fence_after_sync();
-  const uint32_t tb = s.tmem_slot;
-  const uint32_t tq = tb + (static_cast<uint32_t>(32 * q4) << 16);     // this warp's lanes
+  unsigned char* const sKL1 = s.HS + SPAN;
+  __nv_bfloat16* const stq = reinterpret_cast<__nv_bfloat16*>(s.V);      // phase D: dq, dk before their coalesced stores
+  __nv_bfloat16* const stk = reinterpret_cast<__nv_bfloat16*>(s.TI);
 
   // thread 0: the phase-A operands of tile idx -- state tiles by bulk copy, dO by two tiled loads (64 value columns each)
-  auto fetch_state = [&](long long idx) {
+  auto fetch_state = [&](long long idx, int slot) {
     const size_t tl = static_cast<size_t>(idx);
     const int cc = static_cast<int>(idx / p.H), hh = static_cast<int>(idx % p.H);
     const ChunkInfo cn = chunk_info(p.seq_chunk_off, p.chunk_seq, p.cu, cc);
+    s.ci_tok0[slot] = cn.tok0;
+    s.ci_len[slot] = cn.len;
     mbar_expect_tx(&s.barS, 2 * TILE_VK + 2 * TILE_VT + TILE_TK);
     bulk_g2s(s.HS, p.HS + tl * TILE_VK, TILE_VK, &s.barS);
     bulk_g2s(s.DH, p.DH + tl * TILE_VK, TILE_VK, &s.barS);
@@ -135,33 +128,98 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __g
     tma_load_rows(s.dO, &p.tm_do, 0, hh, static_cast<int>(cn.tok0), &s.barS);
     tma_load_rows(s.dO + 8192, &p.tm_do, 64, hh, static_cast<int>(cn.tok0), &s.barS);
   };
+  // thread 0: q, k, g of tile idx
+  auto fetch_qkg = [&](long long idx, int slot) {      // after fetch_state(idx, slot)
+    const int hh = static_cast<int>(idx % p.H);
+    const int tk = static_cast<int>(s.ci_tok0[slot]);
+    mbar_expect_tx(&s.barQ, 2 * TILE_TK + C * KD * 4);
+    tma_load_rows(s.q, &p.tm_q, 0, hh, tk, &s.barQ);
+    tma_load_rows(s.k, &p.tm_k, 0, hh, tk, &s.barQ);
+    tma_load_rows(s.G, &p.tm_g, 0, hh, tk, &s.barQ);
+  };
   // rows of a partial chunk beyond its length hold the next sequence's tokens after a tiled load: clear them
   auto zero_rows_sw = [&](unsigned char* tile, int len) {          // [64][64] bf16 sub-tile, 128-byte rows
     for (int i = len * 8 + tid; i < C * 8; i += NT) *reinterpret_cast<uint4*>(tile + i * 16) = make_uint4(0u, 0u, 0u, 0u);
   };
-  if (static_cast<long long>(blockIdx.x) < total_tiles && tid == 0) fetch_state(blockIdx.x);
+  if (tid == 0) {
+    mbar_init(&s.barS, 1);
+    mbar_init(&s.barQ, 1);
+    mbar_init(&s.barB, 1);
+    mbar_init(&s.barM, 1);
+    fence_mbar_init();
+    if (static_cast<long long>(blockIdx.x) < total_tiles) {
+      fetch_state(blockIdx.x, 0);
+      fetch_qkg(blockIdx.x, 0);
+    }
+  }
+  __syncwarp();
+  if (warp == 0) umma::tmem_alloc(&s.tmem_slot, 512);
+  umma::fence_before_sync();
+  __syncthreads();
+  umma::fence_after_sync();
+  const uint32_t tb = s.tmem_slot;
+  const uint32_t tq = tb + (static_cast<uint32_t>(32 * q4) << 16);     // this warp's lanes
+
+  // Operands of phase C, built while the phase-B products run (rows R of the stacked tiles, 16-byte pieces pc):
+  // kR_I[j][kk] = k_j 2^(G_r - G_j),  r = 16 I,  j < 16 I            rows stacked: I=1 -> 0..15, I=2 -> 16..47, I=3 -> 48..95
+  // qL_J[t][kk] = scale q_t 2^(G_t - G_e), kL_J = k_t 2^(G_t - G_e), e = 16 J + 15, t >= 16 (J+1)
+  //                                                                   rows stacked: J=0 -> 0..47, J=1 -> 48..79, J=2 -> 80..95
+  // One item = four key columns of one row (a warp covers one row: conflict-free 8- and 16-byte accesses).
+  auto build_kR = [&]() {
+    for (int i = tid; i < 96 * 32; i += NT) {
+      const int R = i >> 5, g4 = i & 31;
+      const int I = (R < 16) ? 1 : (R < 48 ? 2 : 3);
+      const int j = R - (I == 1 ? 0 : (I == 2 ? 16 : 48));
+      const int r = 16 * I;
+      const uint2 kr = *reinterpret_cast<const uint2*>(&s.k[j * KD + g4 * 4]);
+      const float4 Ga = *reinterpret_cast<const float4*>(&s.G[j * KD + g4 * 4]);
+      const float4 Ra = *reinterpret_cast<const float4*>(&s.G[r * KD + g4 * 4]);
+      const float2 k0 = unpack_bf16(kr.x), k1 = unpack_bf16(kr.y);
+      *reinterpret_cast<uint2*>(sw_piece((g4 >> 4) ? sKR1 : sKR0, R, (g4 >> 1) & 7) + (g4 & 1) * 8) =
+          make_uint2(pack_bf16(k0.x * ex2(Ra.x - Ga.x), k0.y * ex2(Ra.y - Ga.y)), pack_bf16(k1.x * ex2(Ra.z - Ga.z), k1.y * ex2(Ra.w - Ga.w)));
+    }
+  };
+  auto build_qkL = [&](int R0, int R1) {
+    for (int i = R0 * 32 + tid; i < R1 * 32; i += NT) {
+      const int R = i >> 5, g4 = i & 31;
+      const int J = (R < 48) ? 0 : (R < 80 ? 1 : 2);
+      const int t = 16 * (J + 1) + R - (J == 0 ? 0 : (J == 1 ? 48 : 80));
+      const int e = 16 * J + 15;
+      const uint2 qr = *reinterpret_cast<const uint2*>(&s.q[t * KD + g4 * 4]);
+      const uint2 kr = *reinterpret_cast<const uint2*>(&s.k[t * KD + g4 * 4]);
+      const float4 Ga = *reinterpret_cast<const float4*>(&s.G[t * KD + g4 * 4]);
+      const float4 Ea = *reinterpret_cast<const float4*>(&s.G[e * KD + g4 * 4]);
+      const float f0 = ex2(Ga.x - Ea.x), f1 = ex2(Ga.y - Ea.y), f2 = ex2(Ga.z - Ea.z), f3 = ex2(Ga.w - Ea.w);
+      const float2 q0 = unpack_bf16(qr.x), q1 = unpack_bf16(qr.y), k0 = unpack_bf16(kr.x), k1 = unpack_bf16(kr.y);
+      const int off = (g4 & 1) * 8, pc = (g4 >> 1) & 7;
+      *reinterpret_cast<uint2*>(sw_piece((g4 >> 4) ? sQL1 : sQL0, R, pc) + off) =
+          make_uint2(pack_bf16(p.scale * q0.x * f0, p.scale * q0.y * f1), pack_bf16(p.scale * q1.x * f2, p.scale * q1.y * f3));
+      *reinterpret_cast<uint2*>(sw_piece((g4 >> 4) ? sKL1 : sKL0, R, pc) + off) =
+          make_uint2(pack_bf16(k0.x * f0, k0.y * f1), pack_bf16(k1.x * f2, k1.y * f3));
+    }
+  };
 
   uint32_t mph = 0;      // phase counter of barM
   bool alive = true;
   int it = 0;
   for (long long idx = blockIdx.x; idx < total_tiles && alive; idx += gridDim.x, ++it) {
-    const int c = static_cast<int>(idx / p.H), h = static_cast<int>(idx % p.H);
-    const ChunkInfo ci = chunk_info(p.seq_chunk_off, p.chunk_seq, p.cu, c);
+    const int h = static_cast<int>(idx % p.H);
+    struct { long long tok0; int len; } ci;
+    ci.tok0 = s.ci_tok0[it & 1];
+    ci.len = s.ci_len[it & 1];
     const int len = ci.len;
     const size_t tile = static_cast<size_t>(idx);
     const long long next_idx = idx + gridDim.x;
     long long* const dbg = (it == 2) ? p.dbg : nullptr;   // development aid: clocks of a steady-state tile
 
     KDA_DBG_CLOCK(dbg, 0);
-    // ---- second load group: Tm, raw kk (bulk); q, k, g, v, beta (async copies); lands behind phase A ------------
+    // ---- third load group: Tm, raw kk (bulk), v (tiled), beta (async copies); needed from phase B1 on ---------------
     if (tid == 0) {
-      mbar_expect_tx(&s.barB, 2 * TILE_TT + 3 * TILE_TK + C * KD * 4);
+      fence_proxy_async();        // the previous tile read its dq / dk staging out of this memory
+      mbar_expect_tx(&s.barB, 2 * TILE_TT + TILE_TK);
       bulk_g2s(s.TI, p.TI + tile * TILE_TT, TILE_TT, &s.barB);
       bulk_g2s(s.RKK, p.RKK + tile * TILE_TT, TILE_TT, &s.barB);
       const int tk = static_cast<int>(ci.tok0);
-      tma_load_rows(s.q, &p.tm_q, 0, h, tk, &s.barB);
-      tma_load_rows(s.k, &p.tm_k, 0, h, tk, &s.barB);
-      tma_load_rows(s.G, &p.tm_g, 0, h, tk, &s.barB);
       tma_load_rows(s.V, &p.tm_v, 0, h, tk, &s.barB);
       tma_load_rows(s.V + 8192, &p.tm_v, 64, h, tk, &s.barB);
     }
@@ -202,9 +260,21 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __g
       umma::commit(&s.barM);
     }
     KDA_DBG_CLOCK(dbg, 2);
-    // ---- meanwhile: the second load group, G = cumsum(g) log2(e), sum_v h dh' ------------------------------------
-    cp_async_wait<0>();
-    if (alive && !mbar_wait(&s.barB, it & 1)) {
+    // ---- meanwhile: sum_v h dh', then (q, k, g arrived during the previous tile's phase D) G = cumsum(g) log2(e) ----
+    {
+      const int kp = tid & 63, vq = tid >> 6;
+      float ax = 0.f, ay = 0.f;
+#pragma unroll 4
+      for (int vv = vq * 16; vv < vq * 16 + 16; ++vv) {
+        const float2 hh = unpack_bf16(*reinterpret_cast<const uint32_t*>(s.HS + vk_off(vv, 2 * kp)));
+        const float2 dd = unpack_bf16(*reinterpret_cast<const uint32_t*>(s.DH + vk_off(vv, 2 * kp)));
+        ax += hh.x * dd.x;
+        ay += hh.y * dd.y;
+      }
+      s.hdh_part[vq][2 * kp] = ax;
+      s.hdh_part[vq][2 * kp + 1] = ay;
+    }
+    if (alive && !mbar_wait(&s.barQ, it & 1)) {
       if (tid == 0) atomicOr(p.status, 32u);
       alive = false;
     }
@@ -215,9 +285,6 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __g
         reinterpret_cast<uint4*>(s.G)[2 * i] = make_uint4(0u, 0u, 0u, 0u);
         reinterpret_cast<uint4*>(s.G)[2 * i + 1] = make_uint4(0u, 0u, 0u, 0u);
       }
-      zero_rows_sw(s.V, len);
-      zero_rows_sw(s.V + 8192, len);
-      fence_proxy_async();
     }
     __syncthreads();
     {
@@ -238,19 +305,6 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __g
       for (int b = 0; b < 3; ++b) pre += (b < qr) ? s.carry[b][col] : 0.f;
 #pragma unroll
       for (int i = 0; i < 16; ++i) s.G[(qr * 16 + i) * KD + col] = (pre + gv[i]) * LOG2E;
-    }
-    {
-      const int kp = tid & 63, vq = tid >> 6;
-      float ax = 0.f, ay = 0.f;
-#pragma unroll 4
-      for (int vv = vq * 16; vv < vq * 16 + 16; ++vv) {
-        const float2 hh = unpack_bf16(*reinterpret_cast<const uint32_t*>(s.HS + vk_off(vv, 2 * kp)));
-        const float2 dd = unpack_bf16(*reinterpret_cast<const uint32_t*>(s.DH + vk_off(vv, 2 * kp)));
-        ax += hh.x * dd.x;
-        ay += hh.y * dd.y;
-      }
-      s.hdh_part[vq][2 * kp] = ax;
-      s.hdh_part[vq][2 * kp + 1] = ay;
     }
     if (alive && !mbar_wait(&s.barM, mph & 1)) {
       if (tid == 0) atomicOr(p.status, 64u);
@@ -287,19 +341,27 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __g
         }
       }
     }
-    for (int i = tid; i < C * 16; i += NT) {          // k Gam as two K-major sub-tiles [64 j][64 kk]
-      const int j = i >> 4, pc = i & 15;
-      const uint4 kr = *reinterpret_cast<const uint4*>(&s.k[j * KD + pc * 8]);
-      const float4 Ga = *reinterpret_cast<const float4*>(&s.G[j * KD + pc * 8]);
-      const float4 Gb = *reinterpret_cast<const float4*>(&s.G[j * KD + pc * 8 + 4]);
-      const float2 k0 = unpack_bf16(kr.x), k1 = unpack_bf16(kr.y), k2 = unpack_bf16(kr.z), k3 = unpack_bf16(kr.w);
-      *reinterpret_cast<uint4*>(sw_piece(sKG + (pc >> 3) * 8192, j, pc & 7)) =
-          make_uint4(pack_bf16(k0.x * ex2(Ga.x), k0.y * ex2(Ga.y)), pack_bf16(k1.x * ex2(Ga.z), k1.y * ex2(Ga.w)),
-                     pack_bf16(k2.x * ex2(Gb.x), k2.y * ex2(Gb.y)), pack_bf16(k3.x * ex2(Gb.z), k3.y * ex2(Gb.w)));
+    for (int i = tid; i < C * 32; i += NT) {          // k Gam as two K-major sub-tiles [64 j][64 kk]
+      const int j = i >> 5, g4 = i & 31;
+      const uint2 kr = *reinterpret_cast<const uint2*>(&s.k[j * KD + g4 * 4]);
+      const float4 Ga = *reinterpret_cast<const float4*>(&s.G[j * KD + g4 * 4]);
+      const float2 k0 = unpack_bf16(kr.x), k1 = unpack_bf16(kr.y);
+      *reinterpret_cast<uint2*>(sw_piece(sKG + (g4 >> 4) * 8192, j, (g4 >> 1) & 7) + (g4 & 1) * 8) =
+          make_uint2(pack_bf16(k0.x * ex2(Ga.x), k0.y * ex2(Ga.y)), pack_bf16(k1.x * ex2(Ga.z), k1.y * ex2(Ga.w)));
+    }
+    cp_async_wait<0>();
+    if (!mbar_wait(&s.barB, it & 1)) alive = false;       // Tm, raw kk, v
+    if (len < C) {
+      zero_rows_sw(s.V, len);
+      zero_rows_sw(s.V + 8192, len);
     }
     fence_proxy_async();
     umma::fence_before_sync();
-    __syncthreads();
+    alive = __syncthreads_and(alive);
+    if (!alive) {
+      if (tid == 0) atomicOr(p.status, 32u);
+      break;
+    }
     umma::fence_after_sync();
 
     KDA_DBG_CLOCK(dbg, 4);
@@ -333,6 +395,7 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __g
       }
       umma::commit(&s.barM);
     }
+    build_kR();            // into the v_new and dO tiles, which only phase A read
     if (!mbar_wait(&s.barM, mph & 1)) alive = false;
     ++mph;
     umma::fence_after_sync();
@@ -391,6 +454,7 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __g
       for (int sK = 0; sK < 4; ++sK) umma::mma_ss(tb + C_XY, dDt + static_cast<uint64_t>(sK) * 2u, dTiK + static_cast<uint64_t>(sK) * 2u, iX, sK > 0);
       umma::commit(&s.barM);
     }
+    build_qkL(0, 48);      // into the dv_new, v, k Gam and dw^T tiles, which phase B1 read last
     if (!mbar_wait(&s.barM, mph & 1)) alive = false;
     ++mph;
     umma::fence_after_sync();
@@ -425,6 +489,7 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __g
         umma::mma_ss(tb + C_XY, dTiM + static_cast<uint64_t>(sK) * 128u, dXm + static_cast<uint64_t>(sK) * 128u, iY, sK > 0);
       umma::commit(&s.barM);
     }
+    build_qkL(48, 96);
     if (!mbar_wait(&s.barM, mph & 1)) alive = false;
     ++mph;
     umma::fence_after_sync();
@@ -460,61 +525,15 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __g
         }
       }
     }
+    fence_proxy_async();
     umma::fence_before_sync();
-    alive = __syncthreads_and(alive);      // TI / RKK are dead: their memory now takes phase-C operands
+    alive = __syncthreads_and(alive);
     if (!alive) {
       if (tid == 0) atomicOr(p.status, 64u);
       break;
     }
-
-    KDA_DBG_CLOCK(dbg, 8);
-    // ---- operands of phase C -------------------------------------------------------------------------------------------
-    // kR_I[j][kk] = k_j 2^(G_r - G_j),  r = 16 I,  j < 16 I            rows stacked: I=1 -> 0..15, I=2 -> 16..47, I=3 -> 48..95
-    // qL_J[t][kk] = scale q_t 2^(G_t - G_e), kL_J = k_t 2^(G_t - G_e), e = 16 J + 15, t >= 16 (J+1)
-    //                                                                   rows stacked: J=0 -> 0..47, J=1 -> 48..79, J=2 -> 80..95
-    for (int i = tid; i < 96 * 16; i += NT) {
-      const int R = i >> 4, pc = i & 15;
-      {
-        const int I = (R < 16) ? 1 : (R < 48 ? 2 : 3);
-        const int j = R - (I == 1 ? 0 : (I == 2 ? 16 : 48));
-        const int r = 16 * I;
-        const uint4 kr = *reinterpret_cast<const uint4*>(&s.k[j * KD + pc * 8]);
-        const float4 Ga = *reinterpret_cast<const float4*>(&s.G[j * KD + pc * 8]);
-        const float4 Gb = *reinterpret_cast<const float4*>(&s.G[j * KD + pc * 8 + 4]);
-        const float4 Ra = *reinterpret_cast<const float4*>(&s.G[r * KD + pc * 8]);
-        const float4 Rb = *reinterpret_cast<const float4*>(&s.G[r * KD + pc * 8 + 4]);
-        const float2 k0 = unpack_bf16(kr.x), k1 = unpack_bf16(kr.y), k2 = unpack_bf16(kr.z), k3 = unpack_bf16(kr.w);
-        *reinterpret_cast<uint4*>(sw_piece((pc >> 3) ? sKR1 : sKR0, R, pc & 7)) =
-            make_uint4(pack_bf16(k0.x * ex2(Ra.x - Ga.x), k0.y * ex2(Ra.y - Ga.y)), pack_bf16(k1.x * ex2(Ra.z - Ga.z), k1.y * ex2(Ra.w - Ga.w)),
-                       pack_bf16(k2.x * ex2(Rb.x - Gb.x), k2.y * ex2(Rb.y - Gb.y)), pack_bf16(k3.x * ex2(Rb.z - Gb.z), k3.y * ex2(Rb.w - Gb.w)));
-      }
-      {
-        const int J = (R < 48) ? 0 : (R < 80 ? 1 : 2);
-        const int t = 16 * (J + 1) + R - (J == 0 ? 0 : (J == 1 ? 48 : 80));
-        const int e = 16 * J + 15;
-        const uint4 qr = *reinterpret_cast<const uint4*>(&s.q[t * KD + pc * 8]);
-        const uint4 kr = *reinterpret_cast<const uint4*>(&s.k[t * KD + pc * 8]);
-        const float4 Ga = *reinterpret_cast<const float4*>(&s.G[t * KD + pc * 8]);
-        const float4 Gb = *reinterpret_cast<const float4*>(&s.G[t * KD + pc * 8 + 4]);
-        const float4 Ea = *reinterpret_cast<const float4*>(&s.G[e * KD + pc * 8]);
-        const float4 Eb = *reinterpret_cast<const float4*>(&s.G[e * KD + pc * 8 + 4]);
-        const float f[8] = {ex2(Ga.x - Ea.x), ex2(Ga.y - Ea.y), ex2(Ga.z - Ea.z), ex2(Ga.w - Ea.w),
-                            ex2(Gb.x - Eb.x), ex2(Gb.y - Eb.y), ex2(Gb.z - Eb.z), ex2(Gb.w - Eb.w)};
-        const uint32_t qw[4] = {qr.x, qr.y, qr.z, qr.w}, kw[4] = {kr.x, kr.y, kr.z, kr.w};
-        uint32_t oq[4], ok[4];
-#pragma unroll
-        for (int e2 = 0; e2 < 4; ++e2) {
-          const float2 qq = unpack_bf16(qw[e2]), kk2 = unpack_bf16(kw[e2]);
-          oq[e2] = pack_bf16(p.scale * qq.x * f[2 * e2], p.scale * qq.y * f[2 * e2 + 1]);
-          ok[e2] = pack_bf16(kk2.x * f[2 * e2], kk2.y * f[2 * e2 + 1]);
-        }
-        *reinterpret_cast<uint4*>(sw_piece((pc >> 3) ? sQL1 : sQL0, R, pc & 7)) = make_uint4(oq[0], oq[1], oq[2], oq[3]);
-        *reinterpret_cast<uint4*>(sw_piece((pc >> 3) ? sKL1 : sKL0, R, pc & 7)) = make_uint4(ok[0], ok[1], ok[2], ok[3]);
-      }
-    }
-    fence_proxy_async();
-    __syncthreads();
     umma::fence_after_sync();
+    KDA_DBG_CLOCK(dbg, 8);
 
     KDA_DBG_CLOCK(dbg, 9);
     // =========================== phase C: off-diagonal blocks of the intra-chunk terms ==============================
@@ -560,7 +579,7 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __g
     umma::fence_after_sync();
     KDA_DBG_CLOCK(dbg, 10);
     // every shared-memory operand tile is dead now: fetch the next tile's phase-A operands behind phase D
-    if (next_idx < total_tiles && tid == 0) fetch_state(next_idx);
+    if (next_idx < total_tiles && tid == 0) fetch_state(next_idx, (it + 1) & 1);
     if (tid < len)
       p.dbeta[static_cast<size_t>(ci.tok0 + tid) * p.H + h] = s.dbp[0][tid] + s.dbp[1][tid] + s.dbp[2][tid] + s.dbp[3][tid] +
                                                              s.dbp[4][tid] + s.dbp[5][tid] + s.dbp[6][tid] + s.dbp[7][tid];
@@ -570,47 +589,78 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __g
     {
       const int kk = 32 * q4 + lane, blk = part, t0 = 16 * blk;
       float cq[16], cp[16], cn[16], lam[16], qv[16], kv[16];
+      float gam_last;
       {
-        float Gc[16], a[16], b[16];
+        // Decay inside the block as running products of lam_i = 2^(G_i - G_{i-1}) (every factor <= 1):
+        //   2^(G_i - G_first) = fl_i,  2^(G_i) = 2^(G_first) fl_i,  2^(G_e - G_i) = fr_i,  2^(G_last - G_i) = 2^(G_last - G_e) fr_i
+        float a[16], b[16];
+        float g_first, e_last;
+        {
+          float prev = s.G[t0 * KD + kk];
+          g_first = ex2(prev);
+          lam[0] = 1.f;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) Gc[i] = s.G[(t0 + i) * KD + kk];
-        const float Glast = s.G[(C - 1) * KD + kk];
+          for (int i = 1; i < 16; ++i) {
+            const float cur = s.G[(t0 + i) * KD + kk];
+            lam[i] = ex2(cur - prev);
+            prev = cur;
+          }
+          const float Glast = s.G[(C - 1) * KD + kk];
+          gam_last = ex2(Glast);
+          e_last = ex2(Glast - prev);
+        }
         // dk-: dkg 2^(G_last - G) + 2^(G_e - G) Cn ;  sum of k dk_end feeds dG at the chunk's last row
         umma::tmem_ld16(tq + C_DKG + t0, a);
         umma::tmem_ld16(tq + C_CN + t0, b);
         umma::tmem_ld_wait();
-        float dglp = 0.f;
+        {
+          float dglp = 0.f, fr = 1.f;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          kv[i] = __bfloat162float(s.k[(t0 + i) * KD + kk]);
-          const float dke = a[i] * ex2(Glast - Gc[i]);
-          dglp = fmaf(kv[i], dke, dglp);
-          cn[i] = (blk < 3) ? fmaf(ex2(Gc[15] - Gc[i]), b[i], dke) : dke;
+          for (int i = 15; i >= 0; --i) {
+            const float dke = a[i] * (e_last * fr);
+            dglp = fmaf(__bfloat162float(s.k[(t0 + i) * KD + kk]), dke, dglp);
+            cn[i] = (blk < 3) ? fmaf(fr, b[i], dke) : dke;
+            fr *= lam[i];
+          }
+          s.dglp[blk][kk] = dglp;
         }
-        s.dglp[blk][kk] = dglp;
         // dq: scale (Gam dqg + L Cq)
         umma::tmem_ld16(tq + C_DQG + t0, a);
         umma::tmem_ld16(tq + C_CQ + t0, b);
         umma::tmem_ld_wait();
+        {
+          float fl = p.scale;
+          const float gs = g_first;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float x = ex2(Gc[i]) * a[i];
-          if (blk > 0) x = fmaf(ex2(Gc[i] - Gc[0]), b[i], x);
-          cq[i] = p.scale * x;
+          for (int i = 0; i < 16; ++i) {
+            fl *= lam[i];
+            float x = (gs * fl) * a[i];
+            if (blk > 0) x = fmaf(fl, b[i], x);
+            cq[i] = x;
+          }
         }
         // dk+: Gam beta dbk + L Cp
         umma::tmem_ld16(tq + C_DBK + t0, a);
         umma::tmem_ld16(tq + C_CP + t0, b);
         umma::tmem_ld_wait();
+        {
+          float fl = 1.f;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            fl *= lam[i];
+            float x = (g_first * fl) * s.beta[t0 + i] * a[i];
+            if (blk > 0) x = fmaf(fl, b[i], x);
+            cp[i] = x;
+          }
+        }
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          float x = ex2(Gc[i]) * s.beta[t0 + i] * a[i];
-          if (blk > 0) x = fmaf(ex2(Gc[i] - Gc[0]), b[i], x);
-          cp[i] = x;
           qv[i] = __bfloat162float(s.q[(t0 + i) * KD + kk]);
-          lam[i] = (i > 0) ? ex2(Gc[i] - Gc[i - 1]) : 1.f;
+          kv[i] = __bfloat162float(s.k[(t0 + i) * KD + kk]);
         }
       }
+      __syncthreads();       // q, k, G have been read by everybody (and dglp is complete): the next tile's may arrive
+      if (next_idx < total_tiles && tid == 0) fetch_qkg(next_idx, (it + 1) & 1);
       KDA_DBG_CLOCK(dbg, 12);
       // diagonal block, pairwise; D = running product of lam (range-safe)
 #pragma unroll
@@ -627,18 +677,16 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __g
         }
       }
       KDA_DBG_CLOCK(dbg, 13);
-      // dG, dq, dk (in place of q, k)
+      // dG; dq, dk into their staging tiles
       float dGv[16];
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
         dGv[i] = qv[i] * cq[i] + kv[i] * (cp[i] - cn[i]);
-        s.q[(t0 + i) * KD + kk] = __float2bfloat16_rn(cq[i]);
-        s.k[(t0 + i) * KD + kk] = __float2bfloat16_rn(cp[i] + cn[i]);
+        stq[(t0 + i) * KD + kk] = __float2bfloat16_rn(cq[i]);
+        stk[(t0 + i) * KD + kk] = __float2bfloat16_rn(cp[i] + cn[i]);
       }
-      __syncthreads();       // dglp complete
       if (blk == 3)          // the chunk's last row carries the chunk-end terms
-        dGv[15] += s.dglp[0][kk] + s.dglp[1][kk] + s.dglp[2][kk] + s.dglp[3][kk] +
-                   ex2(s.G[(C - 1) * KD + kk]) * s.hdh[kk];
+        dGv[15] += s.dglp[0][kk] + s.dglp[1][kk] + s.dglp[2][kk] + s.dglp[3][kk] + gam_last * s.hdh[kk];
       {
         float run = 0.f;
 #pragma unroll
@@ -648,34 +696,28 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __g
         }
         s.carry[blk][kk] = run;
       }
-      __syncthreads();
+      __syncthreads();       // block totals and the staged dq, dk are complete
       {
         float add = 0.f;             // totals of the later blocks
 #pragma unroll
         for (int bb = 1; bb < 4; ++bb) add += (bb > blk) ? s.carry[bb][kk] : 0.f;
+        float* const dgp = p.dg + (static_cast<size_t>(ci.tok0 + t0) * p.H + h) * KD + kk;      // a warp stores 128 contiguous bytes
 #pragma unroll
-        for (int i = 0; i < 16; ++i) s.G[(t0 + i) * KD + kk] = dGv[i] + add;
+        for (int i = 0; i < 16; ++i)
+          if (t0 + i < len) dgp[static_cast<size_t>(i) * p.H * KD] = dGv[i] + add;
       }
-      umma::fence_before_sync();
-      __syncthreads();
       for (int i = tid; i < C * 16; i += NT) {
         const int r = i >> 4, pc = i & 15;
         if (r < len) {
           const size_t row = (static_cast<size_t>(ci.tok0 + r) * p.H + h) * KD + pc * 8;
-          *reinterpret_cast<uint4*>(p.dq + row) = *reinterpret_cast<const uint4*>(&s.q[r * KD + pc * 8]);
-          *reinterpret_cast<uint4*>(p.dk + row) = *reinterpret_cast<const uint4*>(&s.k[r * KD + pc * 8]);
-        }
-      }
-      for (int i = tid; i < C * 32; i += NT) {
-        const int r = i >> 5, pc = i & 31;
-        if (r < len) {
-          const size_t row = (static_cast<size_t>(ci.tok0 + r) * p.H + h) * KD + pc * 4;
-          *reinterpret_cast<float4*>(p.dg + row) = *reinterpret_cast<const float4*>(&s.G[r * KD + pc * 4]);
+          *reinterpret_cast<uint4*>(p.dq + row) = *reinterpret_cast<const uint4*>(&stq[r * KD + pc * 8]);
+          *reinterpret_cast<uint4*>(p.dk + row) = *reinterpret_cast<const uint4*>(&stk[r * KD + pc * 8]);
         }
       }
     }
     KDA_DBG_CLOCK(dbg, 14);
-    __syncthreads();   // q, k, G, beta, Ad, ... may be overwritten by the next tile
+    umma::fence_before_sync();
+    __syncthreads();   // beta, Ad, the staging tiles, TMEM ... may be overwritten by the next tile
   }
 
   // drain: a copy that is still in flight must not outlive the CTA's shared memory
