@@ -37,8 +37,10 @@ def _stale(target: str, deps: list[str]) -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) -> str:
-    """Compiles every .cu under csrc/ and links libkda_b200.so next to the package.  Returns its path."""
+def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False, phase_clocks: bool = False) -> str:
+    """Compiles every .cu under csrc/ and links libkda_b200.so next to the package.  Returns its path.
+
+    phase_clocks compiles the development-only per-phase clock marks into the kernels (always with force)."""
     nvcc = _nvcc()
     os.makedirs(OBJ, exist_ok=True)
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
@@ -49,7 +51,8 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
         obj = os.path.join(OBJ, os.path.basename(src)[:-3] + ".o")
         objs.append(obj)
         if force or _stale(obj, [src] + headers):
-            cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if ptxas_info else []) + ["-c", src, "-o", obj]
+            cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if ptxas_info else []) + (["-DKDA_PHASE_CLOCKS"] if phase_clocks else [])
+            cmd += ["-c", src, "-o", obj]
             if verbose:
                 print(" ".join(cmd), flush=True)
             procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
@@ -72,4 +75,5 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose=True, ptxas_info="--ptxas" in sys.argv))
+    clocks = "--clocks" in sys.argv
+    print(build(force="--force" in sys.argv or clocks, verbose=True, ptxas_info="--ptxas" in sys.argv, phase_clocks=clocks))

@@ -100,12 +100,20 @@ __device__ __forceinline__ uint32_t vk_off(int v, int k) { return (static_cast<u
 // byte offset of element (t, k) of a [64 t][128 k] tile: sub-tile k/64, then the 128-byte-row swizzle
 __device__ __forceinline__ uint32_t tk_off(int t, int k) { return (static_cast<uint32_t>(k >> 6) << 13) + swz<128>(t, k & 63); }
 
-// ---- development aid: phase clocks of CTA (0,0), written when a buffer has been registered --------------
+// ---- development aid: phase clocks of one CTA (x = 0, y = half the grid: a steady-state one), written when a buffer has been registered; compiled in
+// only with -DKDA_PHASE_CLOCKS (python -m kda_b200.build --clocks), otherwise the marks vanish ----------------
 extern long long* g_dbg_clocks;   // device pointer or NULL
+#ifdef KDA_PHASE_CLOCKS
 #define KDA_DBG_CLOCK(ptr, idx)                                                        \
   do {                                                                                 \
-    if ((ptr) != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) (ptr)[idx] = clock64(); \
+    if ((ptr) != nullptr && blockIdx.x == 0 && blockIdx.y == (gridDim.y >> 1) && threadIdx.x == 0) (ptr)[idx] = clock64(); \
   } while (0)
+#else
+#define KDA_DBG_CLOCK(ptr, idx) \
+  do {                          \
+    (void)(ptr);                \
+  } while (0)
+#endif
 
 // ---- optional per-kernel timing (host side, see kda_b200_profile_* in the public header) ------------
 struct ProfCall;                                  // one call's worth of events

@@ -96,65 +96,68 @@ __device__ __forceinline__ float butterfly32(float (&v)[32], int lane) {
   return v[0];
 }
 
-// Diagonal 16x16 block `b`, rows RS, RS+4, RS+8, RS+12 of the block, pairwise decay exp2(G_t - G_j).
-// Lanes own four key columns each; the per-lane partial dot products of up to 16 (t, j) pairs per matrix
-// are reduced together by butterfly32 (slots 0..15: q.k, slots 16..31: k.k).
-template <int RS>
-__device__ __forceinline__ void prep_diag_task(PrepSmem& s, const int b, const int lane, const float scale) {
-  const int r0 = 16 * b;
-  // pass A: rows RS and RS+4 (slots 0..3 / 4..11, and 16..19 / 20..27); pass B: row RS+8; pass C: row RS+12
+// ---- diagonal 16x16 blocks of Aqk / Akk -------------------------------------------------------------------
+// A warp takes one block b and one half of the key columns; a lane owns two adjacent key columns.  Rows are
+// walked upwards while E_j = k_j 2^(G_t - G_j) is carried per column j as a running product of
+// lam_t = 2^(G_t - G_{t-1}) (every factor <= 1: range-safe, and one ex2 per row instead of one per pair).
+// Row t contributes t+1 values of q_t.E_j and t values of k_t.E_j; rows are grouped so that a group fills at
+// most 32 slots, which butterfly32 then sums over the lanes: lane L ends up with the total of slot L.
+constexpr int DIAG_GROUPS = 10;
+__host__ __device__ constexpr int diag_group(int t) { return t <= 4 ? 0 : (t <= 6 ? 1 : (t <= 8 ? 2 : t - 6)); }
+__host__ __device__ constexpr int diag_base(int t) {      // first slot of row t inside its group
+  return t == 1 ? 1 : (t == 2 ? 4 : (t == 3 ? 9 : (t == 4 ? 16 : (t == 6 ? 11 : (t == 8 ? 15 : 0)))));
+}
+__host__ __device__ constexpr bool diag_last(int t) { return t == 4 || t == 6 || t >= 8; }
+
+__device__ __forceinline__ void prep_diag_half(const PrepSmem& s, const int b, const int hh, const int lane, float (&res)[DIAG_GROUPS]) {
+  const int r0 = 16 * b, kk = hh * 64 + 2 * lane;
+  float2 E[16];
+  float val[32];
 #pragma unroll
-  for (int pass = 0; pass < 3; ++pass) {
-    const int nrows = (pass == 0) ? 2 : 1;
-    const int rbase = (pass == 0) ? RS : (pass == 1 ? RS + 8 : RS + 12);      // first row of the pass
-    const int jmax = (pass == 0) ? RS + 4 : rbase;                            // last column needed
-    float4 Gt[2];
-    float qv[2][4], kv[2][4];
+  for (int i = 0; i < 32; ++i) val[i] = 0.f;
+  float2 Gprev = make_float2(0.f, 0.f);
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      if (i < nrows) {
-        const int t = r0 + rbase + 4 * i;
-        Gt[i] = *reinterpret_cast<const float4*>(&s.G[t * GS + lane * 4]);
-        const uint2 qr = *reinterpret_cast<const uint2*>(&s.q[t * QS + lane * 4]);
-        const uint2 kr = *reinterpret_cast<const uint2*>(&s.k[t * QS + lane * 4]);
-        const float2 q0 = unpack_bf16(qr.x), q1 = unpack_bf16(qr.y), k0 = unpack_bf16(kr.x), k1 = unpack_bf16(kr.y);
-        qv[i][0] = q0.x; qv[i][1] = q0.y; qv[i][2] = q1.x; qv[i][3] = q1.y;
-        kv[i][0] = k0.x; kv[i][1] = k0.y; kv[i][2] = k1.x; kv[i][3] = k1.y;
+  for (int t = 0; t < 16; ++t) {
+    const float2 Gt = *reinterpret_cast<const float2*>(&s.G[(r0 + t) * GS + kk]);
+    const float2 qt = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.q[(r0 + t) * QS + kk]));
+    const float2 kt = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.k[(r0 + t) * QS + kk]));
+    if (t > 0) {
+      const float lx = ex2(Gt.x - Gprev.x), ly = ex2(Gt.y - Gprev.y);
+#pragma unroll
+      for (int j = 0; j < t; ++j) {
+        E[j].x *= lx;
+        E[j].y *= ly;
       }
     }
-    float val[32];
+    Gprev = Gt;
+    E[t] = kt;
+    const int base = diag_base(t);
 #pragma unroll
-    for (int i = 0; i < 32; ++i) val[i] = 0.f;
+    for (int j = 0; j <= t; ++j) val[base + j] = fmaf(qt.y, E[j].y, qt.x * E[j].x);
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      if (j <= jmax) {
-        const float4 Gj = *reinterpret_cast<const float4*>(&s.G[(r0 + j) * GS + lane * 4]);
-        const uint2 jr = *reinterpret_cast<const uint2*>(&s.k[(r0 + j) * QS + lane * 4]);
-        const float2 j0 = unpack_bf16(jr.x), j1 = unpack_bf16(jr.y);
+    for (int j = 0; j < t; ++j) val[base + t + 1 + j] = fmaf(kt.y, E[j].y, kt.x * E[j].x);
+    if (diag_last(t)) {
+      res[diag_group(t)] = butterfly32(val, lane);
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          if (i < nrows && j <= rbase + 4 * i) {
-            const float d0 = j0.x * ex2(Gt[i].x - Gj.x), d1 = j0.y * ex2(Gt[i].y - Gj.y);
-            const float d2 = j1.x * ex2(Gt[i].z - Gj.z), d3 = j1.y * ex2(Gt[i].w - Gj.w);
-            const int slot = (pass == 0 && i == 1) ? 4 + j : j;
-            val[slot] = qv[i][0] * d0 + qv[i][1] * d1 + qv[i][2] * d2 + qv[i][3] * d3;
-            val[16 + slot] = kv[i][0] * d0 + kv[i][1] * d1 + kv[i][2] * d2 + kv[i][3] * d3;
-          }
-        }
-      }
+      for (int i = 0; i < 32; ++i) val[i] = 0.f;
     }
-    const float x = butterfly32(val, lane);
-    // lane -> (row, column, matrix)
-    const int sl = lane & 15;
-    int i = 0, j = sl;
-    if (pass == 0 && sl >= 4) { i = 1; j = sl - 4; }
-    const int trow = rbase + 4 * i;                 // row inside the block
-    const bool in_range = (pass == 0) ? (sl < 12) : true;
-    const int t = r0 + trow;
-    if (lane < 16) {
-      if (in_range && j <= trow) s.Aqk[t * TS + r0 + j] = __float2bfloat16_rn(scale * x);
-    } else {
-      if (in_range && j < trow) s.Akk[t * AS + r0 + j] = x;   // raw; beta_t is applied later
+  }
+}
+
+// Which (row, column, matrix) the value of lane L in group g is.  row < 0: unused slot.
+__device__ __forceinline__ void diag_decode(const int g, const int L, int& row, int& col, bool& is_kk) {
+  row = -1;
+  col = 0;
+  is_kk = false;
+#pragma unroll
+  for (int t = 0; t < 16; ++t) {
+    if (diag_group(t) == g) {
+      const int off = L - diag_base(t);
+      if (off >= 0 && off < 2 * t + 1) {
+        row = t;
+        is_kk = off > t;
+        col = is_kk ? off - (t + 1) : off;
+      }
     }
   }
 }
@@ -170,7 +173,7 @@ __global__ void __launch_bounds__(256, 2) kda_chunk_prepare_kernel(const PrepPar
   const size_t tile = static_cast<size_t>(c) * p.H + h;
   KDA_DBG_CLOCK(p.dbg, 16);
 
-  // ---- P1: stage q, k, v, g, beta; rows >= len are zero-filled -----------------------------------
+  // ---- P1: stage q, k, g, beta (v follows after P3a); rows >= len are zero-filled -----------------------------------
   {
     for (int i = tid; i < C * 16; i += 256) {
       const int r = i >> 4, pc = i & 15;
@@ -178,7 +181,6 @@ __global__ void __launch_bounds__(256, 2) kda_chunk_prepare_kernel(const PrepPar
       const size_t row = (static_cast<size_t>(ci.tok0 + (ok ? r : 0)) * p.H + h) * KD + pc * 8;
       cp_async16(&s.q[r * QS + pc * 8], p.q + row, ok);
       cp_async16(&s.k[r * QS + pc * 8], p.k + row, ok);
-      cp_async16(&s.v[r * QS + pc * 8], p.v + row, ok);
     }
     for (int i = tid; i < C * 32; i += 256) {
       const int r = i >> 5, pc = i & 31;
@@ -237,17 +239,39 @@ __global__ void __launch_bounds__(256, 2) kda_chunk_prepare_kernel(const PrepPar
   __syncthreads();
 
   KDA_DBG_CLOCK(p.dbg, 18);
-  // ---- P3a: diagonal 16x16 blocks, pairwise decay exp2(G_t - G_j) (never a factorisation: range-safe).
-  // Task (block b, row set RS); a warp takes RS and 3-RS of one block so that every warp has 68 pairs.
+  // ---- P3a: diagonal 16x16 blocks, pairwise decay as running products (never a factorisation: range-safe).
+  // Warp = (block, key half).  The halves meet in the v buffer, whose load is issued only afterwards.
   {
-    const int b = warp & 3;
-    if (warp < 4) {
-      prep_diag_task<0>(s, b, lane, p.scale);
-      prep_diag_task<3>(s, b, lane, p.scale);
-    } else {
-      prep_diag_task<1>(s, b, lane, p.scale);
-      prep_diag_task<2>(s, b, lane, p.scale);
+    const int b = warp & 3, hh = warp >> 2, r0 = 16 * b;
+    float res[DIAG_GROUPS];
+    prep_diag_half(s, b, hh, lane, res);
+    float* const scratch = reinterpret_cast<float*>(s.v) + b * (DIAG_GROUPS * 32);
+    if (hh == 1) {
+#pragma unroll
+      for (int g = 0; g < DIAG_GROUPS; ++g) scratch[g * 32 + lane] = res[g];
     }
+    __syncthreads();
+    if (hh == 0) {
+#pragma unroll
+      for (int g = 0; g < DIAG_GROUPS; ++g) {
+        int row, col;
+        bool is_kk;
+        diag_decode(g, lane, row, col, is_kk);
+        const float x = res[g] + scratch[g * 32 + lane];
+        if (row >= 0) {
+          if (is_kk) s.Akk[(r0 + row) * AS + r0 + col] = x;                            // raw; beta_t is applied later
+          else s.Aqk[(r0 + row) * TS + r0 + col] = __float2bfloat16_rn(p.scale * x);
+        }
+      }
+    }
+    __syncthreads();
+    for (int i = tid; i < C * 16; i += 256) {       // v: needed by the last phase only
+      const int r = i >> 4, pc = i & 15;
+      const bool ok = r < len;
+      const size_t row = (static_cast<size_t>(ci.tok0 + (ok ? r : 0)) * p.H + h) * KD + pc * 8;
+      cp_async16(&s.v[r * QS + pc * 8], p.v + row, ok);
+    }
+    cp_async_commit();
   }
 
   KDA_DBG_CLOCK(p.dbg, 19);
@@ -467,6 +491,7 @@ __global__ void __launch_bounds__(256, 2) kda_chunk_prepare_kernel(const PrepPar
           make_uint4(pack_bf16(t0.x, t0.y), pack_bf16(t0.z, t0.w), pack_bf16(t1.x, t1.y), pack_bf16(t1.z, t1.w));
     }
   }
+  cp_async_wait<0>();   // v
   __syncthreads();   // G is dead from here on: its buffer stages the UT and W tiles
   KDA_DBG_CLOCK(p.dbg, 23);
 
