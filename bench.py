@@ -54,6 +54,10 @@ KERNEL_WORK = {
     "bwd_main": (6 * K_ * V_ + 12 * C_ * K_ + 6 * C_ * V_ + 4 * C_ * C_,
                  _IN + 2 * V_ + 2 * _TT + 2 * _VK + 2 * _TK + (2 * K_ + 2 * K_ + 2 * V_ + 4 * K_ + 4)),   # = 4,616 B
 }
+# DRAM bytes per (token, head) that ncu measured (dram__bytes_read.sum + dram__bytes_write.sum of one launch) on a
+# small case of each kernel (B=1 T=8192, 262,144 (token, head) units; summaries under profiles/).  Traffic grows in
+# proportion to the units, so a launch's traffic is this figure times its units.
+KERNEL_TRAFFIC = {"prepare": 2522.0, "scan": 2049.0, "bwd_scan": 1822.0, "bwd_main": 4572.0, "decode": 125600.0}
 
 
 def load_peaks():
@@ -308,7 +312,8 @@ def main():
         byt = B * H * decode_bytes_per_seq_head()
         ach = byt / (ms_step * 1e-3) / 1e9
         roof = {"kernel": "kda_recurrent_kernel", "bound": "hbm", "achieved": ach, "peak": peaks["hbm"], "unit": "GB/s",
-                "frac": ach / peaks["hbm"], "traffic": None, "peak_source": peaks["src"]}
+                "frac": ach / peaks["hbm"], "traffic": KERNEL_TRAFFIC["decode"] * B * H,
+                "traffic_source": "ncu capture of a smaller case, scaled by units", "peak_source": peaks["src"]}
         kernels = {}
     else:
         kernels = {s: {"ms_per_launch": (ms / n), "launches": n} for s, (ms, n) in stages.items() if n > 0}
@@ -324,7 +329,8 @@ def main():
             ach = by * th / sec / 1e9
             roof = {"kernel": dom, "bound": "hbm", "achieved": ach, "peak": peaks["hbm"], "unit": "GB/s",
                     "frac": ach / peaks["hbm"]}
-        roof.update({"traffic": None, "peak_source": peaks["src"], "ms_per_launch": kernels[dom]["ms_per_launch"],
+        roof.update({"traffic": KERNEL_TRAFFIC[dom] * th, "traffic_source": "ncu capture of a smaller case, scaled by units",
+                     "peak_source": peaks["src"], "ms_per_launch": kernels[dom]["ms_per_launch"],
                      "algorithmic_flops_per_launch": fl * th, "algorithmic_bytes_per_launch": by * th})
     # whole-step roofline fractions (both bounds), for context
     fl_step = flops_per_token_head(backward=w.backward) * th
