@@ -53,6 +53,10 @@ KERNEL_WORK = {
     "bwd_scan": (6 * K_ * V_ + 2 * C_ * V_, 3 * _TK + _TT + 8 + 2 * V_ + _VK + _TK),
     "bwd_main": (6 * K_ * V_ + 12 * C_ * K_ + 6 * C_ * V_ + 4 * C_ * C_,
                  _IN + 2 * V_ + 2 * _TT + 2 * _VK + 2 * _TK + (2 * K_ + 2 * K_ + 2 * V_ + 4 * K_ + 4)),   # = 4,616 B
+    # gate front end with bf16 raw inputs: fwd reads g_raw, beta logits, writes g, beta (fp32);
+    # bwd reads dg, dbeta (fp32), g_raw, beta logits, writes dg_raw, dbeta_raw (bf16)
+    "gate_fwd": (12 * K_, 2 * K_ + 4 * K_ + 2 + 4),                # = 774 B
+    "gate_bwd": (20 * K_, 4 * K_ + 2 * K_ + 2 * K_ + 4 + 2 + 2),   # = 1,032 B
 }
 # DRAM bytes per (token, head) that ncu measured (dram__bytes_read.sum + dram__bytes_write.sum of one launch) on a
 # small case of each kernel (B=1 T=8192, 262,144 (token, head) units; summaries under profiles/).  Traffic grows in
@@ -170,6 +174,9 @@ def main():
     ap.add_argument("--scale-down", type=int, default=1, help="divide the batch (smaller case for profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--gate", action="store_true",
+                    help="call the operator as the layer does: raw bf16 gate input + A_log + dt_bias and beta logits "
+                         "(use_gate_in_kernel, use_beta_sigmoid_in_kernel); training workloads only")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -192,6 +199,14 @@ def main():
     peaks = load_peaks()
     host = make_workload(args.workload, seed=rank, scale_down=args.scale_down)
     cu_host = host.pop("cu_seqlens")
+    if args.gate:
+        if not w.backward:
+            raise SystemExit("--gate needs a forward+backward workload")
+        gen = torch.Generator().manual_seed(1000 + rank)
+        host["g"] = torch.randn(host["g"].shape, generator=gen).bfloat16()                      # raw gate input
+        host["beta"] = torch.randn(host["beta"].shape, generator=gen).bfloat16()                # beta logits
+        host["A_log"] = torch.log(torch.empty(w.H).uniform_(1, 16, generator=gen))
+        host["dt_bias"] = torch.randn(w.H * w.K, generator=gen)
     names = [n for n, t in host.items() if t is not None]
     pinned = {n: host[n].pin_memory() for n in names}
     devt = {n: pinned[n].to(dev, non_blocking=True) for n in names}
@@ -224,15 +239,17 @@ def main():
         launches_per_step = 1
         grad_names = []
     elif w.backward:
-        grad_names = ["q", "k", "v", "g", "beta"] + (["h0"] if "h0" in devt else [])
+        grad_names = ["q", "k", "v", "g", "beta"] + (["h0"] if "h0" in devt else []) + (["A_log", "dt_bias"] if args.gate else [])
+        gate_kw = dict(use_gate_in_kernel=True, use_beta_sigmoid_in_kernel=True) if args.gate else {}
 
         def step(x=devt):
             leaves = [x[n].requires_grad_(True) for n in grad_names]
+            kw = dict(gate_kw, A_log=x["A_log"], dt_bias=x["dt_bias"]) if args.gate else {}
             o, ht = chunk_kda(x["q"], x["k"], x["v"], x["g"], x["beta"], initial_state=x.get("h0"),
-                              output_final_state=True, cu_seqlens=cu)
+                              output_final_state=True, cu_seqlens=cu, **kw)
             grads = torch.autograd.grad([o, ht], leaves, [x["do"], x["dht"]])
             return (o, ht) + tuple(grads)
-        launches_per_step = 5
+        launches_per_step = 10 if args.gate else 5      # gate: + activation, beta sigmoid; + their backward and the reduction
     else:
         grad_names = []
 
@@ -270,7 +287,7 @@ def main():
     e2e = None
     if not args.no_e2e:
         out_host = None
-        pipelined = w.backward and cu is None and args.workload != "decode"
+        pipelined = w.backward and cu is None and args.workload != "decode" and not args.gate
 
         def e2e_step():
             nonlocal out_host
@@ -317,6 +334,9 @@ def main():
         kernels = {}
     else:
         kernels = {s: {"ms_per_launch": (ms / n), "launches": n} for s, (ms, n) in stages.items() if n > 0}
+        for s_, kv in kernels.items():          # every kernel against the HBM roof at its algorithmic bytes ("of measured")
+            if s_ in KERNEL_WORK:
+                kv["hbm_frac"] = KERNEL_WORK[s_][1] * th / (kv["ms_per_launch"] * 1e-3) / 1e9 / peaks["hbm"]
         dom = max((s for s in kernels if s in KERNEL_WORK), key=lambda s: kernels[s]["ms_per_launch"] * kernels[s]["launches"])
         fl, by = KERNEL_WORK[dom]
         sec = kernels[dom]["ms_per_launch"] * 1e-3
@@ -329,7 +349,7 @@ def main():
             ach = by * th / sec / 1e9
             roof = {"kernel": dom, "bound": "hbm", "achieved": ach, "peak": peaks["hbm"], "unit": "GB/s",
                     "frac": ach / peaks["hbm"]}
-        roof.update({"traffic": KERNEL_TRAFFIC[dom] * th, "traffic_source": "ncu capture of a smaller case, scaled by units",
+        roof.update({"traffic": KERNEL_TRAFFIC[dom] * th if dom in KERNEL_TRAFFIC else None, "traffic_source": "ncu capture of a smaller case, scaled by units",
                      "peak_source": peaks["src"], "ms_per_launch": kernels[dom]["ms_per_launch"],
                      "algorithmic_flops_per_launch": fl * th, "algorithmic_bytes_per_launch": by * th})
     # whole-step roofline fractions (both bounds), for context
@@ -347,12 +367,13 @@ def main():
                          f"B=1 T=512 H=32 K=V=128, {dt:.1f} s"}
 
     line = {
-        "metric": METRIC if args.workload == "train_bf16" else f"KDA {args.workload} tokens/s",
+        "metric": METRIC if (args.workload == "train_bf16" and not args.gate) else f"KDA {args.workload}{' +gate' if args.gate else ''} tokens/s",
         "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"{args.workload} (B={B} T={T} H={H} K=V=128, chunk 64"
-                               f"{', fwd+bwd' if w.backward else ''}{', packed varlen' if cu is not None else ''})",
+                               f"{', fwd+bwd' if w.backward else ''}{', packed varlen' if cu is not None else ''}"
+                               f"{', gate + beta sigmoid in kernel' if args.gate else ''})",
                    "per_gpu_batch": B, "l2": "inputs (>= 3 GB per step) far exceed the 126 MB L2; no flush needed",
                    "seed": "rank"},
         "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,

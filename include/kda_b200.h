@@ -163,8 +163,52 @@ int kda_chunk_bwd(const kda_chunk_args* args, void* stream);
 int kda_chunk_fwd_noalloc(const kda_chunk_args* args, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * Gate front end: the decay activation and the beta sigmoid that the layer applies in front of the
+ * operator, and their backward.  Stands behind chunk_kda(..., use_gate_in_kernel=True, A_log=..., dt_bias=...,
+ * use_beta_sigmoid_in_kernel=True, lower_bound=...) (fla/ops/kda/chunk.py:176-177,225-240,365-378) and
+ * fused_kda_gate / kda_gate_fwd / kda_gate_bwd (fla/ops/kda/gate.py:26-69,88-127,144-207,210-279,321-344):
+ *
+ *     x = g_raw + dt_bias[h, k]
+ *     g = -exp(A_log[h]) * softplus(x)                  softplus(x) = x for x > 20        (lower bound off)
+ *     g = lower_bound * sigmoid(exp(A_log[h]) * x)                                       (lower bound on)
+ *     beta = sigmoid(beta_raw)
+ *
+ * kda_gate_fwd writes g (and beta when beta_raw is given) in fp32, the types the chunked entry points read.
+ * kda_gate_bwd turns dg (and dbeta) into dg_raw (dbeta_raw) in the dtype of the raw tensors and reduces
+ * dA_log [H] and, when ddt_bias is non-NULL, ddt_bias [H*K] over all tokens; the reduction runs through
+ * per-CTA partial sums in `workspace` and is summed in a fixed order (bit-reproducible).
+ * K must be a multiple of 8; g_raw, dt_bias, g, dg, dg_raw and the workspace 16-byte aligned.
+ * g_raw == NULL with beta_raw != NULL runs the beta sigmoid alone (use_beta_sigmoid_in_kernel without the gate).
+ * ------------------------------------------------------------------------------------------------ */
+typedef struct kda_gate_args {
+  const void* g_raw;     /* [tokens, H, K] g_dtype: gate input before the activation, or NULL */
+  const float* A_log;    /* [H] */
+  const float* dt_bias;  /* [H*K] or NULL */
+  const void* beta_raw;  /* [tokens, H] beta_dtype: beta logits, or NULL (no beta sigmoid) */
+  float* g;              /* out, forward: [tokens, H, K] fp32 */
+  float* beta;           /* out, forward: [tokens, H] fp32 (needed iff beta_raw) */
+  const float* dg;       /* in, backward: [tokens, H, K] fp32 */
+  const float* dbeta;    /* in, backward: [tokens, H] fp32 (needed iff beta_raw) */
+  void* dg_raw;          /* out, backward: [tokens, H, K] g_dtype */
+  void* dbeta_raw;       /* out, backward: [tokens, H] beta_dtype (needed iff beta_raw) */
+  float* dA_log;         /* out, backward: [H] */
+  float* ddt_bias;       /* out, backward: [H*K] or NULL */
+  void* workspace;       /* backward scratch of kda_gate_bwd_workspace_bytes() bytes */
+  size_t workspace_bytes;
+  int64_t tokens;
+  int32_t H, K;
+  int32_t g_dtype, beta_dtype; /* KDA_BF16 or KDA_FP32 */
+  int32_t use_lower_bound;
+  float lower_bound;
+} kda_gate_args;
+
+size_t kda_gate_bwd_workspace_bytes(int64_t tokens, int32_t H, int32_t K);
+int kda_gate_fwd(const kda_gate_args* args, void* stream);
+int kda_gate_bwd(const kda_gate_args* args, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
  * Per-kernel timing for benchmarks (no counterpart in the Python operator; fla times whole calls).
- * While enabled, kda_chunk_fwd / kda_chunk_bwd record a CUDA event on the call's stream before their
+ * While enabled, kda_chunk_fwd / kda_chunk_bwd / kda_gate_fwd / kda_gate_bwd record a CUDA event on the call's stream before their
  * first kernel and after each kernel.  The events live in a fixed ring owned by the library (created
  * on the first enable; this is the one place the library creates CUDA objects).  kda_b200_profile_read
  * waits for the recorded events and returns, per stage, the summed milliseconds and the launch count
@@ -177,7 +221,9 @@ int kda_chunk_fwd_noalloc(const kda_chunk_args* args, void* stream);
 #define KDA_STAGE_BWD_MAIN 4
 #define KDA_STAGE_BWD_FINISH 5
 #define KDA_STAGE_L2NORM 6
-#define KDA_NUM_STAGES 7
+#define KDA_STAGE_GATE_FWD 7
+#define KDA_STAGE_GATE_BWD 8
+#define KDA_NUM_STAGES 9
 int kda_b200_profile_enable(int on);
 int kda_b200_profile_read(float* stage_ms, int* stage_launches, int reset);
 

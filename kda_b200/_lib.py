@@ -40,10 +40,22 @@ class ChunkArgs(C.Structure):
     ]
 
 
+class GateArgs(C.Structure):
+    _fields_ = [
+        ("g_raw", C.c_void_p), ("A_log", C.c_void_p), ("dt_bias", C.c_void_p), ("beta_raw", C.c_void_p),
+        ("g", C.c_void_p), ("beta", C.c_void_p), ("dg", C.c_void_p), ("dbeta", C.c_void_p),
+        ("dg_raw", C.c_void_p), ("dbeta_raw", C.c_void_p), ("dA_log", C.c_void_p), ("ddt_bias", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("tokens", C.c_int64), ("H", C.c_int32), ("K", C.c_int32), ("g_dtype", C.c_int32), ("beta_dtype", C.c_int32),
+        ("use_lower_bound", C.c_int32), ("lower_bound", C.c_float),
+    ]
+
+
 EXPORTS = (
     "kda_b200_abi_version", "kda_b200_strerror", "kda_recurrent_fwd",
     "kda_chunk_max_chunks", "kda_chunk_workspace_bytes", "kda_chunk_bwd_workspace_bytes",
-    "kda_chunk_fwd", "kda_chunk_bwd", "kda_chunk_fwd_noalloc", "kda_b200_profile_enable", "kda_b200_profile_read",
+    "kda_chunk_fwd", "kda_chunk_bwd", "kda_chunk_fwd_noalloc", "kda_gate_bwd_workspace_bytes", "kda_gate_fwd", "kda_gate_bwd",
+    "kda_b200_profile_enable", "kda_b200_profile_read",
 )
 
 _lib = None
@@ -74,6 +86,12 @@ def load() -> C.CDLL:
         fn = getattr(lib, name)
         fn.restype = C.c_int
         fn.argtypes = [C.POINTER(ChunkArgs), C.c_void_p]
+    lib.kda_gate_bwd_workspace_bytes.restype = C.c_size_t
+    lib.kda_gate_bwd_workspace_bytes.argtypes = [C.c_int64, C.c_int32, C.c_int32]
+    for name in ("kda_gate_fwd", "kda_gate_bwd"):
+        fn = getattr(lib, name)
+        fn.restype = C.c_int
+        fn.argtypes = [C.POINTER(GateArgs), C.c_void_p]
     lib.kda_b200_profile_enable.restype = C.c_int
     lib.kda_b200_profile_enable.argtypes = [C.c_int]
     lib.kda_b200_profile_read.restype = C.c_int
@@ -94,7 +112,7 @@ def check(code: int, what: str) -> None:
         raise KdaError(f"{what} failed with code {code}: {msg}")
 
 
-STAGES = ("tables", "prepare", "scan", "bwd_scan", "bwd_main", "bwd_finish", "l2norm")
+STAGES = ("tables", "prepare", "scan", "bwd_scan", "bwd_main", "bwd_finish", "l2norm", "gate_fwd", "gate_bwd")
 
 
 def profile_enable(on: bool) -> None:

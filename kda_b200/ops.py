@@ -81,6 +81,138 @@ def _as_i32(cu: torch.Tensor, device) -> torch.Tensor:
 
 
 # =================================================================================================
+# gate front end: decay activation and beta sigmoid
+# =================================================================================================
+
+class KDAGateFunction(torch.autograd.Function):
+    """g = -exp(A_log) * softplus(g_raw + dt_bias)  (or lower_bound * sigmoid(exp(A_log) * (g_raw + dt_bias))) and,
+    when `beta_raw` is given, beta = sigmoid(beta_raw); both come out in float32.  Mirrors KDAGateFunction and the
+    beta sigmoid of fla (fla/ops/kda/gate.py:282-318, fla/ops/kda/chunk.py:58-61,158-160)."""
+
+    @staticmethod
+    def forward(ctx, g_raw, A_log, dt_bias, beta_raw, lower_bound):
+        if not g_raw.is_cuda:
+            raise RuntimeError("kda_b200 runs on CUDA (sm_100a) tensors only; there is no CPU path")
+        H, K = g_raw.shape[-2:]
+        if K % 8:
+            raise NotImplementedError(f"kda_b200: the gate kernels need K to be a multiple of 8, got {K}")
+        if g_raw.dtype not in _DT or (beta_raw is not None and beta_raw.dtype not in _DT):
+            raise NotImplementedError("kda_b200: raw gate / beta inputs must be bfloat16 or float32")
+        assert A_log.numel() == H, f"A_log must have H={H} elements, got {A_log.numel()}"
+        assert dt_bias is None or dt_bias.numel() == H * K, f"dt_bias must have H*K={H * K} elements"
+        dev = g_raw.device
+        g_raw = g_raw.contiguous()
+        A32 = A_log.detach().contiguous().float()
+        b32 = dt_bias.detach().contiguous().float() if dt_bias is not None else None
+        beta_raw = beta_raw.contiguous() if beta_raw is not None else None
+        tokens = g_raw.numel() // (H * K)
+        g = torch.empty(g_raw.shape, dtype=torch.float32, device=dev)
+        beta = torch.empty(beta_raw.shape, dtype=torch.float32, device=dev) if beta_raw is not None else None
+        a = _lib.GateArgs(g_raw=_ptr(g_raw), A_log=_ptr(A32), dt_bias=_ptr(b32), beta_raw=_ptr(beta_raw), g=_ptr(g),
+                          beta=_ptr(beta), tokens=tokens, H=H, K=K, g_dtype=_DT[g_raw.dtype],
+                          beta_dtype=_DT[beta_raw.dtype] if beta_raw is not None else _lib.KDA_FP32,
+                          use_lower_bound=int(lower_bound is not None), lower_bound=float(lower_bound or 0.0))
+        with torch.cuda.device(dev):
+            _lib.check(_lib.load().kda_gate_fwd(C.byref(a), _stream(dev)), "kda_gate_fwd")
+        ctx.save_for_backward(g_raw, A32, b32, beta_raw)
+        ctx.meta = (tokens, H, K, lower_bound, A_log.dtype, A_log.shape, dt_bias.dtype if dt_bias is not None else None,
+                    dt_bias.shape if dt_bias is not None else None)
+        return g, beta
+
+    @staticmethod
+    def backward(ctx, dg, dbeta):
+        g_raw, A32, b32, beta_raw = ctx.saved_tensors
+        tokens, H, K, lower_bound, A_dtype, A_shape, b_dtype, b_shape = ctx.meta
+        dev = g_raw.device
+        lib = _lib.load()
+        if dg is None:
+            dg = torch.zeros(g_raw.shape, dtype=torch.float32, device=dev)
+        dg = dg.contiguous().float()
+        dg_raw = torch.empty_like(g_raw)
+        dA = torch.empty(H, dtype=torch.float32, device=dev)
+        db = torch.empty(H * K, dtype=torch.float32, device=dev) if b32 is not None else None
+        dbeta_raw = None
+        if beta_raw is not None:
+            dbeta = dbeta.contiguous().float() if dbeta is not None else torch.zeros(beta_raw.shape, dtype=torch.float32, device=dev)
+            dbeta_raw = torch.empty_like(beta_raw)
+        ws = torch.empty(lib.kda_gate_bwd_workspace_bytes(tokens, H, K), dtype=torch.uint8, device=dev)
+        a = _lib.GateArgs(g_raw=_ptr(g_raw), A_log=_ptr(A32), dt_bias=_ptr(b32), beta_raw=_ptr(beta_raw), dg=_ptr(dg),
+                          dbeta=_ptr(dbeta if beta_raw is not None else None), dg_raw=_ptr(dg_raw), dbeta_raw=_ptr(dbeta_raw),
+                          dA_log=_ptr(dA), ddt_bias=_ptr(db), workspace=_ptr(ws), workspace_bytes=ws.numel(), tokens=tokens,
+                          H=H, K=K, g_dtype=_DT[g_raw.dtype],
+                          beta_dtype=_DT[beta_raw.dtype] if beta_raw is not None else _lib.KDA_FP32,
+                          use_lower_bound=int(lower_bound is not None), lower_bound=float(lower_bound or 0.0))
+        with torch.cuda.device(dev):
+            _lib.check(lib.kda_gate_bwd(C.byref(a), _stream(dev)), "kda_gate_bwd")
+        return (dg_raw, dA.view(A_shape).to(A_dtype), db.view(b_shape).to(b_dtype) if db is not None else None,
+                dbeta_raw, None)
+
+
+@torch.compiler.disable
+def fused_kda_gate(g, A_log, dt_bias=None, lower_bound=None, output_dtype=torch.float32):
+    """Drop-in for fla.ops.kda.gate.fused_kda_gate (fla/ops/kda/gate.py:321-344): the decay activation with
+    autograd.  g [..., H, K] raw gate input, A_log [H], dt_bias [H*K] or None."""
+    out, _ = KDAGateFunction.apply(g, A_log, dt_bias, None, lower_bound)
+    return out if output_dtype == torch.float32 else out.to(output_dtype)
+
+
+def _gate_front_end(g, beta, use_gate_in_kernel, use_beta_sigmoid_in_kernel, safe_gate, lower_bound, kwargs):
+    """Applies the options of the operator that activate g and beta before the recurrence
+    (fla/ops/kda/chunk.py:365-378): returns (g, beta) as the chunked / recurrent kernels want them."""
+    A_log, dt_bias = None, None
+    if use_gate_in_kernel:
+        assert "A_log" in kwargs, "A_log must be provided when use_gate_in_kernel=True."
+        A_log, dt_bias = kwargs["A_log"], kwargs.get("dt_bias")
+        if safe_gate:
+            if lower_bound is None:
+                raise ValueError("`lower_bound` must be specified when `safe_gate=True` and `use_gate_in_kernel=True`.")
+            if not (-5 <= lower_bound < 0):
+                raise ValueError(f"`lower_bound` must be in the safe range [-5, 0), got {lower_bound}.")
+    if use_gate_in_kernel:
+        g, b = KDAGateFunction.apply(g, A_log, dt_bias, beta if use_beta_sigmoid_in_kernel else None, lower_bound)
+        if use_beta_sigmoid_in_kernel:
+            beta = b
+    elif use_beta_sigmoid_in_kernel:
+        beta = BetaSigmoidFunction.apply(beta)
+    return g, beta
+
+
+class BetaSigmoidFunction(torch.autograd.Function):
+    """beta = sigmoid(beta_raw) in float32 without the gate (use_beta_sigmoid_in_kernel alone;
+    fla/ops/kda/chunk.py:58-61,158-160)."""
+
+    @staticmethod
+    def _args(beta_raw, **kw):
+        H = beta_raw.shape[-1]
+        return _lib.GateArgs(beta_raw=_ptr(beta_raw), tokens=beta_raw.numel() // H, H=H, K=8, g_dtype=_lib.KDA_FP32,
+                             beta_dtype=_DT[beta_raw.dtype], **{n: _ptr(t) for n, t in kw.items()})
+
+    @staticmethod
+    def forward(ctx, beta_raw):
+        if not beta_raw.is_cuda:
+            raise RuntimeError("kda_b200 runs on CUDA (sm_100a) tensors only; there is no CPU path")
+        if beta_raw.dtype not in _DT:
+            raise NotImplementedError("kda_b200: raw beta must be bfloat16 or float32")
+        beta_raw = beta_raw.contiguous()
+        beta = torch.empty(beta_raw.shape, dtype=torch.float32, device=beta_raw.device)
+        with torch.cuda.device(beta_raw.device):
+            _lib.check(_lib.load().kda_gate_fwd(C.byref(BetaSigmoidFunction._args(beta_raw, beta=beta)), _stream(beta_raw.device)),
+                       "kda_gate_fwd")
+        ctx.save_for_backward(beta_raw)
+        return beta
+
+    @staticmethod
+    def backward(ctx, dbeta):
+        (beta_raw,) = ctx.saved_tensors
+        dbeta = dbeta.contiguous().float()
+        dbeta_raw = torch.empty_like(beta_raw)
+        with torch.cuda.device(beta_raw.device):
+            _lib.check(_lib.load().kda_gate_bwd(C.byref(BetaSigmoidFunction._args(beta_raw, dbeta=dbeta, dbeta_raw=dbeta_raw)),
+                                                _stream(beta_raw.device)), "kda_gate_bwd")
+        return dbeta_raw
+
+
+# =================================================================================================
 # decode / token-recurrent forward
 # =================================================================================================
 
@@ -127,19 +259,19 @@ def fused_recurrent_kda(q, k, v, g, beta, A_log=None, dt_bias=None, scale=None, 
                         use_beta_sigmoid_in_kernel=False, lower_bound=None, cu_seqlens=None,
                         transpose_state_layout=False, **kwargs):
     """Drop-in for fla.ops.kda.fused_recurrent_kda (fla/ops/kda/fused_recurrent.py:329-452): forward only.
-    q,k [B,T,H,K]; v [B,T,H,V]; g [B,T,H,K] log-decay; beta [B,T,H]; initial_state [N,H,K,V] fp32.
-    Returns (o, final_state or None)."""
-    _unsupported("use_gate_in_kernel", use_gate_in_kernel, False)
-    _unsupported("use_beta_sigmoid_in_kernel", use_beta_sigmoid_in_kernel, False)
+    q,k [B,T,H,K]; v [B,T,H,V]; g [B,T,H,K] log-decay (raw gate input with `use_gate_in_kernel`, activated with
+    `A_log`, `dt_bias`, `lower_bound` as in chunk_kda); beta [B,T,H] (logits with `use_beta_sigmoid_in_kernel`);
+    initial_state [N,H,K,V] fp32.  Returns (o, final_state or None)."""
     _unsupported("transpose_state_layout", transpose_state_layout, False)
-    _unsupported("lower_bound", lower_bound, None)
-    if A_log is not None or dt_bias is not None:
-        raise NotImplementedError("kda_b200: the fused gate activation (A_log, dt_bias) is not supported")
     if "use_qk_l2norm" in kwargs:
         use_qk_l2norm_in_kernel = kwargs.pop("use_qk_l2norm")
     _check_common(q, k, v, g, beta, initial_state, cu_seqlens)
     if scale is None:
         scale = k.shape[-1] ** -0.5
+    if use_gate_in_kernel:
+        assert A_log is not None, "A_log must be provided when use_gate_in_kernel=True."
+    g, beta = _gate_front_end(g, beta, use_gate_in_kernel, use_beta_sigmoid_in_kernel, False, lower_bound,
+                              {"A_log": A_log, "dt_bias": dt_bias} if use_gate_in_kernel else {})
     return fused_recurrent_kda_fwd(q, k, v, g, beta, scale, initial_state, False, output_final_state,
                                    use_qk_l2norm_in_kernel, cu_seqlens)
 
@@ -223,20 +355,21 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
               return_intermediate_states=False, cp_context=None, transpose_state_layout=False, **kwargs):
     """Drop-in for fla.ops.kda.chunk_kda (fla/ops/kda/chunk.py:167-411).
 
-    q, k [B,T,H,K]; v [B,T,H,V]; g [B,T,H,K] log-space decay (already activated); beta [B,T,H]
-    (already sigmoid-ed); initial_state [N,H,K,V] fp32; cu_seqlens [N+1] with B == 1.
-    Returns (o, final_state or None); differentiable w.r.t. q, k, v, g, beta, initial_state.
+    q, k [B,T,H,K]; v [B,T,H,V]; g [B,T,H,K] log-space decay; beta [B,T,H]; initial_state [N,H,K,V] fp32;
+    cu_seqlens [N+1] with B == 1.  With `use_gate_in_kernel=True` g is the raw gate input and `A_log` [H]
+    (and optionally `dt_bias` [H*K]) are keyword arguments: g = -exp(A_log) softplus(g + dt_bias), or, with
+    `lower_bound`, lower_bound * sigmoid(exp(A_log) (g + dt_bias)); with `use_beta_sigmoid_in_kernel=True` beta
+    holds logits.  Returns (o, final_state or None); differentiable w.r.t. q, k, v, g, beta, initial_state,
+    A_log and dt_bias.
 
     bf16 inputs with K = V = 128 take the chunked tensor-core kernels.  float32 inputs take the exact
     token-recurrent fp32 kernel (forward only).  `safe_gate` and `disable_recompute` only select
-    faster variants upstream and are accepted as no-ops; options that change results raise.
+    faster variants upstream and are accepted as no-ops (the kernels here are range-safe for any gate);
+    options that change results and are not built raise.
     """
-    _unsupported("use_gate_in_kernel", use_gate_in_kernel, False)
-    _unsupported("use_beta_sigmoid_in_kernel", use_beta_sigmoid_in_kernel, False)
     _unsupported("return_intermediate_states", return_intermediate_states, False)
     _unsupported("transpose_state_layout", transpose_state_layout, False)
     _unsupported("cp_context", cp_context, None)
-    _unsupported("lower_bound", lower_bound, None)
     if "use_qk_l2norm" in kwargs:
         use_qk_l2norm_in_kernel = kwargs.pop("use_qk_l2norm")
     chunk_size = kwargs.pop("chunk_size", 64)
@@ -244,11 +377,10 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
         raise ValueError(f"`chunk_size` must be either 32 or 64 for KDA, got {chunk_size}.")
     if chunk_size != CHUNK:
         raise NotImplementedError("kda_b200: only chunk_size=64 is implemented")
-    if kwargs.get("A_log") is not None or kwargs.get("dt_bias") is not None:
-        raise NotImplementedError("kda_b200: the fused gate activation (A_log, dt_bias) is not supported")
     B, T, H, K, V = _check_common(q, k, v, g, beta, initial_state, cu_seqlens)
     if scale is None:
         scale = K ** -0.5
+    g, beta = _gate_front_end(g, beta, use_gate_in_kernel, use_beta_sigmoid_in_kernel, safe_gate, lower_bound, kwargs)
     if q.dtype == torch.float32:
         if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (q, k, v, g, beta, initial_state)):
             raise NotImplementedError("kda_b200: the float32 path is forward-only; use bfloat16 inputs for training")

@@ -131,3 +131,27 @@ def cosine(x: torch.Tensor, ref: torch.Tensor) -> float:
     if nx == 0.0 or nr == 0.0:
         return 0.0
     return float((x @ ref).item() / (nx * nr))
+
+
+# ---- gate front end -------------------------------------------------------------------------------------
+def kda_gate(g_raw, A_log, dt_bias=None, lower_bound=None, dtype=torch.float64):
+    """Decay activation in front of the operator, differentiable, in `dtype`.
+
+    g = -exp(A_log[h]) * softplus(g_raw + dt_bias[h, k])                    (fla/ops/kda/gate.py:26-55)
+    g = lower_bound * sigmoid(exp(A_log[h]) * (g_raw + dt_bias[h, k]))      (fla/ops/kda/gate.py:58-69)
+    g_raw [..., H, K]; A_log [H]; dt_bias [H*K] or None.  softplus switches to the identity above 20
+    (fla/ops/utils/softplus.py:17-26), which in float64 differs from log1p(exp(x)) by < 3e-9.
+    """
+    H, K = g_raw.shape[-2:]
+    x = g_raw.to(dtype)
+    if dt_bias is not None:
+        x = x + dt_bias.to(dtype).view(H, K)
+    a = A_log.to(dtype).view(H, 1).exp()
+    if lower_bound is None:
+        return -a * torch.where(x > 20.0, x, torch.log1p(torch.exp(torch.clamp(x, max=20.0))))
+    return lower_bound * torch.sigmoid(a * x)
+
+
+def beta_sigmoid(beta_raw, dtype=torch.float64):
+    """beta = sigmoid(beta_raw) (fla/ops/kda/chunk.py:58-61)."""
+    return torch.sigmoid(beta_raw.to(dtype))

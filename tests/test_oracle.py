@@ -89,3 +89,22 @@ def test_empty_sequence():
     o, ht = recurrent_kda(d["q"], d["k"], d["v"], d["g"], d["beta"], initial_state=d["h0"], output_final_state=True)
     assert o.shape == (1, 0, 2, 8)
     assert torch.equal(ht, d["h0"].double())
+
+
+def test_gate_oracle_matches_golden(golden_dir):
+    """The float64 gate restatement against fla's naive_kda_gate / naive_kda_lowerbound_gate outputs and their
+    autograd gradients (fp32 fixtures: 2e-6 relative)."""
+    import numpy as np
+    from oracle.kda_oracle import kda_gate
+    z = np.load(os.path.join(golden_dir, "kda_gate.npz"))
+    dy = torch.from_numpy(z["dy"]).double()
+    for tag, use_bias, lb in (("sp", True, None), ("sp_nobias", False, None), ("lb", True, float(z["lower_bound"]))):
+        g, a, b = (torch.from_numpy(z[n]).double().requires_grad_(True) for n in ("g_raw", "A_log", "dt_bias"))
+        y = kda_gate(g, a, b if use_bias else None, lower_bound=lb)
+        grads = torch.autograd.grad((y * dy).sum(), [g, a] + ([b] if use_bias else []))
+        pairs = [(y, z[f"y_{tag}"]), (grads[0], z[f"dg_{tag}"]), (grads[1], z[f"dA_{tag}"])]
+        if use_bias:
+            pairs.append((grads[2], z[f"db_{tag}"]))
+        for got, ref in pairs:
+            ref = torch.from_numpy(ref).double()
+            assert (got.detach() - ref).abs().max() <= 2e-6 * max(1.0, ref.abs().max().item()), tag
