@@ -234,7 +234,7 @@ def main():
         scale = 128 ** -0.5
 
         def step(x=devt):
-            return fused_recurrent_kda_fwd(x["q"], x["k"], x["v"], x["g"], x["beta"], scale, initial_state=state,
+            return fused_recurrent_kda_fwd(x["q"], x["k"], x["v"], x["g"], x["beta"], scale=scale, initial_state=state,
                                            inplace_final_state=True)
         launches_per_step = 1
         grad_names = []

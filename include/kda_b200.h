@@ -31,7 +31,7 @@ extern "C" {
 #pragma GCC visibility push(default) /* the entry points below are the library's only exports */
 #endif
 
-#define KDA_B200_ABI_VERSION 1
+#define KDA_B200_ABI_VERSION 2
 #define KDA_CHUNK 64 /* tokens per chunk of the chunked kernels */
 
 /* io_dtype of q, k, v, o and of their gradients */
@@ -68,7 +68,11 @@ typedef struct kda_recurrent_args {
   float* ht;                   /* [slots, H, K, V] fp32 final states, or NULL; may equal h0 (in place) */
   void* o;                     /* [tokens, H, V] io_dtype */
   const int32_t* cu_seqlens;   /* device [N+1] or NULL (then every sequence has T tokens) */
-  const int32_t* state_indices;/* device [N] or NULL: sequence n reads/writes state slot state_indices[n] */
+  const int32_t* state_indices;/* device, or NULL.  Continuous batching (fla/ops/kda/fused_recurrent.py:122-144,195-210):
+                                  sequence n starts from slot state_indices[n * state_indices_stride + a], where
+                                  a = num_accepted_tokens[n] - 1 (0 without it), and the state after its token t is
+                                  written to slot state_indices[n * state_indices_stride + t]; needs ht == h0.
+                                  With one token per sequence and stride 1 this is "slot state_indices[n]". */
   int64_t tokens;              /* total tokens */
   int32_t N;                   /* sequences */
   int32_t T;                   /* tokens per sequence when cu_seqlens is NULL */
@@ -76,6 +80,8 @@ typedef struct kda_recurrent_args {
   int32_t io_dtype;            /* KDA_BF16 or KDA_FP32 */
   int32_t use_qk_l2norm;       /* x * rsqrt(sum x^2 + 1e-6) on q and k rows inside the kernel */
   float scale;
+  const int32_t* num_accepted_tokens; /* device [N] or NULL: speculative decoding, see state_indices */
+  int32_t state_indices_stride;       /* elements between two sequences' rows of state_indices (>= 1 when it is used) */
 } kda_recurrent_args;
 
 int kda_recurrent_fwd(const kda_recurrent_args* args, void* stream);

@@ -11,7 +11,7 @@ LIB_PATH = os.path.join(PKG, "libkda_b200.so")
 
 KDA_BF16, KDA_FP32 = 0, 1
 NOALLOC_SCRATCH_BYTES = 32 << 20
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 
 class RecurrentArgs(C.Structure):
@@ -21,6 +21,7 @@ class RecurrentArgs(C.Structure):
         ("state_indices", C.c_void_p),
         ("tokens", C.c_int64), ("N", C.c_int32), ("T", C.c_int32), ("H", C.c_int32), ("K", C.c_int32),
         ("V", C.c_int32), ("io_dtype", C.c_int32), ("use_qk_l2norm", C.c_int32), ("scale", C.c_float),
+        ("num_accepted_tokens", C.c_void_p), ("state_indices_stride", C.c_int32),
     ]
 
 

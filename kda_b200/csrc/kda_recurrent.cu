@@ -62,7 +62,9 @@ __global__ void __launch_bounds__(REC_WARPS * 32) kda_recurrent_kernel(const kda
     bos = static_cast<long long>(n) * a.T;
     eos = bos + a.T;
   }
-  const long long slot = a.state_indices ? a.state_indices[n] : n;
+  // continuous batching: the sequence's row of slot numbers; it starts from the slot of the last accepted token
+  const int32_t* slots = a.state_indices ? a.state_indices + static_cast<size_t>(n) * a.state_indices_stride : nullptr;
+  const long long slot = slots ? slots[a.num_accepted_tokens ? a.num_accepted_tokens[n] - 1 : 0] : n;
   const size_t sbase = (static_cast<size_t>(slot) * a.H + h) * K * a.V + col;
 
   float4 S[R];
@@ -146,10 +148,15 @@ __global__ void __launch_bounds__(REC_WARPS * 32) kda_recurrent_kernel(const kda
       oa.w += __shfl_xor_sync(0xffffffffu, oa.w, off);
     }
     if (rg == 0) IoTraits<IO>::st4(op + (static_cast<size_t>(t) * a.H + h) * a.V + col, oa);
+    if (slots && a.ht) {      // the state after every token goes to that token's slot
+      const size_t tb = (static_cast<size_t>(slots[t - bos]) * a.H + h) * K * a.V + col;
+#pragma unroll
+      for (int i = 0; i < R; ++i) __stcs(reinterpret_cast<float4*>(a.ht + tb + static_cast<size_t>(rg + RG * i) * a.V), S[i]);
+    }
     __syncwarp();
   }
 
-  if (a.ht) {
+  if (a.ht && !slots) {
 #pragma unroll
     for (int i = 0; i < R; ++i)
       __stcs(reinterpret_cast<float4*>(a.ht + sbase + static_cast<size_t>(rg + RG * i) * a.V), S[i]);
@@ -181,7 +188,13 @@ static int dispatch_rec(const kda_recurrent_args& a, cudaStream_t st) {
 
 extern "C" int kda_recurrent_fwd(const kda_recurrent_args* args, void* stream) {
   if (!args) return KDA_E_NULL;
-  const kda_recurrent_args& a = *args;
+  kda_recurrent_args a = *args;
+  if (a.state_indices) {
+    if (a.state_indices_stride <= 0) a.state_indices_stride = 1;
+    if (a.ht && a.ht != a.h0) return KDA_E_SHAPE;      // slot-addressed states are updated in place
+  } else if (a.num_accepted_tokens) {
+    return KDA_E_NULL;                                 // accepted-token counts only mean something with slots
+  }
   if (a.N < 0 || a.H <= 0 || a.V <= 0 || a.V % 32 != 0 || a.tokens < 0) return KDA_E_SHAPE;
   if (a.N == 0 || a.tokens == 0) {
     // nothing to scan; with distinct h0/ht buffers the final state is the initial one

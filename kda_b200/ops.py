@@ -216,14 +216,27 @@ class BetaSigmoidFunction(torch.autograd.Function):
 # decode / token-recurrent forward
 # =================================================================================================
 
-def fused_recurrent_kda_fwd(q, k, v, g, beta, scale, initial_state=None, inplace_final_state=False,
-                            output_final_state=True, use_qk_l2norm_in_kernel=False, cu_seqlens=None,
-                            ssm_state_indices=None):
-    """Lower-level entry (fla/ops/kda/fused_recurrent.py:229-325).  With `inplace_final_state` the
-    kernel writes the final state over `initial_state` (optionally through `ssm_state_indices`, one
-    state slot per sequence) and returns that tensor."""
+def fused_recurrent_kda_fwd(q, k, v, g, beta, A_log=None, dt_bias=None, initial_state=None, scale=None,
+                            output_final_state=False, inplace_final_state=True, cu_seqlens=None, ssm_state_indices=None,
+                            num_accepted_tokens=None, use_qk_l2norm_in_kernel=False, use_gate_in_kernel=False,
+                            use_beta_sigmoid_in_kernel=False, lower_bound=None, out=None, transpose_state_layout=False,
+                            **kwargs):
+    """Lower-level decode entry with fla's signature (fla/ops/kda/fused_recurrent.py:229-325), forward only.
+
+    With `inplace_final_state` the kernel writes states over `initial_state` and returns that tensor.
+    Continuous batching: `ssm_state_indices` [N] or [N, T] names the state slot of every token; a sequence starts
+    from the slot of its first token -- with `num_accepted_tokens` [N] (speculative decoding) from the slot of its
+    last accepted token -- and the state after token t lands in slot `ssm_state_indices[n, t]`."""
+    _unsupported("transpose_state_layout", transpose_state_layout, False)
     B, T, H, K, V = _check_common(q, k, v, g, beta, None, cu_seqlens)
+    if scale is None:
+        scale = K ** -0.5
     dev = q.device
+    with torch.no_grad():
+        if use_gate_in_kernel:
+            assert A_log is not None, "A_log must be provided when use_gate_in_kernel=True."
+        g, beta = _gate_front_end(g, beta, use_gate_in_kernel, use_beta_sigmoid_in_kernel, False, lower_bound,
+                                  {"A_log": A_log, "dt_bias": dt_bias} if use_gate_in_kernel else {})
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     g = g.contiguous().float()
     beta = beta.contiguous().float()
@@ -231,23 +244,38 @@ def fused_recurrent_kda_fwd(q, k, v, g, beta, scale, initial_state=None, inplace
     cu = _as_i32(cu_seqlens, dev) if cu_seqlens is not None else None
     h0 = initial_state.contiguous() if initial_state is not None else None
     if inplace_final_state:
-        if h0 is None or h0.data_ptr() != initial_state.data_ptr():
+        assert initial_state is not None
+        if h0.data_ptr() != initial_state.data_ptr() or h0.dtype != torch.float32:
             raise ValueError("inplace_final_state needs a contiguous fp32 initial_state")
         ht = h0
     elif output_final_state:
         ht = torch.empty(N, H, K, V, dtype=torch.float32, device=dev)
     else:
         ht = None
-    idx = None
+    idx, acc, stride = None, None, 0
     if ssm_state_indices is not None:
         if not inplace_final_state:
             raise ValueError("ssm_state_indices requires inplace_final_state=True")
         idx = ssm_state_indices.to(device=dev, dtype=torch.int32).contiguous()
-    o = torch.empty_like(v)
+        stride = 1 if idx.ndim == 1 else idx.stride(0)
+        if idx.ndim == 1 and cu_seqlens is None and T > 1:
+            raise ValueError("ssm_state_indices must be [N, T] when a sequence has more than one token")
+        if num_accepted_tokens is not None:
+            acc = num_accepted_tokens.to(device=dev, dtype=torch.int32).contiguous()
+    elif num_accepted_tokens is not None:
+        raise ValueError("num_accepted_tokens requires ssm_state_indices")
+    if out is None:
+        o = torch.empty_like(v)
+    else:
+        assert out.shape == v.shape
+        if not out.is_contiguous() or out.dtype != v.dtype:
+            raise ValueError("`out` must be contiguous and of v's dtype")
+        o = out
     args = _lib.RecurrentArgs(
         q=_ptr(q), k=_ptr(k), v=_ptr(v), g=_ptr(g), beta=_ptr(beta), h0=_ptr(h0), ht=_ptr(ht), o=_ptr(o),
         cu_seqlens=_ptr(cu), state_indices=_ptr(idx), tokens=B * T, N=N, T=T, H=H, K=K, V=V,
-        io_dtype=_DT[q.dtype], use_qk_l2norm=int(bool(use_qk_l2norm_in_kernel)), scale=float(scale))
+        io_dtype=_DT[q.dtype], use_qk_l2norm=int(bool(use_qk_l2norm_in_kernel)), scale=float(scale),
+        num_accepted_tokens=_ptr(acc), state_indices_stride=stride)
     with torch.cuda.device(dev):
         _lib.check(_lib.load().kda_recurrent_fwd(C.byref(args), _stream(dev)), "kda_recurrent_fwd")
     return o, ht
@@ -268,12 +296,10 @@ def fused_recurrent_kda(q, k, v, g, beta, A_log=None, dt_bias=None, scale=None, 
     _check_common(q, k, v, g, beta, initial_state, cu_seqlens)
     if scale is None:
         scale = k.shape[-1] ** -0.5
-    if use_gate_in_kernel:
-        assert A_log is not None, "A_log must be provided when use_gate_in_kernel=True."
-    g, beta = _gate_front_end(g, beta, use_gate_in_kernel, use_beta_sigmoid_in_kernel, False, lower_bound,
-                              {"A_log": A_log, "dt_bias": dt_bias} if use_gate_in_kernel else {})
-    return fused_recurrent_kda_fwd(q, k, v, g, beta, scale, initial_state, False, output_final_state,
-                                   use_qk_l2norm_in_kernel, cu_seqlens)
+    return fused_recurrent_kda_fwd(q, k, v, g, beta, A_log=A_log, dt_bias=dt_bias, initial_state=initial_state, scale=scale,
+                                   output_final_state=output_final_state, inplace_final_state=False, cu_seqlens=cu_seqlens,
+                                   use_qk_l2norm_in_kernel=use_qk_l2norm_in_kernel, use_gate_in_kernel=use_gate_in_kernel,
+                                   use_beta_sigmoid_in_kernel=use_beta_sigmoid_in_kernel, lower_bound=lower_bound)
 
 
 # =================================================================================================
@@ -384,8 +410,9 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
     if q.dtype == torch.float32:
         if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (q, k, v, g, beta, initial_state)):
             raise NotImplementedError("kda_b200: the float32 path is forward-only; use bfloat16 inputs for training")
-        return fused_recurrent_kda_fwd(q, k, v, g, beta, scale, initial_state, False, output_final_state,
-                                       use_qk_l2norm_in_kernel, cu_seqlens)
+        return fused_recurrent_kda_fwd(q, k, v, g, beta, initial_state=initial_state, scale=scale,
+                                       output_final_state=output_final_state, inplace_final_state=False,
+                                       use_qk_l2norm_in_kernel=use_qk_l2norm_in_kernel, cu_seqlens=cu_seqlens)
     if K != 128 or V != 128:
         raise NotImplementedError(f"kda_b200: the bf16 chunked kernels are built for K = V = 128, got K={K}, V={V}")
     return ChunkKDAFunction.apply(q, k, v, g, beta, float(scale), initial_state, bool(output_final_state),

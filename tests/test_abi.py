@@ -25,7 +25,10 @@ def test_exports_every_declared_symbol(lib):
 
 
 def test_version_and_error_text(lib):
-    assert lib.kda_b200_abi_version() == 1
+    import re
+    from kda_b200 import _lib
+    header = open(os.path.join(ROOT, "include", "kda_b200.h")).read()
+    assert lib.kda_b200_abi_version() == int(re.search(r"#define KDA_B200_ABI_VERSION (\d+)", header).group(1)) == _lib.ABI_VERSION
     assert lib.kda_b200_strerror(0) == b"ok"
     assert b"NULL" in lib.kda_b200_strerror(-1)
     assert b"workspace" in lib.kda_b200_strerror(-5)

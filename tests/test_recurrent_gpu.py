@@ -71,12 +71,37 @@ def test_decode_inplace_steps_match_scan():
     outs = []
     for t in range(3):
         o_t, _ = fused_recurrent_kda_fwd(d["q"][:, t:t + 1], d["k"][:, t:t + 1], d["v"][:, t:t + 1], d["g"][:, t:t + 1],
-                                         d["beta"][:, t:t + 1], scale, initial_state=pool, inplace_final_state=True,
+                                         d["beta"][:, t:t + 1], scale=scale, initial_state=pool, inplace_final_state=True,
                                          ssm_state_indices=slots)
         outs.append(o_t)
     assert torch.equal(torch.cat(outs, 1), o_ref)
     assert torch.equal(pool[slots.long()], h_ref)
     assert torch.count_nonzero(pool[1]) == 0 and torch.count_nonzero(pool[3]) == 0
+
+
+def test_speculative_decoding_state_slots():
+    """Continuous batching with per-token state slots (fla/ops/kda/fused_recurrent.py:122-144,195-210): a sequence
+    starts from the slot of its last accepted token and the state after draft token t lands in slot [n, t]."""
+    from kda_b200 import fused_recurrent_kda, fused_recurrent_kda_fwd
+    N, T = 3, 4
+    d = _cuda(make_inputs(N, T, 2, 128, 128, torch.bfloat16, seed=9, h0_std=0.02))
+    slots = torch.tensor([[7, 1, 12, 3], [0, 9, 4, 14], [5, 2, 11, 8]], device="cuda", dtype=torch.int32)
+    accepted = torch.tensor([1, 3, 2], device="cuda", dtype=torch.int32)
+    pool = torch.zeros(16, 2, 128, 128, device="cuda")
+    for n in range(N):
+        pool[int(slots[n, int(accepted[n]) - 1])] = d["h0"][n]
+    o, ret = fused_recurrent_kda_fwd(d["q"], d["k"], d["v"], d["g"], d["beta"], initial_state=pool, inplace_final_state=True,
+                                     ssm_state_indices=slots, num_accepted_tokens=accepted)
+    assert ret.data_ptr() == pool.data_ptr()
+    for t in range(T):
+        o_ref, h_ref = fused_recurrent_kda(d["q"][:, :t + 1], d["k"][:, :t + 1], d["v"][:, :t + 1], d["g"][:, :t + 1],
+                                           d["beta"][:, :t + 1], initial_state=d["h0"], output_final_state=True)
+        assert torch.equal(o[:, :t + 1], o_ref)
+        assert torch.equal(pool[slots[:, t].long()], h_ref), t
+    untouched = sorted(set(range(16)) - set(slots.flatten().tolist()))
+    assert all(torch.count_nonzero(pool[i]) == 0 for i in untouched)
+    with pytest.raises(ValueError, match="requires ssm_state_indices"):
+        fused_recurrent_kda_fwd(d["q"], d["k"], d["v"], d["g"], d["beta"], initial_state=pool, num_accepted_tokens=accepted)
 
 
 def test_empty_and_errors():
@@ -85,8 +110,10 @@ def test_empty_and_errors():
     with pytest.raises(ValueError):
         fused_recurrent_kda(d["q"].repeat(2, 1, 1, 1), d["k"].repeat(2, 1, 1, 1), d["v"].repeat(2, 1, 1, 1),
                             d["g"].repeat(2, 1, 1, 1), d["beta"].repeat(2, 1, 1), cu_seqlens=torch.tensor([0, 8]).cuda())
-    with pytest.raises(NotImplementedError):
+    with pytest.raises(AssertionError, match="A_log must be provided"):
         chunk_kda(d["q"], d["k"], d["v"], d["g"], d["beta"], use_gate_in_kernel=True)
+    with pytest.raises(NotImplementedError):
+        chunk_kda(d["q"], d["k"], d["v"], d["g"], d["beta"], transpose_state_layout=True)
     with pytest.raises(RuntimeError):
         chunk_kda(d["q"].cpu(), d["k"].cpu(), d["v"].cpu(), d["g"].cpu(), d["beta"].cpu())
     e = _cuda(make_inputs(2, 0, 2, 64, 64, torch.float32, seed=1, h0_std=0.1))
