@@ -225,7 +225,7 @@ int kda_gate_bwd(const kda_gate_args* args, void* stream);
 #define KDA_STAGE_SCAN 2
 #define KDA_STAGE_BWD_SCAN 3
 #define KDA_STAGE_BWD_MAIN 4
-#define KDA_STAGE_BWD_FINISH 5
+#define KDA_STAGE_BWD_FINISH 5 /* unused: the per-chunk backward is one kernel */
 #define KDA_STAGE_L2NORM 6
 #define KDA_STAGE_GATE_FWD 7
 #define KDA_STAGE_GATE_BWD 8

@@ -114,12 +114,18 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __g
   __nv_bfloat16* const stk = reinterpret_cast<__nv_bfloat16*>(s.TI);
 
   // thread 0: the phase-A operands of tile idx -- state tiles by bulk copy, dO by two tiled loads (64 value columns each)
-  auto fetch_state = [&](long long idx, int slot) {
-    const size_t tl = static_cast<size_t>(idx);
-    const int cc = static_cast<int>(idx / p.H), hh = static_cast<int>(idx % p.H);
-    const ChunkInfo cn = chunk_info(p.seq_chunk_off, p.chunk_seq, p.cu, cc);
+  // thread 0: first token and length of tile idx's chunk into slot (two dependent global loads: done early, off the
+  // critical path, while phase B2 executes and the other warps build operands)
+  auto stash_chunk = [&](long long idx, int slot) {
+    const ChunkInfo cn = chunk_info(p.seq_chunk_off, p.chunk_seq, p.cu, static_cast<int>(idx / p.H));
     s.ci_tok0[slot] = cn.tok0;
     s.ci_len[slot] = cn.len;
+  };
+  auto fetch_state = [&](long long idx, int slot) {      // after stash_chunk(idx, slot)
+    const size_t tl = static_cast<size_t>(idx);
+    const int hh = static_cast<int>(idx % p.H);
+    struct { long long tok0; } cn;
+    cn.tok0 = s.ci_tok0[slot];
     mbar_expect_tx(&s.barS, 2 * TILE_VK + 2 * TILE_VT + TILE_TK);
     bulk_g2s(s.HS, p.HS + tl * TILE_VK, TILE_VK, &s.barS);
     bulk_g2s(s.DH, p.DH + tl * TILE_VK, TILE_VK, &s.barS);
@@ -148,6 +154,7 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __g
     mbar_init(&s.barM, 1);
     fence_mbar_init();
     if (static_cast<long long>(blockIdx.x) < total_tiles) {
+      stash_chunk(blockIdx.x, 0);
       fetch_state(blockIdx.x, 0);
       fetch_qkg(blockIdx.x, 0);
     }
@@ -157,7 +164,9 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __g
   umma::fence_before_sync();
   __syncthreads();
   umma::fence_after_sync();
-  const uint32_t tb = s.tmem_slot;
+  const uint32_t tb = __shfl_sync(0xffffffffu, s.tmem_slot, 0);          // warp-uniform for the compiler
+  const int warp_u = __shfl_sync(0xffffffffu, warp, 0);
+  const uint32_t lead = lane == 0;                                      // the lane of warp 0 that issues the MMAs
   const uint32_t tq = tb + (static_cast<uint32_t>(32 * q4) << 16);     // this warp's lanes
 
   // Operands of phase C, built while the phase-B products run (rows R of the stacked tiles, 16-byte pieces pc):
@@ -165,8 +174,8 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __g
   // qL_J[t][kk] = scale q_t 2^(G_t - G_e), kL_J = k_t 2^(G_t - G_e), e = 16 J + 15, t >= 16 (J+1)
   //                                                                   rows stacked: J=0 -> 0..47, J=1 -> 48..79, J=2 -> 80..95
   // One item = four key columns of one row (a warp covers one row: conflict-free 8- and 16-byte accesses).
-  auto build_kR = [&]() {
-    for (int i = tid; i < 96 * 32; i += NT) {
+  auto build_kR = [&](int first, int stride) {
+    for (int i = first; i < 96 * 32; i += stride) {
       const int R = i >> 5, g4 = i & 31;
       const int I = (R < 16) ? 1 : (R < 48 ? 2 : 3);
       const int j = R - (I == 1 ? 0 : (I == 2 ? 16 : 48));
@@ -179,8 +188,8 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __g
           make_uint2(pack_bf16(k0.x * ex2(Ra.x - Ga.x), k0.y * ex2(Ra.y - Ga.y)), pack_bf16(k1.x * ex2(Ra.z - Ga.z), k1.y * ex2(Ra.w - Ga.w)));
     }
   };
-  auto build_qkL = [&](int R0, int R1) {
-    for (int i = R0 * 32 + tid; i < R1 * 32; i += NT) {
+  auto build_qkL = [&](int R0, int R1, int first, int stride) {
+    for (int i = R0 * 32 + first; i < R1 * 32; i += stride) {
       const int R = i >> 5, g4 = i & 31;
       const int J = (R < 48) ? 0 : (R < 80 ? 1 : 2);
       const int t = 16 * (J + 1) + R - (J == 0 ? 0 : (J == 1 ? 48 : 80));
@@ -239,7 +248,7 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __g
 
     KDA_DBG_CLOCK(dbg, 1);
     // =========================== phase A: state-dependent products ==================================================
-    if (tid == 0 && alive) {
+    if (warp_u == 0 && alive) {
       const uint32_t aHS = smem_u32(s.HS), aDH = smem_u32(s.DH), aVN = smem_u32(s.VN), aDVN = smem_u32(s.DVN), aDO = smem_u32(s.dO);
       constexpr uint32_t i1 = umma::instr_desc(128, 64, true, false);
       constexpr uint32_t i2 = umma::instr_desc(128, 64, true, true, false, true);
@@ -252,12 +261,12 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __g
 #pragma unroll
       for (int sK = 0; sK < 8; ++sK) {
         const uint64_t mn = static_cast<uint64_t>(sK) * 128u, dDOk = ((sK >> 2) ? dDO1 : dDO0) + static_cast<uint64_t>(sK & 3) * 2u;
-        umma::mma_ss(tb + C_DQG, dHS + mn, dDOk, i1, sK > 0);                 // dqg^T = h dO^T
-        umma::mma_ss(tb + C_DW, dHS + mn, dDVNm + mn, i2, sK > 0);            // dw^T = -h dv_new^T
-        umma::mma_ss(tb + C_DKG, dDHm + mn, dVNm + mn, i3, sK > 0);           // dkg^T = dh' v_new^T
-        umma::mma_ss(tb + C_DAQ, dDOk, dVNm + mn, i4, sK > 0);                // dAqk = dO v_new^T
+        umma::mma_ss_lead(tb + C_DQG, dHS + mn, dDOk, i1, sK > 0, lead);                 // dqg^T = h dO^T
+        umma::mma_ss_lead(tb + C_DW, dHS + mn, dDVNm + mn, i2, sK > 0, lead);            // dw^T = -h dv_new^T
+        umma::mma_ss_lead(tb + C_DKG, dDHm + mn, dVNm + mn, i3, sK > 0, lead);           // dkg^T = dh' v_new^T
+        umma::mma_ss_lead(tb + C_DAQ, dDOk, dVNm + mn, i4, sK > 0, lead);                // dAqk = dO v_new^T
       }
-      umma::commit(&s.barM);
+      if (lead) umma::commit(&s.barM);
     }
     KDA_DBG_CLOCK(dbg, 2);
     // ---- meanwhile: sum_v h dh', then (q, k, g arrived during the previous tile's phase D) G = cumsum(g) log2(e) ----
@@ -366,7 +375,7 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __g
 
     KDA_DBG_CLOCK(dbg, 4);
     // =========================== phase B1 ===========================================================================
-    if (tid == 0) {
+    if (warp_u == 0) {
       const uint32_t aDVN = smem_u32(s.DVN), aV = smem_u32(s.V), aDWT = smem_u32(sDWT), aKG = smem_u32(sKG), aTI = smem_u32(s.TI);
       constexpr uint32_t iT = umma::instr_desc(64, 64, true, false);
       constexpr uint32_t iTt = umma::instr_desc(64, 64, false, true);
@@ -378,24 +387,24 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __g
 #pragma unroll
       for (int sK = 0; sK < 8; ++sK) {
         const uint64_t mn = static_cast<uint64_t>(sK) * 128u, dVk = ((sK >> 2) ? dV1 : dV0) + static_cast<uint64_t>(sK & 3) * 2u;
-        umma::mma_ss(tb + C_DAQ, dDuM + mn, dVk, iT, sK > 0);       // dTm[t][j]   += sum_v du[t][v] v[j][v]
-        umma::mma_ss(tb + C_DTT, dVk, dDuM + mn, iTt, sK > 0);      // dTm^T[j][t] += the same
+        umma::mma_ss_lead(tb + C_DAQ, dDuM + mn, dVk, iT, sK > 0, lead);       // dTm[t][j]   += sum_v du[t][v] v[j][v]
+        umma::mma_ss_lead(tb + C_DTT, dVk, dDuM + mn, iTt, sK > 0, lead);      // dTm^T[j][t] += the same
       }
 #pragma unroll
       for (int sK = 0; sK < 8; ++sK) {
         const uint64_t mn = static_cast<uint64_t>(sK) * 128u, dKg = ((sK >> 2) ? dKg1 : dKg0) + static_cast<uint64_t>(sK & 3) * 2u;
-        umma::mma_ss(tb + C_DAQ, dDwM + mn, dKg, iT, 1);            // += sum_kk dw[t][kk] kGam[j][kk]
-        umma::mma_ss(tb + C_DTT, dKg, dDwM + mn, iTt, 1);
+        umma::mma_ss_lead(tb + C_DAQ, dDwM + mn, dKg, iT, 1, lead);            // += sum_kk dw[t][kk] kGam[j][kk]
+        umma::mma_ss_lead(tb + C_DTT, dKg, dDwM + mn, iTt, 1, lead);
       }
 #pragma unroll
       for (int sK = 0; sK < 4; ++sK) {
         const uint64_t dTi = dTiM + static_cast<uint64_t>(sK) * 128u;
-        umma::mma_ss(tb + C_DBV, dDuK + static_cast<uint64_t>(sK) * 2u, dTi, iB, sK > 0);     // dbv^T[v][t] = sum_t' du[t'][v] Tm[t'][t]
-        umma::mma_ss(tb + C_DBK, dDwK + static_cast<uint64_t>(sK) * 2u, dTi, iB, sK > 0);     // dbk^T[kk][t] = sum_t' dw[t'][kk] Tm[t'][t]
+        umma::mma_ss_lead(tb + C_DBV, dDuK + static_cast<uint64_t>(sK) * 2u, dTi, iB, sK > 0, lead);     // dbv^T[v][t] = sum_t' du[t'][v] Tm[t'][t]
+        umma::mma_ss_lead(tb + C_DBK, dDwK + static_cast<uint64_t>(sK) * 2u, dTi, iB, sK > 0, lead);     // dbk^T[kk][t] = sum_t' dw[t'][kk] Tm[t'][t]
       }
-      umma::commit(&s.barM);
+      if (lead) umma::commit(&s.barM);
     }
-    build_kR();            // into the v_new and dO tiles, which only phase A read
+    if (warp_u != 0) build_kR(tid - 32, NT - 32);      // warp 0 is busy issuing; into the v_new and dO tiles, which only phase A read
     if (!mbar_wait(&s.barM, mph & 1)) alive = false;
     ++mph;
     umma::fence_after_sync();
@@ -445,16 +454,19 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __g
 
     KDA_DBG_CLOCK(dbg, 6);
     // =========================== phase B2: X = dTm Tm^T ============================================================
-    if (tid == 0) {
+    if (warp_u == 0) {
       const uint32_t aDT = smem_u32(sDT), aTI = smem_u32(s.TI);
       constexpr uint32_t iX = umma::instr_desc(64, 64, false, false);
 #pragma unroll
       const uint64_t dDt = umma::desc_kmajor(aDT, 0), dTiK = umma::desc_kmajor(aTI, 0);
 #pragma unroll
-      for (int sK = 0; sK < 4; ++sK) umma::mma_ss(tb + C_XY, dDt + static_cast<uint64_t>(sK) * 2u, dTiK + static_cast<uint64_t>(sK) * 2u, iX, sK > 0);
-      umma::commit(&s.barM);
+      for (int sK = 0; sK < 4; ++sK) umma::mma_ss_lead(tb + C_XY, dDt + static_cast<uint64_t>(sK) * 2u, dTiK + static_cast<uint64_t>(sK) * 2u, iX, sK > 0, lead);
+      if (lead) {
+        umma::commit(&s.barM);
+        if (next_idx < total_tiles) stash_chunk(next_idx, (it + 1) & 1);      // warp 0 sits this build out: the look-up's latency hides here
+      }
     }
-    build_qkL(0, 48);      // into the dv_new, v, k Gam and dw^T tiles, which phase B1 read last
+    if (warp_u != 0) build_qkL(0, 48, tid - 32, NT - 32);      // into the dv_new, v, k Gam and dw^T tiles, which phase B1 read last
     if (!mbar_wait(&s.barM, mph & 1)) alive = false;
     ++mph;
     umma::fence_after_sync();
@@ -479,17 +491,17 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __g
 
     KDA_DBG_CLOCK(dbg, 7);
     // =========================== phase B3: Y = Tm^T X,  dAkk = -tril(Y, -1) ==========================================
-    if (tid == 0) {
+    if (warp_u == 0) {
       const uint32_t aX = smem_u32(sX), aTI = smem_u32(s.TI);
       constexpr uint32_t iY = umma::instr_desc(64, 64, true, true);
 #pragma unroll
       const uint64_t dTiM = umma::desc_mnmajor(aTI, 0, SPAN), dXm = umma::desc_mnmajor(aX, 0, SPAN);
 #pragma unroll
       for (int sK = 0; sK < 4; ++sK)
-        umma::mma_ss(tb + C_XY, dTiM + static_cast<uint64_t>(sK) * 128u, dXm + static_cast<uint64_t>(sK) * 128u, iY, sK > 0);
-      umma::commit(&s.barM);
+        umma::mma_ss_lead(tb + C_XY, dTiM + static_cast<uint64_t>(sK) * 128u, dXm + static_cast<uint64_t>(sK) * 128u, iY, sK > 0, lead);
+      if (lead) umma::commit(&s.barM);
     }
-    build_qkL(48, 96);
+    build_qkL(48, 96, tid, NT);
     if (!mbar_wait(&s.barM, mph & 1)) alive = false;
     ++mph;
     umma::fence_after_sync();
@@ -537,7 +549,7 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __g
 
     KDA_DBG_CLOCK(dbg, 9);
     // =========================== phase C: off-diagonal blocks of the intra-chunk terms ==============================
-    if (tid == 0) {
+    if (warp_u == 0) {
       const uint32_t aKR = smem_u32(sKR0), aQL = smem_u32(sQL0), aKL = smem_u32(sKL0), aDAQ = smem_u32(sDAQ), aDAK = smem_u32(sDAK);
       const uint32_t lKR = smem_u32(sKR1) - aKR, lQL = smem_u32(sQL1) - aQL, lKL = smem_u32(sKL1) - aKL;
       constexpr uint32_t iC1 = umma::instr_desc(128, 16, true, false);
@@ -552,8 +564,8 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __g
         for (int sK = 0; sK < I; ++sK) {
           const uint64_t dA = dKr + static_cast<uint64_t>((rb + 16 * sK) * 8);                 // A[kk][j] = kR_I[j][kk]: row offset in 16-byte units
           const uint64_t bo = static_cast<uint64_t>(16 * I * 8 + sK * 2);                      // B[t][j]: rows 16 I.., k-step sK
-          umma::mma_ss(tb + C_CQ + 16 * I, dA, dAq + bo, iC1, sK > 0);
-          umma::mma_ss(tb + C_CP + 16 * I, dA, dAk + bo, iC1, sK > 0);
+          umma::mma_ss_lead(tb + C_CQ + 16 * I, dA, dAq + bo, iC1, sK > 0, lead);
+          umma::mma_ss_lead(tb + C_CP + 16 * I, dA, dAk + bo, iC1, sK > 0, lead);
         }
       }
 #pragma unroll
@@ -563,104 +575,130 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __g
         for (int sK = 0; sK < 3 - J; ++sK) {
           const uint64_t ao = static_cast<uint64_t>((rb + 16 * sK) * 8);
           const uint64_t bo = static_cast<uint64_t>((16 * (J + 1) + 16 * sK) * 8 + 2 * J);     // B[j][t] = dA[t][j]: rows t, columns 16 J..
-          umma::mma_ss(tb + C_CN + 16 * J, dQl + ao, dAq + bo, iC2, sK > 0);
-          umma::mma_ss(tb + C_CN + 16 * J, dKl + ao, dAk + bo, iC2, 1);
+          umma::mma_ss_lead(tb + C_CN + 16 * J, dQl + ao, dAq + bo, iC2, sK > 0, lead);
+          umma::mma_ss_lead(tb + C_CN + 16 * J, dKl + ao, dAk + bo, iC2, 1, lead);
         }
       }
-      umma::commit(&s.barM);
+      if (lead) umma::commit(&s.barM);
+    }
+    // =========================== phase D: one thread per key column and 16-row block ================================
+    // Part 1 needs only accumulators of phases A and B1 and runs while phase C executes.
+    const int kk = 32 * q4 + lane, blk = part, t0 = 16 * blk;
+    float cq[16], cp[16], cn[16], lam[16], qv[16], kv[16];
+    float gam_last;
+    {
+      // Decay inside the block as running products of lam_i = 2^(G_i - G_{i-1}) (every factor <= 1):
+      //   2^(G_i - G_first) = fl_i,  2^(G_i) = 2^(G_first) fl_i,  2^(G_e - G_i) = fr_i,  2^(G_last - G_i) = 2^(G_last - G_e) fr_i
+      float a[16];
+      float g_first, e_last;
+      {
+        float prev = s.G[t0 * KD + kk];
+        g_first = ex2(prev);
+        lam[0] = 1.f;
+#pragma unroll
+        for (int i = 1; i < 16; ++i) {
+          const float cur = s.G[(t0 + i) * KD + kk];
+          lam[i] = ex2(cur - prev);
+          prev = cur;
+        }
+        const float Glast = s.G[(C - 1) * KD + kk];
+        gam_last = ex2(Glast);
+        e_last = ex2(Glast - prev);
+      }
+      // dk-: dkg 2^(G_last - G);  sum of k dk_end feeds dG at the chunk's last row
+      umma::tmem_ld16(tq + C_DKG + t0, a);
+      umma::tmem_ld_wait();
+      {
+        float dglp = 0.f, fr = 1.f;
+#pragma unroll
+        for (int i = 15; i >= 0; --i) {
+          const float dke = a[i] * (e_last * fr);
+          dglp = fmaf(__bfloat162float(s.k[(t0 + i) * KD + kk]), dke, dglp);
+          cn[i] = dke;
+          fr *= lam[i];
+        }
+        s.dglp[blk][kk] = dglp;
+      }
+      // dq: scale Gam dqg
+      umma::tmem_ld16(tq + C_DQG + t0, a);
+      umma::tmem_ld_wait();
+      {
+        float fl = p.scale * g_first;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          fl *= lam[i];
+          cq[i] = fl * a[i];
+        }
+      }
+      // dk+: Gam beta dbk
+      umma::tmem_ld16(tq + C_DBK + t0, a);
+      umma::tmem_ld_wait();
+      {
+        float fl = g_first;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          fl *= lam[i];
+          cp[i] = fl * s.beta[t0 + i] * a[i];
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        qv[i] = __bfloat162float(s.q[(t0 + i) * KD + kk]);
+        kv[i] = __bfloat162float(s.k[(t0 + i) * KD + kk]);
+      }
     }
     if (!mbar_wait(&s.barM, mph & 1)) alive = false;
     ++mph;
-    alive = __syncthreads_and(alive);
+    alive = __syncthreads_and(alive);      // phase C complete; q, k, G have been read by everybody; dglp is complete
     if (!alive) {
       if (tid == 0) atomicOr(p.status, 64u);
       break;
     }
     umma::fence_after_sync();
     KDA_DBG_CLOCK(dbg, 10);
-    // every shared-memory operand tile is dead now: fetch the next tile's phase-A operands behind phase D
-    if (next_idx < total_tiles && tid == 0) fetch_state(next_idx, (it + 1) & 1);
+    // every shared-memory operand tile is dead now and q, k, g are in registers: fetch the next tile behind the rest
+    if (next_idx < total_tiles && tid == 0) {
+      fetch_state(next_idx, (it + 1) & 1);
+      fetch_qkg(next_idx, (it + 1) & 1);
+    }
     if (tid < len)
       p.dbeta[static_cast<size_t>(ci.tok0 + tid) * p.H + h] = s.dbp[0][tid] + s.dbp[1][tid] + s.dbp[2][tid] + s.dbp[3][tid] +
                                                              s.dbp[4][tid] + s.dbp[5][tid] + s.dbp[6][tid] + s.dbp[7][tid];
 
     KDA_DBG_CLOCK(dbg, 11);
-    // =========================== phase D: one thread per key column and 16-row block ================================
     {
-      const int kk = 32 * q4 + lane, blk = part, t0 = 16 * blk;
-      float cq[16], cp[16], cn[16], lam[16], qv[16], kv[16];
-      float gam_last;
       {
-        // Decay inside the block as running products of lam_i = 2^(G_i - G_{i-1}) (every factor <= 1):
-        //   2^(G_i - G_first) = fl_i,  2^(G_i) = 2^(G_first) fl_i,  2^(G_e - G_i) = fr_i,  2^(G_last - G_i) = 2^(G_last - G_e) fr_i
-        float a[16], b[16];
-        float g_first, e_last;
-        {
-          float prev = s.G[t0 * KD + kk];
-          g_first = ex2(prev);
-          lam[0] = 1.f;
-#pragma unroll
-          for (int i = 1; i < 16; ++i) {
-            const float cur = s.G[(t0 + i) * KD + kk];
-            lam[i] = ex2(cur - prev);
-            prev = cur;
-          }
-          const float Glast = s.G[(C - 1) * KD + kk];
-          gam_last = ex2(Glast);
-          e_last = ex2(Glast - prev);
-        }
-        // dk-: dkg 2^(G_last - G) + 2^(G_e - G) Cn ;  sum of k dk_end feeds dG at the chunk's last row
-        umma::tmem_ld16(tq + C_DKG + t0, a);
-        umma::tmem_ld16(tq + C_CN + t0, b);
-        umma::tmem_ld_wait();
-        {
-          float dglp = 0.f, fr = 1.f;
+        // part 2: the off-diagonal blocks of phase C, scaled back from their reference rows
+        float b[16];
+        if (blk < 3) {                          // dk-: + 2^(G_e - G) Cn
+          umma::tmem_ld16(tq + C_CN + t0, b);
+          umma::tmem_ld_wait();
+          float fr = 1.f;
 #pragma unroll
           for (int i = 15; i >= 0; --i) {
-            const float dke = a[i] * (e_last * fr);
-            dglp = fmaf(__bfloat162float(s.k[(t0 + i) * KD + kk]), dke, dglp);
-            cn[i] = (blk < 3) ? fmaf(fr, b[i], dke) : dke;
+            cn[i] = fmaf(fr, b[i], cn[i]);
             fr *= lam[i];
           }
-          s.dglp[blk][kk] = dglp;
         }
-        // dq: scale (Gam dqg + L Cq)
-        umma::tmem_ld16(tq + C_DQG + t0, a);
-        umma::tmem_ld16(tq + C_CQ + t0, b);
-        umma::tmem_ld_wait();
-        {
-          float fl = p.scale;
-          const float gs = g_first;
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            fl *= lam[i];
-            float x = (gs * fl) * a[i];
-            if (blk > 0) x = fmaf(fl, b[i], x);
-            cq[i] = x;
-          }
-        }
-        // dk+: Gam beta dbk + L Cp
-        umma::tmem_ld16(tq + C_DBK + t0, a);
-        umma::tmem_ld16(tq + C_CP + t0, b);
-        umma::tmem_ld_wait();
-        {
+        if (blk > 0) {                          // dq: + scale L Cq;  dk+: + L Cp
+          umma::tmem_ld16(tq + C_CQ + t0, b);
+          umma::tmem_ld_wait();
           float fl = 1.f;
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             fl *= lam[i];
-            float x = (g_first * fl) * s.beta[t0 + i] * a[i];
-            if (blk > 0) x = fmaf(fl, b[i], x);
-            cp[i] = x;
+            cq[i] = fmaf(p.scale * fl, b[i], cq[i]);
+          }
+          umma::tmem_ld16(tq + C_CP + t0, b);
+          umma::tmem_ld_wait();
+          fl = 1.f;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            fl *= lam[i];
+            cp[i] = fmaf(fl, b[i], cp[i]);
           }
         }
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          qv[i] = __bfloat162float(s.q[(t0 + i) * KD + kk]);
-          kv[i] = __bfloat162float(s.k[(t0 + i) * KD + kk]);
-        }
       }
-      __syncthreads();       // q, k, G have been read by everybody (and dglp is complete): the next tile's may arrive
-      if (next_idx < total_tiles && tid == 0) fetch_qkg(next_idx, (it + 1) & 1);
       KDA_DBG_CLOCK(dbg, 12);
       // diagonal block, pairwise; D = running product of lam (range-safe)
 #pragma unroll
