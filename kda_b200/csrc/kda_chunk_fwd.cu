@@ -96,70 +96,60 @@ __device__ __forceinline__ float butterfly32(float (&v)[32], int lane) {
   return v[0];
 }
 
-// ---- diagonal 16x16 blocks of Aqk / Akk -------------------------------------------------------------------
-// A warp takes one block b and one half of the key columns; a lane owns two adjacent key columns.  Rows are
-// walked upwards while E_j = k_j 2^(G_t - G_j) is carried per column j as a running product of
-// lam_t = 2^(G_t - G_{t-1}) (every factor <= 1: range-safe, and one ex2 per row instead of one per pair).
-// Row t contributes t+1 values of q_t.E_j and t values of k_t.E_j; rows are grouped so that a group fills at
-// most 32 slots, which butterfly32 then sums over the lanes: lane L ends up with the total of slot L.
-constexpr int DIAG_GROUPS = 10;
-__host__ __device__ constexpr int diag_group(int t) { return t <= 4 ? 0 : (t <= 6 ? 1 : (t <= 8 ? 2 : t - 6)); }
-__host__ __device__ constexpr int diag_base(int t) {      // first slot of row t inside its group
-  return t == 1 ? 1 : (t == 2 ? 4 : (t == 3 ? 9 : (t == 4 ? 16 : (t == 6 ? 11 : (t == 8 ? 15 : 0)))));
-}
-__host__ __device__ constexpr bool diag_last(int t) { return t == 4 || t == 6 || t >= 8; }
+// ---- diagonal 8x8 blocks of Aqk / Akk ------------------------------------------------------------------------
+// Pairwise decay is needed only where no row lies between j and t that both factors could be taken around; with
+// the lower-left 8x8 quarter of every 16x16 diagonal block factored around the block's row 8 (tensor cores, see the
+// kernel), what remains pairwise are the eight 8x8 diagonal blocks.
+// A warp takes one 16-row block b and one half of the key columns; a lane owns two adjacent key columns.  Inside an
+// 8x8 block the rows are walked upwards while E_j = k_j 2^(G_t - G_j) is carried per column j as a running product
+// of lam_t = 2^(G_t - G_{t-1}) (every factor <= 1: range-safe, one ex2 per row instead of one per pair).
+// Row t contributes t+1 values of q_t.E_j and t values of k_t.E_j: slot t*t + j, resp. t*t + t+1 + j, 64 slots per
+// 8x8 block = two groups of 32 that butterfly32 sums over the lanes (lane L ends up with the total of slot L).
+constexpr int DIAG_GROUPS = 4;      // per warp: two 8x8 blocks x two groups
 
 __device__ __forceinline__ void prep_diag_half(const PrepSmem& s, const int b, const int hh, const int lane, float (&res)[DIAG_GROUPS]) {
-  const int r0 = 16 * b, kk = hh * 64 + 2 * lane;
-  float2 E[16];
-  float val[32];
+  const int kk = hh * 64 + 2 * lane;
 #pragma unroll
-  for (int i = 0; i < 32; ++i) val[i] = 0.f;
-  float2 Gprev = make_float2(0.f, 0.f);
+  for (int u = 0; u < 2; ++u) {
+    const int r0 = 16 * b + 8 * u;
+    float2 E[8];
+    float val0[32], val1[32];
+#define KDA_DIAG_VAL(sl) ((sl) < 32 ? val0[(sl) & 31] : val1[(sl) & 31])
+    float2 Gprev = make_float2(0.f, 0.f);
 #pragma unroll
-  for (int t = 0; t < 16; ++t) {
-    const float2 Gt = *reinterpret_cast<const float2*>(&s.G[(r0 + t) * GS + kk]);
-    const float2 qt = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.q[(r0 + t) * QS + kk]));
-    const float2 kt = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.k[(r0 + t) * QS + kk]));
-    if (t > 0) {
-      const float lx = ex2(Gt.x - Gprev.x), ly = ex2(Gt.y - Gprev.y);
+    for (int t = 0; t < 8; ++t) {
+      const float2 Gt = *reinterpret_cast<const float2*>(&s.G[(r0 + t) * GS + kk]);
+      const float2 qt = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.q[(r0 + t) * QS + kk]));
+      const float2 kt = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.k[(r0 + t) * QS + kk]));
+      if (t > 0) {
+        const float lx = ex2(Gt.x - Gprev.x), ly = ex2(Gt.y - Gprev.y);
 #pragma unroll
-      for (int j = 0; j < t; ++j) {
-        E[j].x *= lx;
-        E[j].y *= ly;
+        for (int j = 0; j < t; ++j) {
+          E[j].x *= lx;
+          E[j].y *= ly;
+        }
       }
+      Gprev = Gt;
+      E[t] = kt;
+#pragma unroll
+      for (int j = 0; j <= t; ++j) KDA_DIAG_VAL(t * t + j) = fmaf(qt.y, E[j].y, qt.x * E[j].x);
+#pragma unroll
+      for (int j = 0; j < t; ++j) KDA_DIAG_VAL(t * t + t + 1 + j) = fmaf(kt.y, E[j].y, kt.x * E[j].x);
+      if (t == 5) res[2 * u] = butterfly32(val0, lane);      // slots 0..31 are complete (row 5 ends at slot 35)
     }
-    Gprev = Gt;
-    E[t] = kt;
-    const int base = diag_base(t);
-#pragma unroll
-    for (int j = 0; j <= t; ++j) val[base + j] = fmaf(qt.y, E[j].y, qt.x * E[j].x);
-#pragma unroll
-    for (int j = 0; j < t; ++j) val[base + t + 1 + j] = fmaf(kt.y, E[j].y, kt.x * E[j].x);
-    if (diag_last(t)) {
-      res[diag_group(t)] = butterfly32(val, lane);
-#pragma unroll
-      for (int i = 0; i < 32; ++i) val[i] = 0.f;
-    }
+    res[2 * u + 1] = butterfly32(val1, lane);
+#undef KDA_DIAG_VAL
   }
 }
 
-// Which (row, column, matrix) the value of lane L in group g is.  row < 0: unused slot.
+// Which (row, column, matrix) of the 16x16 block the value of lane L in group g is.
 __device__ __forceinline__ void diag_decode(const int g, const int L, int& row, int& col, bool& is_kk) {
-  row = -1;
-  col = 0;
-  is_kk = false;
-#pragma unroll
-  for (int t = 0; t < 16; ++t) {
-    if (diag_group(t) == g) {
-      const int off = L - diag_base(t);
-      if (off >= 0 && off < 2 * t + 1) {
-        row = t;
-        is_kk = off > t;
-        col = is_kk ? off - (t + 1) : off;
-      }
-    }
-  }
+  const int u = g >> 1, sl = 32 * (g & 1) + L;
+  const int t = (sl >= 49) ? 7 : (sl >= 36) ? 6 : (sl >= 25) ? 5 : (sl >= 16) ? 4 : (sl >= 9) ? 3 : (sl >= 4) ? 2 : (sl >= 1) ? 1 : 0;
+  const int off = sl - t * t;
+  is_kk = off > t;
+  row = 8 * u + t;
+  col = 8 * u + (is_kk ? off - t - 1 : off);
 }
 
 __global__ void __launch_bounds__(256, 2) kda_chunk_prepare_kernel(const PrepParams p) {
@@ -239,7 +229,7 @@ __global__ void __launch_bounds__(256, 2) kda_chunk_prepare_kernel(const PrepPar
   __syncthreads();
 
   KDA_DBG_CLOCK(p.dbg, 18);
-  // ---- P3a: diagonal 16x16 blocks, pairwise decay as running products (never a factorisation: range-safe).
+  // ---- P3a: diagonal 8x8 blocks, pairwise decay as running products (never a factorisation there: range-safe).
   // Warp = (block, key half).  The halves meet in the v buffer, whose load is issued only afterwards.
   {
     const int b = warp & 3, hh = warp >> 2, r0 = 16 * b;
@@ -258,7 +248,7 @@ __global__ void __launch_bounds__(256, 2) kda_chunk_prepare_kernel(const PrepPar
         bool is_kk;
         diag_decode(g, lane, row, col, is_kk);
         const float x = res[g] + scratch[g * 32 + lane];
-        if (row >= 0) {
+        {
           if (is_kk) s.Akk[(r0 + row) * AS + r0 + col] = x;                            // raw; beta_t is applied later
           else s.Aqk[(r0 + row) * TS + r0 + col] = __float2bfloat16_rn(p.scale * x);
         }
@@ -277,7 +267,8 @@ __global__ void __launch_bounds__(256, 2) kda_chunk_prepare_kernel(const PrepPar
   KDA_DBG_CLOCK(p.dbg, 19);
   // ---- P3b: off-diagonal 16x16 blocks on tensor cores.  For row block I the decay is factored around
   // the block's first row r0 = 16 I:  exp2(G_t - G_r0) * exp2(G_r0 - G_j), both factors <= 1 for j < r0 <= t.
-  // Six units (I, 16 columns j): I=1 -> 1, I=2 -> 2, I=3 -> 3; warps 0..5 take one each.
+  // Six units (I, 16 columns j): I=1 -> 1, I=2 -> 2, I=3 -> 3; warps 0..5 take one each.  Warps 6 and 7 take the
+  // lower-left 8x8 quarters of the four diagonal blocks (rows 16b+8.., columns 16b..16b+7, factored around row 16b+8).
   if (warp < 6) {
     const int I = (warp < 1) ? 1 : (warp < 3 ? 2 : 3);
     const int np = (warp < 1) ? 0 : (warp < 3 ? warp - 1 : warp - 3);
@@ -330,6 +321,42 @@ __global__ void __launch_bounds__(256, 2) kda_chunk_prepare_kernel(const PrepPar
       *reinterpret_cast<uint32_t*>(&s.Aqk[tb * TS + col]) = pack_bf16(p.scale * cq[n][2], p.scale * cq[n][3]);
       *reinterpret_cast<float2*>(&s.Akk[ta * AS + col]) = make_float2(ck[n][0], ck[n][1]);
       *reinterpret_cast<float2*>(&s.Akk[tb * AS + col]) = make_float2(ck[n][2], ck[n][3]);
+    }
+  } else {
+#pragma unroll 1
+    for (int bb = 0; bb < 2; ++bb) {
+      const int b = 2 * (warp - 6) + bb;
+      const int r0 = 16 * b + 8, ta = r0 + gid, ja = 16 * b + gid;      // m16 tile: rows gid real, rows gid + 8 a copy
+      float cq[4] = {0.f, 0.f, 0.f, 0.f}, ck[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 2
+      for (int ks = 0; ks < 8; ++ks) {
+        const int k0 = ks * 16 + tig * 2, k1 = k0 + 8;
+        const float2 R0 = *reinterpret_cast<const float2*>(&s.G[r0 * GS + k0]);
+        const float2 R1 = *reinterpret_cast<const float2*>(&s.G[r0 * GS + k1]);
+        const float2 Ga0 = *reinterpret_cast<const float2*>(&s.G[ta * GS + k0]);
+        const float2 Ga1 = *reinterpret_cast<const float2*>(&s.G[ta * GS + k1]);
+        const float ea0x = ex2(Ga0.x - R0.x), ea0y = ex2(Ga0.y - R0.y), ea1x = ex2(Ga1.x - R1.x), ea1y = ex2(Ga1.y - R1.y);
+        const float2 qa0 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.q[ta * QS + k0]));
+        const float2 qa1 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.q[ta * QS + k1]));
+        const float2 ka0 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.k[ta * QS + k0]));
+        const float2 ka1 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.k[ta * QS + k1]));
+        uint32_t aq[4], ak[4];
+        aq[0] = aq[1] = pack_bf16(qa0.x * ea0x, qa0.y * ea0y);
+        aq[2] = aq[3] = pack_bf16(qa1.x * ea1x, qa1.y * ea1y);
+        ak[0] = ak[1] = pack_bf16(ka0.x * ea0x, ka0.y * ea0y);
+        ak[2] = ak[3] = pack_bf16(ka1.x * ea1x, ka1.y * ea1y);
+        const float2 Gj0 = *reinterpret_cast<const float2*>(&s.G[ja * GS + k0]);
+        const float2 Gj1 = *reinterpret_cast<const float2*>(&s.G[ja * GS + k1]);
+        const float2 kj0 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.k[ja * QS + k0]));
+        const float2 kj1 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.k[ja * QS + k1]));
+        const uint32_t b0 = pack_bf16(kj0.x * ex2(R0.x - Gj0.x), kj0.y * ex2(R0.y - Gj0.y));
+        const uint32_t b1 = pack_bf16(kj1.x * ex2(R1.x - Gj1.x), kj1.y * ex2(R1.y - Gj1.y));
+        mma16816(cq, aq, b0, b1);
+        mma16816(ck, ak, b0, b1);
+      }
+      const int col = 16 * b + tig * 2;
+      *reinterpret_cast<uint32_t*>(&s.Aqk[ta * TS + col]) = pack_bf16(p.scale * cq[0], p.scale * cq[1]);
+      *reinterpret_cast<float2*>(&s.Akk[ta * AS + col]) = make_float2(ck[0], ck[1]);
     }
   }
   __syncthreads();
