@@ -89,14 +89,17 @@ def _gated_inputs(T, seed, B=1, H=2):
     return d
 
 
+@pytest.mark.parametrize("raw_dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("lb", [None, -5.0])
-def test_chunk_kda_with_gate_in_kernel(lb):
-    """The operator as the layer calls it (raw gate, beta logits, l2norm in kernel), forward and every gradient
+def test_chunk_kda_with_gate_in_kernel(lb, raw_dtype):
+    """bf16 raw gate input: the chunk kernels apply the activation themselves; fp32: the gate kernel runs first.
+    The operator as the layer calls it (raw gate, beta logits, l2norm in kernel), forward and every gradient
     including A_log and dt_bias, against float64 autograd through oracle gate + oracle recurrence (bf16 mode:
     2e-2 max-normalised and cosine 0.9999; dA_log and ddt_bias are sums over all tokens of the bf16-noisy dg with
     heavy cancellation, so the element noise of dg shows up amplified there: 5e-2 and cosine 0.999 for those)."""
     from kda_b200 import chunk_kda
     d = _gated_inputs(200, 41)
+    d["g_raw"] = d["g_raw"].to(raw_dtype)
     names = ("q", "k", "v", "g_raw", "beta_raw", "A_log", "dt_bias", "h0")
     lo = {n: d[n].double().requires_grad_(True) for n in names}
     o_ref, ht_ref = recurrent_kda(lo["q"], lo["k"], lo["v"], kda_gate(lo["g_raw"], lo["A_log"], lo["dt_bias"], lower_bound=lb),
