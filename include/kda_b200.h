@@ -31,7 +31,7 @@ extern "C" {
 #pragma GCC visibility push(default) /* the entry points below are the library's only exports */
 #endif
 
-#define KDA_B200_ABI_VERSION 2
+#define KDA_B200_ABI_VERSION 3
 #define KDA_CHUNK 64 /* tokens per chunk of the chunked kernels */
 
 /* io_dtype of q, k, v, o and of their gradients */
@@ -82,6 +82,8 @@ typedef struct kda_recurrent_args {
   float scale;
   const int32_t* num_accepted_tokens; /* device [N] or NULL: speculative decoding, see state_indices */
   int32_t state_indices_stride;       /* elements between two sequences' rows of state_indices (>= 1 when it is used) */
+  int32_t transpose_state;            /* nonzero: states are [slots, H, V, K] (K contiguous), fla's transpose_state_layout;
+                                         K in {64, 128} */
 } kda_recurrent_args;
 
 int kda_recurrent_fwd(const kda_recurrent_args* args, void* stream);
@@ -167,6 +169,16 @@ int kda_chunk_bwd(const kda_chunk_args* args, void* stream);
  * ------------------------------------------------------------------------------------------------ */
 #define KDA_NOALLOC_SCRATCH_BYTES (32u << 20)
 int kda_chunk_fwd_noalloc(const kda_chunk_args* args, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Intermediate states for inference engines: chunk_kda(..., return_intermediate_states=True)
+ * (fla/ops/kda/chunk.py:95-98; fla/ops/common/chunk_delta_h.py stores the state at the START of every chunk).
+ * Reads the workspace of a kda_chunk_fwd call made with save_for_backward != 0 (same tokens, N, H) and writes
+ * h_out [chunks, H, K, V] bf16, chunks in sequence order (a sequence of length L owns ceil(L / 64) of them).
+ * h_out must hold kda_chunk_max_chunks(tokens, N) * H * 128 * 128 elements; chunks beyond the real count stay untouched.
+ * ------------------------------------------------------------------------------------------------ */
+int kda_chunk_export_states(const void* workspace, size_t workspace_bytes, int64_t tokens, int32_t N, int32_t H, void* h_out,
+                            void* stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Gate front end: the decay activation and the beta sigmoid that the layer applies in front of the

@@ -11,7 +11,7 @@ LIB_PATH = os.path.join(PKG, "libkda_b200.so")
 
 KDA_BF16, KDA_FP32 = 0, 1
 NOALLOC_SCRATCH_BYTES = 32 << 20
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 
 class RecurrentArgs(C.Structure):
@@ -21,7 +21,7 @@ class RecurrentArgs(C.Structure):
         ("state_indices", C.c_void_p),
         ("tokens", C.c_int64), ("N", C.c_int32), ("T", C.c_int32), ("H", C.c_int32), ("K", C.c_int32),
         ("V", C.c_int32), ("io_dtype", C.c_int32), ("use_qk_l2norm", C.c_int32), ("scale", C.c_float),
-        ("num_accepted_tokens", C.c_void_p), ("state_indices_stride", C.c_int32),
+        ("num_accepted_tokens", C.c_void_p), ("state_indices_stride", C.c_int32), ("transpose_state", C.c_int32),
     ]
 
 
@@ -55,7 +55,8 @@ class GateArgs(C.Structure):
 EXPORTS = (
     "kda_b200_abi_version", "kda_b200_strerror", "kda_recurrent_fwd",
     "kda_chunk_max_chunks", "kda_chunk_workspace_bytes", "kda_chunk_bwd_workspace_bytes",
-    "kda_chunk_fwd", "kda_chunk_bwd", "kda_chunk_fwd_noalloc", "kda_gate_bwd_workspace_bytes", "kda_gate_fwd", "kda_gate_bwd",
+    "kda_chunk_fwd", "kda_chunk_bwd", "kda_chunk_fwd_noalloc", "kda_chunk_export_states",
+    "kda_gate_bwd_workspace_bytes", "kda_gate_fwd", "kda_gate_bwd",
     "kda_b200_profile_enable", "kda_b200_profile_read",
 )
 
@@ -87,6 +88,8 @@ def load() -> C.CDLL:
         fn = getattr(lib, name)
         fn.restype = C.c_int
         fn.argtypes = [C.POINTER(ChunkArgs), C.c_void_p]
+    lib.kda_chunk_export_states.restype = C.c_int
+    lib.kda_chunk_export_states.argtypes = [C.c_void_p, C.c_size_t, C.c_int64, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]
     lib.kda_gate_bwd_workspace_bytes.restype = C.c_size_t
     lib.kda_gate_bwd_workspace_bytes.argtypes = [C.c_int64, C.c_int32, C.c_int32]
     for name in ("kda_gate_fwd", "kda_gate_bwd"):

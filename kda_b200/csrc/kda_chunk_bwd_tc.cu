@@ -410,8 +410,10 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __g
     umma::fence_after_sync();
     KDA_DBG_CLOCK(dbg, 5);
     if (alive) {
-      float v[16];
+      float v[16], v2[16], v3[16];                     // the three loads are in flight together
       umma::tmem_ld16(tq + C_DAQ + 16 * part, v);      // dTm rows (M = 64 layout): scale the columns by beta_j
+      umma::tmem_ld16(tq + C_DTT + 16 * part, v2);     // dTm_raw^T rows j: dbeta_j += sum_t' Tm[t'][j] dTm_raw[t'][j]
+      umma::tmem_ld16(tq + C_DBV + 16 * part, v3);     // dbv^T rows v: dv[t][v] = beta_t dbv[t][v]
       umma::tmem_ld_wait();
       if (lane < 16) {
         const int t = 16 * q4 + lane;
@@ -420,27 +422,23 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __g
         *reinterpret_cast<uint4*>(sw_piece(sDT, t, 2 * part)) = pack8(&v[0]);
         *reinterpret_cast<uint4*>(sw_piece(sDT, t, 2 * part + 1)) = pack8(&v[8]);
       }
-      umma::tmem_ld16(tq + C_DTT + 16 * part, v);      // dTm_raw^T rows j: dbeta_j += sum_t' Tm[t'][j] dTm_raw[t'][j]
-      umma::tmem_ld_wait();
       if (lane < 16) {
         const int j = 16 * q4 + lane;
         float acc = 0.f;
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           const int t2 = 16 * part + i;
-          acc += v[i] * __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(s.TI + umma::sw128(t2, j)));
+          acc += v2[i] * __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(s.TI + umma::sw128(t2, j)));
         }
         s.dbp[part][j] = acc;
       }
-      umma::tmem_ld16(tq + C_DBV + 16 * part, v);      // dbv^T rows v: dv[t][v] = beta_t dbv[t][v]
-      umma::tmem_ld_wait();
       {
         const int vcol = 32 * q4 + lane;
+        __nv_bfloat16* const dvp = p.dv + (static_cast<size_t>(ci.tok0 + 16 * part) * p.H + h) * VD + vcol;
+        const size_t tstride = static_cast<size_t>(p.H) * VD;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int t = 16 * part + i;
-          if (t < len) p.dv[(static_cast<size_t>(ci.tok0 + t) * p.H + h) * VD + vcol] = __float2bfloat16_rn(s.beta[t] * v[i]);
-        }
+        for (int i = 0; i < 16; ++i)
+          if (16 * part + i < len) dvp[i * tstride] = __float2bfloat16_rn(s.beta[16 * part + i] * v3[i]);
       }
     }
     fence_proxy_async();

@@ -33,6 +33,21 @@ template <> struct IoTraits<__nv_bfloat16> {
 
 constexpr int REC_WARPS = 4;
 
+// Sum over the 32 lanes of 32 per-lane values at once: lane L returns the total of v[L] (31 shuffles).
+__device__ __forceinline__ float butterfly_sum32(float (&v)[32], int lane) {
+#pragma unroll
+  for (int o = 16; o >= 1; o >>= 1) {
+    const bool up = (lane & o) != 0;
+#pragma unroll
+    for (int i = 0; i < o; ++i) {
+      const float mine = up ? v[i + o] : v[i];
+      const float other = up ? v[i] : v[i + o];
+      v[i] = mine + __shfl_xor_sync(0xffffffffu, other, o);
+    }
+  }
+  return v[0];
+}
+
 template <typename IO, int K, int VS>
 __global__ void __launch_bounds__(REC_WARPS * 32) kda_recurrent_kernel(const kda_recurrent_args a) {
   constexpr int CL = VS / 4;      // lanes across the V slice (4 columns each)
@@ -163,6 +178,145 @@ __global__ void __launch_bounds__(REC_WARPS * 32) kda_recurrent_kernel(const kda
   }
 }
 
+// E (2 or 4) consecutive floats of a state row, streaming loads / stores of 8 or 16 bytes
+template <int E>
+__device__ __forceinline__ void ld_row(float (&d)[E], const float* p) {
+  if constexpr (E == 4) {
+    const float4 x = __ldcs(reinterpret_cast<const float4*>(p));
+    d[0] = x.x; d[1] = x.y; d[2] = x.z; d[3] = x.w;
+  } else {
+    const float2 x = __ldcs(reinterpret_cast<const float2*>(p));
+    d[0] = x.x; d[1] = x.y;
+  }
+}
+template <int E>
+__device__ __forceinline__ void st_row(float* p, const float (&d)[E]) {
+  if constexpr (E == 4) __stcs(reinterpret_cast<float4*>(p), make_float4(d[0], d[1], d[2], d[3]));
+  else __stcs(reinterpret_cast<float2*>(p), make_float2(d[0], d[1]));
+}
+
+// ---- transposed state layout [slots, H, V, K] (K contiguous) ------------------------------------------------------
+// One warp owns (sequence, head, 32 value rows); a lane holds the 32 x (K / 32) slice of key columns
+// lane*(K/32) .. of those rows, so every state access is again contiguous over the warp.  The two reductions over K
+// are per-lane partial dot products summed over the lanes 32 values at a time by a butterfly (lane L ends up with
+// the total of value row L); the delta-rule update needs every row's dv in every lane: one shuffle per row.
+template <typename IO, int K>
+__global__ void __launch_bounds__(REC_WARPS * 32) kda_recurrent_t_kernel(const kda_recurrent_args a) {
+  constexpr int E = K / 32;       // key columns per lane
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nvs = a.V / 32;
+  const long long wid = static_cast<long long>(blockIdx.x) * REC_WARPS + warp;
+  const long long total = static_cast<long long>(a.N) * a.H * nvs;
+  if (wid >= total) return;
+  const int vs = static_cast<int>(wid % nvs);
+  const int h = static_cast<int>((wid / nvs) % a.H);
+  const int n = static_cast<int>(wid / (static_cast<long long>(nvs) * a.H));
+  long long bos, eos;
+  if (a.cu_seqlens) {
+    bos = a.cu_seqlens[n];
+    eos = a.cu_seqlens[n + 1];
+  } else {
+    bos = static_cast<long long>(n) * a.T;
+    eos = bos + a.T;
+  }
+  const int32_t* slots = a.state_indices ? a.state_indices + static_cast<size_t>(n) * a.state_indices_stride : nullptr;
+  const long long slot = slots ? slots[a.num_accepted_tokens ? a.num_accepted_tokens[n] - 1 : 0] : n;
+  auto state_ptr = [&](const float* base, long long sl) {
+    return base + ((static_cast<size_t>(sl) * a.H + h) * a.V + vs * 32) * K + lane * E;
+  };
+  float S[32][E];
+  if (a.h0) {
+    const float* p0 = state_ptr(a.h0, slot);
+#pragma unroll
+    for (int r = 0; r < 32; ++r) ld_row<E>(S[r], p0 + static_cast<size_t>(r) * K);
+  } else {
+#pragma unroll
+    for (int r = 0; r < 32; ++r)
+#pragma unroll
+      for (int e = 0; e < E; ++e) S[r][e] = 0.f;
+  }
+  const IO* qp = static_cast<const IO*>(a.q);
+  const IO* kp = static_cast<const IO*>(a.k);
+  const IO* vp = static_cast<const IO*>(a.v);
+  IO* op = static_cast<IO*>(a.o);
+  for (long long t = bos; t < eos; ++t) {
+    const size_t rowk = (static_cast<size_t>(t) * a.H + h) * K + lane * E;
+    float qf[E], kf[E], eg[E];
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      qf[e] = IoTraits<IO>::ld(qp + rowk + e);
+      kf[e] = IoTraits<IO>::ld(kp + rowk + e);
+      eg[e] = expf(__ldg(a.g + rowk + e));
+    }
+    float qs = a.scale;
+    if (a.use_qk_l2norm) {
+      float sq = 0.f, sk = 0.f;
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        sq += qf[e] * qf[e];
+        sk += kf[e] * kf[e];
+      }
+      sq = warp_sum(sq);
+      sk = warp_sum(sk);
+      qs *= rsqrtf(sq + L2NORM_EPS);
+      const float ks = rsqrtf(sk + L2NORM_EPS);
+#pragma unroll
+      for (int e = 0; e < E; ++e) kf[e] *= ks;
+    }
+#pragma unroll
+    for (int e = 0; e < E; ++e) qf[e] *= qs;
+    const float beta = __ldg(a.beta + static_cast<size_t>(t) * a.H + h);
+    const float vt = IoTraits<IO>::ld(vp + (static_cast<size_t>(t) * a.H + h) * a.V + vs * 32 + lane);      // value row `lane`
+    float part[32];
+#pragma unroll
+    for (int r = 0; r < 32; ++r) {
+      float acc = 0.f;
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        S[r][e] *= eg[e];
+        acc = fmaf(kf[e], S[r][e], acc);
+      }
+      part[r] = acc;
+    }
+    const float hk = butterfly_sum32(part, lane);            // S^T k for value row `lane`
+    const float dv = beta * (vt - hk);
+#pragma unroll
+    for (int r = 0; r < 32; ++r) {
+      const float dvr = __shfl_sync(0xffffffffu, dv, r);
+      float acc = 0.f;
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        S[r][e] = fmaf(kf[e], dvr, S[r][e]);
+        acc = fmaf(qf[e], S[r][e], acc);
+      }
+      part[r] = acc;
+    }
+    const float o = butterfly_sum32(part, lane);
+    if (sizeof(IO) == 2) reinterpret_cast<__nv_bfloat16*>(op)[(static_cast<size_t>(t) * a.H + h) * a.V + vs * 32 + lane] = __float2bfloat16_rn(o);
+    else reinterpret_cast<float*>(op)[(static_cast<size_t>(t) * a.H + h) * a.V + vs * 32 + lane] = o;
+    if (slots && a.ht) {
+      float* pt = const_cast<float*>(state_ptr(a.ht, slots[t - bos]));
+#pragma unroll
+      for (int r = 0; r < 32; ++r) st_row<E>(pt + static_cast<size_t>(r) * K, S[r]);
+    }
+  }
+  if (a.ht && !slots) {
+    float* pt = const_cast<float*>(state_ptr(a.ht, slot));
+#pragma unroll
+    for (int r = 0; r < 32; ++r) st_row<E>(pt + static_cast<size_t>(r) * K, S[r]);
+  }
+}
+
+template <typename IO, int K>
+static int launch_rec_t(const kda_recurrent_args& a, cudaStream_t st) {
+  const long long total = static_cast<long long>(a.N) * a.H * (a.V / 32);
+  const long long blocks = (total + REC_WARPS - 1) / REC_WARPS;
+  if (blocks <= 0) return KDA_OK;
+  if (blocks > 0x7fffffffLL) return KDA_E_SHAPE;
+  kda_recurrent_t_kernel<IO, K><<<static_cast<unsigned>(blocks), REC_WARPS * 32, 0, st>>>(a);
+  return static_cast<int>(cudaGetLastError());
+}
+
 template <typename IO, int K, int VS>
 static int launch_rec(const kda_recurrent_args& a, cudaStream_t st) {
   const long long total = static_cast<long long>(a.N) * a.H * (a.V / VS);
@@ -175,6 +329,13 @@ static int launch_rec(const kda_recurrent_args& a, cudaStream_t st) {
 
 template <typename IO>
 static int dispatch_rec(const kda_recurrent_args& a, cudaStream_t st) {
+  if (a.transpose_state) {
+    switch (a.K) {
+      case 64: return launch_rec_t<IO, 64>(a, st);
+      case 128: return launch_rec_t<IO, 128>(a, st);
+      default: return KDA_E_SHAPE;
+    }
+  }
   switch (a.K) {
     case 32: return launch_rec<IO, 32, 32>(a, st);
     case 64: return launch_rec<IO, 64, 32>(a, st);

@@ -226,9 +226,11 @@ def fused_recurrent_kda_fwd(q, k, v, g, beta, A_log=None, dt_bias=None, initial_
     With `inplace_final_state` the kernel writes states over `initial_state` and returns that tensor.
     Continuous batching: `ssm_state_indices` [N] or [N, T] names the state slot of every token; a sequence starts
     from the slot of its first token -- with `num_accepted_tokens` [N] (speculative decoding) from the slot of its
-    last accepted token -- and the state after token t lands in slot `ssm_state_indices[n, t]`."""
-    _unsupported("transpose_state_layout", transpose_state_layout, False)
+    last accepted token -- and the state after token t lands in slot `ssm_state_indices[n, t]`.
+    `transpose_state_layout`: states are [N, H, V, K] instead of [N, H, K, V] (K = 64 or 128)."""
     B, T, H, K, V = _check_common(q, k, v, g, beta, None, cu_seqlens)
+    if transpose_state_layout and K not in (64, 128):
+        raise NotImplementedError(f"kda_b200: transpose_state_layout needs K = 64 or 128, got {K}")
     if scale is None:
         scale = K ** -0.5
     dev = q.device
@@ -249,7 +251,7 @@ def fused_recurrent_kda_fwd(q, k, v, g, beta, A_log=None, dt_bias=None, initial_
             raise ValueError("inplace_final_state needs a contiguous fp32 initial_state")
         ht = h0
     elif output_final_state:
-        ht = torch.empty(N, H, K, V, dtype=torch.float32, device=dev)
+        ht = torch.empty((N, H, V, K) if transpose_state_layout else (N, H, K, V), dtype=torch.float32, device=dev)
     else:
         ht = None
     idx, acc, stride = None, None, 0
@@ -275,7 +277,7 @@ def fused_recurrent_kda_fwd(q, k, v, g, beta, A_log=None, dt_bias=None, initial_
         q=_ptr(q), k=_ptr(k), v=_ptr(v), g=_ptr(g), beta=_ptr(beta), h0=_ptr(h0), ht=_ptr(ht), o=_ptr(o),
         cu_seqlens=_ptr(cu), state_indices=_ptr(idx), tokens=B * T, N=N, T=T, H=H, K=K, V=V,
         io_dtype=_DT[q.dtype], use_qk_l2norm=int(bool(use_qk_l2norm_in_kernel)), scale=float(scale),
-        num_accepted_tokens=_ptr(acc), state_indices_stride=stride)
+        num_accepted_tokens=_ptr(acc), state_indices_stride=stride, transpose_state=int(bool(transpose_state_layout)))
     with torch.cuda.device(dev):
         _lib.check(_lib.load().kda_recurrent_fwd(C.byref(args), _stream(dev)), "kda_recurrent_fwd")
     return o, ht
@@ -289,8 +291,7 @@ def fused_recurrent_kda(q, k, v, g, beta, A_log=None, dt_bias=None, scale=None, 
     """Drop-in for fla.ops.kda.fused_recurrent_kda (fla/ops/kda/fused_recurrent.py:329-452): forward only.
     q,k [B,T,H,K]; v [B,T,H,V]; g [B,T,H,K] log-decay (raw gate input with `use_gate_in_kernel`, activated with
     `A_log`, `dt_bias`, `lower_bound` as in chunk_kda); beta [B,T,H] (logits with `use_beta_sigmoid_in_kernel`);
-    initial_state [N,H,K,V] fp32.  Returns (o, final_state or None)."""
-    _unsupported("transpose_state_layout", transpose_state_layout, False)
+    initial_state [N,H,K,V] fp32 ([N,H,V,K] with `transpose_state_layout`).  Returns (o, final_state or None)."""
     if "use_qk_l2norm" in kwargs:
         use_qk_l2norm_in_kernel = kwargs.pop("use_qk_l2norm")
     _check_common(q, k, v, g, beta, initial_state, cu_seqlens)
@@ -299,7 +300,8 @@ def fused_recurrent_kda(q, k, v, g, beta, A_log=None, dt_bias=None, scale=None, 
     return fused_recurrent_kda_fwd(q, k, v, g, beta, A_log=A_log, dt_bias=dt_bias, initial_state=initial_state, scale=scale,
                                    output_final_state=output_final_state, inplace_final_state=False, cu_seqlens=cu_seqlens,
                                    use_qk_l2norm_in_kernel=use_qk_l2norm_in_kernel, use_gate_in_kernel=use_gate_in_kernel,
-                                   use_beta_sigmoid_in_kernel=use_beta_sigmoid_in_kernel, lower_bound=lower_bound)
+                                   use_beta_sigmoid_in_kernel=use_beta_sigmoid_in_kernel, lower_bound=lower_bound,
+                                   transpose_state_layout=transpose_state_layout)
 
 
 # =================================================================================================
@@ -374,6 +376,37 @@ class ChunkKDAFunction(torch.autograd.Function):
         return dq, dk, dv, dg.to(g_dtype), dbeta.to(beta_dtype), None, dh0, None, None, None
 
 
+def _chunk_fwd_with_states(q, k, v, g, beta, scale, initial_state, output_final_state, use_l2norm, cu_seqlens):
+    """Forward for inference engines (fla/ops/kda/chunk.py:95-98): also returns h, the state at the start of every
+    chunk, [B, NT, H, K, V] bf16 (NT chunks per sequence; with cu_seqlens B = 1 and NT counts all chunks)."""
+    B, T, H, K = q.shape
+    V = v.shape[-1]
+    dev = q.device
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    g32, beta32 = g.contiguous().float(), beta.contiguous().float()
+    h0 = initial_state.contiguous() if initial_state is not None else None
+    if cu_seqlens is None:
+        N, cu = B, _fixed_cu_seqlens(B, T, dev)
+        nt_shape = (B, (T + CHUNK - 1) // CHUNK)
+    else:
+        cu = _as_i32(cu_seqlens, dev)
+        N = cu.numel() - 1
+        lens = (cu[1:] - cu[:-1]).cpu()                       # the output shape depends on the lengths: one host read
+        nt_shape = (1, int(((lens + CHUNK - 1) // CHUNK).sum()))
+    tokens = B * T
+    lib = _lib.load()
+    ws = torch.empty(lib.kda_chunk_workspace_bytes(tokens, N, H, K, V, 1), dtype=torch.uint8, device=dev)
+    o = torch.empty_like(v)
+    ht = torch.empty(N, H, K, V, dtype=torch.float32, device=dev) if output_final_state else None
+    hbuf = torch.empty(lib.kda_chunk_max_chunks(tokens, N), H, K, V, dtype=torch.bfloat16, device=dev)
+    args = _chunk_args(q, k, v, g32, beta32, h0, cu, o, ht, ws, N, H, K, V, tokens, use_l2norm, True, scale)
+    with torch.cuda.device(dev):
+        _lib.check(lib.kda_chunk_fwd(C.byref(args), _stream(dev)), "kda_chunk_fwd")
+        _lib.check(lib.kda_chunk_export_states(_ptr(ws), ws.numel(), tokens, N, H, _ptr(hbuf), _stream(dev)), "kda_chunk_export_states")
+    nt = nt_shape[0] * nt_shape[1]
+    return o, ht, hbuf[:nt].view(nt_shape[0], nt_shape[1], H, K, V)
+
+
 @torch.compiler.disable
 def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False,
               use_qk_l2norm_in_kernel=False, use_gate_in_kernel=False, use_beta_sigmoid_in_kernel=False,
@@ -386,15 +419,15 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
     (and optionally `dt_bias` [H*K]) are keyword arguments: g = -exp(A_log) softplus(g + dt_bias), or, with
     `lower_bound`, lower_bound * sigmoid(exp(A_log) (g + dt_bias)); with `use_beta_sigmoid_in_kernel=True` beta
     holds logits.  Returns (o, final_state or None); differentiable w.r.t. q, k, v, g, beta, initial_state,
-    A_log and dt_bias.
+    A_log and dt_bias.  With `return_intermediate_states=True` (inference mode only) a third value h
+    [B, NT, H, K, V] bf16 holds the state at the start of every chunk.  `transpose_state_layout`: every state
+    tensor is [.., V, K] instead of [.., K, V].
 
     bf16 inputs with K = V = 128 take the chunked tensor-core kernels.  float32 inputs take the exact
     token-recurrent fp32 kernel (forward only).  `safe_gate` and `disable_recompute` only select
     faster variants upstream and are accepted as no-ops (the kernels here are range-safe for any gate);
     options that change results and are not built raise.
     """
-    _unsupported("return_intermediate_states", return_intermediate_states, False)
-    _unsupported("transpose_state_layout", transpose_state_layout, False)
     _unsupported("cp_context", cp_context, None)
     if "use_qk_l2norm" in kwargs:
         use_qk_l2norm_in_kernel = kwargs.pop("use_qk_l2norm")
@@ -412,11 +445,28 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
             raise NotImplementedError("kda_b200: the float32 path is forward-only; use bfloat16 inputs for training")
         return fused_recurrent_kda_fwd(q, k, v, g, beta, initial_state=initial_state, scale=scale,
                                        output_final_state=output_final_state, inplace_final_state=False,
-                                       use_qk_l2norm_in_kernel=use_qk_l2norm_in_kernel, cu_seqlens=cu_seqlens)
+                                       use_qk_l2norm_in_kernel=use_qk_l2norm_in_kernel, cu_seqlens=cu_seqlens,
+                                       transpose_state_layout=transpose_state_layout)
     if K != 128 or V != 128:
         raise NotImplementedError(f"kda_b200: the bf16 chunked kernels are built for K = V = 128, got K={K}, V={V}")
-    return ChunkKDAFunction.apply(q, k, v, g, beta, float(scale), initial_state, bool(output_final_state),
-                                  bool(use_qk_l2norm_in_kernel), cu_seqlens)
+    # transposed state layout ([N, H, V, K]): the chunk kernels keep [N, H, K, V]; states cross the boundary once per
+    # sequence, so they are transposed there (differentiably)
+    tr = (lambda t: t.transpose(-1, -2)) if transpose_state_layout else (lambda t: t)
+    if initial_state is not None:
+        initial_state = tr(initial_state)
+    if return_intermediate_states:
+        assert torch.is_inference_mode_enabled(), "return_intermediate_states is only allowed in inference mode"
+        assert disable_recompute is False, "return_intermediate_states must be used with disable_recompute=False"
+        o, ht, h = _chunk_fwd_with_states(q, k, v, g, beta, float(scale), initial_state, bool(output_final_state),
+                                          bool(use_qk_l2norm_in_kernel), cu_seqlens)
+        if transpose_state_layout:
+            ht, h = (tr(ht).contiguous() if ht is not None else None), tr(h).contiguous()
+        return o, ht, h
+    o, ht = ChunkKDAFunction.apply(q, k, v, g, beta, float(scale), initial_state, bool(output_final_state),
+                                   bool(use_qk_l2norm_in_kernel), cu_seqlens)
+    if transpose_state_layout and ht is not None:
+        ht = tr(ht).contiguous()
+    return o, ht
 
 
 def default_scale(K: int) -> float:

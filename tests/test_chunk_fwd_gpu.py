@@ -102,3 +102,39 @@ def test_chunk_matches_recurrent_kernel_at_production_slice():
         ro, rh = fused_recurrent_kda(d["q"].float(), d["k"].float(), d["v"].float(), d["g"], d["beta"],
                                      initial_state=d["h0"], output_final_state=True)
     _check(o, ht, ro, rh)
+
+
+def test_return_intermediate_states():
+    """h[b, i] = the state at the start of chunk i (fla/ops/kda/chunk.py:95-98), against the fp64 oracle run on the
+    prefix of the sequence; equal-length batch and packed varlen."""
+    from kda_b200 import chunk_kda
+    from oracle.kda_oracle import recurrent_kda
+    d = make_inputs(2, 150, 2, 128, 128, torch.bfloat16, seed=77, h0_std=0.02)
+    c = {n: (t.cuda() if t is not None else None) for n, t in d.items()}
+    with torch.inference_mode():
+        o, ht, h = chunk_kda(c["q"], c["k"], c["v"], c["g"], c["beta"], initial_state=c["h0"], output_final_state=True,
+                             return_intermediate_states=True)
+    assert h.shape == (2, 3, 2, 128, 128) and h.dtype == torch.bfloat16
+    o_ref, ht_ref = recurrent_kda(d["q"], d["k"], d["v"], d["g"], d["beta"], initial_state=d["h0"], output_final_state=True)
+    assert max_norm_err(o, o_ref) <= 2e-2 and max_norm_err(ht, ht_ref) <= 2e-2
+    for i in range(3):
+        if i == 0:
+            ref = d["h0"].double()
+        else:
+            _, ref = recurrent_kda(d["q"][:, :64 * i], d["k"][:, :64 * i], d["v"][:, :64 * i], d["g"][:, :64 * i], d["beta"][:, :64 * i],
+                                   initial_state=d["h0"], output_final_state=True)
+        assert max_norm_err(h[:, i], ref) <= 2e-2, i
+    # packed: 70 + 130 tokens -> 2 + 3 chunks
+    cu = torch.tensor([0, 70, 200], dtype=torch.int32)
+    dv = make_inputs(1, 200, 2, 128, 128, torch.bfloat16, seed=78, h0_std=0.02, n_states=2)
+    cv = {n: (t.cuda() if t is not None else None) for n, t in dv.items()}
+    with torch.inference_mode():
+        _, _, hv = chunk_kda(cv["q"], cv["k"], cv["v"], cv["g"], cv["beta"], initial_state=cv["h0"], cu_seqlens=cu.cuda(),
+                             return_intermediate_states=True)
+    assert hv.shape == (1, 5, 2, 128, 128)
+    _, ref = recurrent_kda(dv["q"][:, 70:134], dv["k"][:, 70:134], dv["v"][:, 70:134], dv["g"][:, 70:134], dv["beta"][:, 70:134],
+                           initial_state=dv["h0"][1:2], output_final_state=True)
+    assert max_norm_err(hv[0, 3], ref[0]) <= 2e-2
+    assert max_norm_err(hv[0, 2], dv["h0"][1].double()) <= 2e-2
+    with pytest.raises(AssertionError, match="inference mode"):
+        chunk_kda(c["q"], c["k"], c["v"], c["g"], c["beta"], return_intermediate_states=True)

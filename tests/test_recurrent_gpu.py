@@ -104,6 +104,37 @@ def test_speculative_decoding_state_slots():
         fused_recurrent_kda_fwd(d["q"], d["k"], d["v"], d["g"], d["beta"], initial_state=pool, num_accepted_tokens=accepted)
 
 
+def test_transposed_state_layout():
+    """transpose_state_layout (states [N, H, V, K]): the dedicated decode kernel against the default layout, with slots;
+    chunk_kda with transposed states in and out (fp32 1e-5 for decode: another summation order; bf16 mode for the chunk path)."""
+    from kda_b200 import chunk_kda, fused_recurrent_kda, fused_recurrent_kda_fwd
+    d = _cuda(make_inputs(3, 5, 2, 128, 128, torch.bfloat16, seed=21, h0_std=0.02))
+    o_ref, h_ref = fused_recurrent_kda(d["q"], d["k"], d["v"], d["g"], d["beta"], initial_state=d["h0"], output_final_state=True,
+                                       use_qk_l2norm_in_kernel=True)
+    o_t, h_t = fused_recurrent_kda(d["q"], d["k"], d["v"], d["g"], d["beta"], initial_state=d["h0"].transpose(-1, -2).contiguous(),
+                                   output_final_state=True, use_qk_l2norm_in_kernel=True, transpose_state_layout=True)
+    assert h_t.shape == (3, 2, 128, 128)
+    assert (o_t.float() - o_ref.float()).abs().max() <= 1e-2 * o_ref.float().abs().max()          # bf16 outputs: one ulp
+    assert (h_t.transpose(-1, -2) - h_ref).abs().max() <= 1e-5 * h_ref.abs().max()
+    # in-place pool with per-token slots, K = 64 fp32
+    d64 = _cuda(make_inputs(2, 3, 2, 64, 64, torch.float32, seed=22, h0_std=0.1))
+    slots = torch.tensor([[3, 0, 5], [1, 4, 2]], device="cuda", dtype=torch.int32)
+    pool, pool_t = torch.zeros(6, 2, 64, 64, device="cuda"), torch.zeros(6, 2, 64, 64, device="cuda")
+    pool[slots[:, 0].long()] = d64["h0"]
+    pool_t[slots[:, 0].long()] = d64["h0"].transpose(-1, -2)
+    o_a, _ = fused_recurrent_kda_fwd(d64["q"], d64["k"], d64["v"], d64["g"], d64["beta"], initial_state=pool, ssm_state_indices=slots)
+    o_b, _ = fused_recurrent_kda_fwd(d64["q"], d64["k"], d64["v"], d64["g"], d64["beta"], initial_state=pool_t, ssm_state_indices=slots,
+                                     transpose_state_layout=True)
+    assert (o_a - o_b).abs().max() <= 1e-5 * o_a.abs().max()
+    assert (pool_t.transpose(-1, -2) - pool).abs().max() <= 1e-5 * pool.abs().max()
+    # chunk path
+    dc = _cuda(make_inputs(2, 130, 2, 128, 128, torch.bfloat16, seed=23, h0_std=0.02))
+    o1, h1 = chunk_kda(dc["q"], dc["k"], dc["v"], dc["g"], dc["beta"], initial_state=dc["h0"], output_final_state=True)
+    o2, h2 = chunk_kda(dc["q"], dc["k"], dc["v"], dc["g"], dc["beta"], initial_state=dc["h0"].transpose(-1, -2).contiguous(),
+                       output_final_state=True, transpose_state_layout=True)
+    assert torch.equal(o1, o2) and torch.equal(h1, h2.transpose(-1, -2))
+
+
 def test_empty_and_errors():
     from kda_b200 import chunk_kda, fused_recurrent_kda
     d = _cuda(make_inputs(1, 8, 2, 64, 64, torch.float32, seed=1, h0_std=0.1))
@@ -113,7 +144,7 @@ def test_empty_and_errors():
     with pytest.raises(AssertionError, match="A_log must be provided"):
         chunk_kda(d["q"], d["k"], d["v"], d["g"], d["beta"], use_gate_in_kernel=True)
     with pytest.raises(NotImplementedError):
-        chunk_kda(d["q"], d["k"], d["v"], d["g"], d["beta"], transpose_state_layout=True)
+        chunk_kda(d["q"], d["k"], d["v"], d["g"], d["beta"], cp_context=object())
     with pytest.raises(RuntimeError):
         chunk_kda(d["q"].cpu(), d["k"].cpu(), d["v"].cpu(), d["g"].cpu(), d["beta"].cpu())
     e = _cuda(make_inputs(2, 0, 2, 64, 64, torch.float32, seed=1, h0_std=0.1))
