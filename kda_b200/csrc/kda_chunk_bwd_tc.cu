@@ -330,14 +330,13 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __g
     KDA_DBG_CLOCK(dbg, 3);
     // ---- post-A: dw^T -> bf16 tile; dAqk -> masked bf16 tile + diagonal blocks; k Gam tile -------------------------
     {
-      float v[16];
-      umma::tmem_ld16(tq + C_DW + 16 * part, v);
-      umma::tmem_ld_wait();
-      const int kk = 32 * q4 + lane;
-      *reinterpret_cast<uint4*>(sw_piece(sDWT, kk, 2 * part)) = pack8(&v[0]);
-      *reinterpret_cast<uint4*>(sw_piece(sDWT, kk, 2 * part + 1)) = pack8(&v[8]);
+      float v[16], w16[16];                            // both loads in flight together
+      umma::tmem_ld16(tq + C_DW + 16 * part, w16);
       umma::tmem_ld16(tq + C_DAQ + 16 * part, v);      // M = 64: rows 16 q4 .. +15 live in lanes 0..15 of this quadrant
       umma::tmem_ld_wait();
+      const int kk = 32 * q4 + lane;
+      *reinterpret_cast<uint4*>(sw_piece(sDWT, kk, 2 * part)) = pack8(&w16[0]);
+      *reinterpret_cast<uint4*>(sw_piece(sDWT, kk, 2 * part + 1)) = pack8(&w16[8]);
       if (lane < 16) {
         const int t = 16 * q4 + lane;
 #pragma unroll
@@ -587,7 +586,7 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __g
     {
       // Decay inside the block as running products of lam_i = 2^(G_i - G_{i-1}) (every factor <= 1):
       //   2^(G_i - G_first) = fl_i,  2^(G_i) = 2^(G_first) fl_i,  2^(G_e - G_i) = fr_i,  2^(G_last - G_i) = 2^(G_last - G_e) fr_i
-      float a[16];
+      float a[16], a2[16];
       float g_first, e_last;
       {
         float prev = s.G[t0 * KD + kk];
@@ -605,6 +604,7 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __g
       }
       // dk-: dkg 2^(G_last - G);  sum of k dk_end feeds dG at the chunk's last row
       umma::tmem_ld16(tq + C_DKG + t0, a);
+      umma::tmem_ld16(tq + C_DQG + t0, a2);
       umma::tmem_ld_wait();
       {
         float dglp = 0.f, fr = 1.f;
@@ -618,14 +618,12 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __g
         s.dglp[blk][kk] = dglp;
       }
       // dq: scale Gam dqg
-      umma::tmem_ld16(tq + C_DQG + t0, a);
-      umma::tmem_ld_wait();
       {
         float fl = p.scale * g_first;
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           fl *= lam[i];
-          cq[i] = fl * a[i];
+          cq[i] = fl * a2[i];
         }
       }
       // dk+: Gam beta dbk

@@ -164,14 +164,8 @@ __global__ void __launch_bounds__(256, 2) kda_chunk_prepare_kernel(const PrepPar
   KDA_DBG_CLOCK(p.dbg, 16);
 
   // ---- P1: stage q, k, g, beta (v follows after P3a); rows >= len are zero-filled -----------------------------------
+  // g goes first and alone in its copy group: the cumsum starts as soon as it is there, while q and k still arrive.
   {
-    for (int i = tid; i < C * 16; i += 256) {
-      const int r = i >> 4, pc = i & 15;
-      const bool ok = r < len;
-      const size_t row = (static_cast<size_t>(ci.tok0 + (ok ? r : 0)) * p.H + h) * KD + pc * 8;
-      cp_async16(&s.q[r * QS + pc * 8], p.q + row, ok);
-      cp_async16(&s.k[r * QS + pc * 8], p.k + row, ok);
-    }
     for (int i = tid; i < C * 32; i += 256) {
       const int r = i >> 5, pc = i & 31;
       const bool ok = r < len;
@@ -179,30 +173,22 @@ __global__ void __launch_bounds__(256, 2) kda_chunk_prepare_kernel(const PrepPar
       cp_async16(&s.G[r * GS + pc * 4], p.g + row, ok);
     }
     cp_async_commit();
+    for (int i = tid; i < C * 16; i += 256) {
+      const int r = i >> 4, pc = i & 15;
+      const bool ok = r < len;
+      const size_t row = (static_cast<size_t>(ci.tok0 + (ok ? r : 0)) * p.H + h) * KD + pc * 8;
+      cp_async16(&s.q[r * QS + pc * 8], p.q + row, ok);
+      cp_async16(&s.k[r * QS + pc * 8], p.k + row, ok);
+    }
+    cp_async_commit();
     if (tid < C) s.beta[tid] = (tid < len) ? __ldg(p.beta + static_cast<size_t>(ci.tok0 + tid) * p.H + h) : 0.f;
     for (int i = tid; i < C * AS; i += 256) s.Akk[i] = 0.f;
     for (int i = tid; i < C * TS / 2; i += 256) reinterpret_cast<uint32_t*>(s.Aqk)[i] = 0u;
-    cp_async_wait<0>();
+    cp_async_wait<1>();
     __syncthreads();
   }
 
   KDA_DBG_CLOCK(p.dbg, 17);
-  // ---- P1b: optional L2 normalisation of q and k rows (result rounded to bf16, as the unfused op does)
-  if (p.use_l2norm) {
-    for (int r = warp; r < C; r += 8) {
-      uint2 qr = *reinterpret_cast<uint2*>(&s.q[r * QS + lane * 4]);
-      uint2 kr = *reinterpret_cast<uint2*>(&s.k[r * QS + lane * 4]);
-      float2 q0 = unpack_bf16(qr.x), q1 = unpack_bf16(qr.y), k0 = unpack_bf16(kr.x), k1 = unpack_bf16(kr.y);
-      float sq = warp_sum(q0.x * q0.x + q0.y * q0.y + q1.x * q1.x + q1.y * q1.y);
-      float sk = warp_sum(k0.x * k0.x + k0.y * k0.y + k1.x * k1.x + k1.y * k1.y);
-      const float rq = rsqrtf(sq + L2NORM_EPS), rk = rsqrtf(sk + L2NORM_EPS);
-      qr.x = pack_bf16(q0.x * rq, q0.y * rq); qr.y = pack_bf16(q1.x * rq, q1.y * rq);
-      kr.x = pack_bf16(k0.x * rk, k0.y * rk); kr.y = pack_bf16(k1.x * rk, k1.y * rk);
-      *reinterpret_cast<uint2*>(&s.q[r * QS + lane * 4]) = qr;
-      *reinterpret_cast<uint2*>(&s.k[r * QS + lane * 4]) = kr;
-    }
-  }
-
   // ---- P2: G = cumsum(g) * log2(e): two half-columns per column, then the carry ----------------------
   {
     const int col = tid & 127, half = tid >> 7;
@@ -226,7 +212,24 @@ __global__ void __launch_bounds__(256, 2) kda_chunk_prepare_kernel(const PrepPar
       for (int i = 0; i < 32; ++i) s.G[(32 + i) * GS + col] = carry + gv[i] * LOG2E;
     }
   }
+  cp_async_wait<0>();   // q, k
   __syncthreads();
+  // ---- P1b: optional L2 normalisation of q and k rows (result rounded to bf16, as the unfused op does)
+  if (p.use_l2norm) {
+    for (int r = warp; r < C; r += 8) {
+      uint2 qr = *reinterpret_cast<uint2*>(&s.q[r * QS + lane * 4]);
+      uint2 kr = *reinterpret_cast<uint2*>(&s.k[r * QS + lane * 4]);
+      float2 q0 = unpack_bf16(qr.x), q1 = unpack_bf16(qr.y), k0 = unpack_bf16(kr.x), k1 = unpack_bf16(kr.y);
+      float sq = warp_sum(q0.x * q0.x + q0.y * q0.y + q1.x * q1.x + q1.y * q1.y);
+      float sk = warp_sum(k0.x * k0.x + k0.y * k0.y + k1.x * k1.x + k1.y * k1.y);
+      const float rq = rsqrtf(sq + L2NORM_EPS), rk = rsqrtf(sk + L2NORM_EPS);
+      qr.x = pack_bf16(q0.x * rq, q0.y * rq); qr.y = pack_bf16(q1.x * rq, q1.y * rq);
+      kr.x = pack_bf16(k0.x * rk, k0.y * rk); kr.y = pack_bf16(k1.x * rk, k1.y * rk);
+      *reinterpret_cast<uint2*>(&s.q[r * QS + lane * 4]) = qr;
+      *reinterpret_cast<uint2*>(&s.k[r * QS + lane * 4]) = kr;
+    }
+  }
+  if (p.use_l2norm) __syncthreads();
 
   KDA_DBG_CLOCK(p.dbg, 18);
   // ---- P3a: diagonal 8x8 blocks, pairwise decay as running products (never a factorisation there: range-safe).
