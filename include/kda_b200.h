@@ -31,7 +31,7 @@ extern "C" {
 #pragma GCC visibility push(default) /* the entry points below are the library's only exports */
 #endif
 
-#define KDA_B200_ABI_VERSION 3
+#define KDA_B200_ABI_VERSION 4
 #define KDA_CHUNK 64 /* tokens per chunk of the chunked kernels */
 
 /* io_dtype of q, k, v, o and of their gradients */
@@ -84,6 +84,8 @@ typedef struct kda_recurrent_args {
   int32_t state_indices_stride;       /* elements between two sequences' rows of state_indices (>= 1 when it is used) */
   int32_t transpose_state;            /* nonzero: states are [slots, H, V, K] (K contiguous), fla's transpose_state_layout;
                                          K in {64, 128} */
+  int32_t HQ;                         /* grouped value heads (GVA): q and k have HQ heads, [tokens, HQ, K], and value head h reads
+                                         q/k head h / (H / HQ); 0 or H: no grouping.  H must be a multiple of HQ. */
 } kda_recurrent_args;
 
 int kda_recurrent_fwd(const kda_recurrent_args* args, void* stream);
@@ -132,13 +134,18 @@ typedef struct kda_chunk_args {
   int32_t use_qk_l2norm;
   int32_t save_for_backward;
   float scale;
+  int32_t HQ;                  /* grouped value heads (GVA, fla/ops/kda/chunk.py:194-196,379-386): q, k, dq, dk have HQ heads
+                                  ([tokens, HQ, K]) while v, g, beta, o, the states and their gradients have H; value head h reads
+                                  q/k head h / (H / HQ), and dq, dk are summed over each group.  0 or H: no grouping. */
 } kda_chunk_args;
 
 /* Upper bound on the number of chunks: every sequence adds at most one partial chunk. */
 int64_t kda_chunk_max_chunks(int64_t tokens, int32_t N);
 /* Bytes of scratch kda_chunk_fwd needs (more when it must keep what the backward reads). */
 size_t kda_chunk_workspace_bytes(int64_t tokens, int32_t N, int32_t H, int32_t K, int32_t V, int32_t save_for_backward);
-/* Bytes of the backward's own scratch (args->bwd_workspace); it need not outlive the backward call. */
+/* Bytes of the backward's own scratch (args->bwd_workspace); it need not outlive the backward call.
+ * use_qk_l2norm is a flag word here: bit 0 = q/k are L2-normalised in the kernels, bit 1 = grouped value heads
+ * (HQ < H), which needs room for the per-value-head dq, dk before they are summed. */
 size_t kda_chunk_bwd_workspace_bytes(int64_t tokens, int32_t N, int32_t H, int32_t K, int32_t V, int32_t use_qk_l2norm);
 
 int kda_chunk_fwd(const kda_chunk_args* args, void* stream);

@@ -34,6 +34,7 @@ struct ChunkWs {
   unsigned char *W, *UT, *KG, *QG, *AQK, *GL;          // always
   unsigned char *TI, *RKK, *HS, *VNEWT;                // save_for_backward only
   unsigned char *DH, *DVNEWT;                          // backward scratch (bf16 tiles)
+  __nv_bfloat16 *DQH, *DKH;                            // [tokens][H][128] per-value-head dq, dk (grouped value heads only)
   __nv_bfloat16 *QN, *KN;                              // [tokens][H][128] normalised q, k (use_qk_l2norm only)
   float *RSTD;                                         // [2][tokens][H]
   size_t fwd_bytes, bwd_bytes;
@@ -43,7 +44,7 @@ inline size_t align_up(size_t x, size_t a = 256) { return (x + a - 1) / a * a; }
 
 // Lays the workspace out.  base may be NULL (sizes only).  bwd_base: separate backward scratch.
 inline ChunkWs carve_ws(unsigned char* base, unsigned char* bwd_base, int64_t tokens, int N, int H, bool save,
-                        bool l2norm = true) {
+                        bool l2norm = true, bool gva = false) {
   ChunkWs w{};
   const size_t NTmax = static_cast<size_t>(tokens / C + N);
   const size_t tiles = NTmax * static_cast<size_t>(H);
@@ -73,6 +74,10 @@ inline ChunkWs carve_ws(unsigned char* base, unsigned char* bwd_base, int64_t to
     w.QN = reinterpret_cast<__nv_bfloat16*>(takeb(static_cast<size_t>(tokens) * H * KD * 2));
     w.KN = reinterpret_cast<__nv_bfloat16*>(takeb(static_cast<size_t>(tokens) * H * KD * 2));
     w.RSTD = reinterpret_cast<float*>(takeb(static_cast<size_t>(tokens) * H * 2 * 4));
+  }
+  if (gva) {
+    w.DQH = reinterpret_cast<__nv_bfloat16*>(takeb(static_cast<size_t>(tokens) * H * KD * 2));
+    w.DKH = reinterpret_cast<__nv_bfloat16*>(takeb(static_cast<size_t>(tokens) * H * KD * 2));
   }
   w.bwd_bytes = boff;
   return w;

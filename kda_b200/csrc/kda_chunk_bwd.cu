@@ -95,9 +95,33 @@ static cudaError_t set_bwd_attrs() {
 
 }  // namespace kda
 
+namespace kda {
+// Grouped value heads: dq, dk [tokens, HQ, 128] = sum over the grp value heads of a group of the per-value-head
+// gradients [tokens, HQ * grp, 128] (fp32 sum, one rounding).  One thread per 16-byte piece of an output row.
+__global__ void __launch_bounds__(256) kda_group_sum_kernel(const __nv_bfloat16* __restrict__ dqh, const __nv_bfloat16* __restrict__ dkh,
+                                                            __nv_bfloat16* __restrict__ dq, __nv_bfloat16* __restrict__ dk, long long pieces,
+                                                            int grp) {
+  const long long i = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+  if (i >= pieces) return;
+  const long long row = i / (KD / 8);
+  const int pc = static_cast<int>(i % (KD / 8));
+  for (int which = 0; which < 2; ++which) {
+    const __nv_bfloat16* src = (which ? dkh : dqh) + row * grp * KD + pc * 8;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < grp; ++j) {
+      const uint4 r = *reinterpret_cast<const uint4*>(src + static_cast<size_t>(j) * KD);
+      const float2 a = unpack_bf16(r.x), b = unpack_bf16(r.y), c = unpack_bf16(r.z), d = unpack_bf16(r.w);
+      acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y; acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
+    }
+    *reinterpret_cast<uint4*>((which ? dk : dq) + row * KD + pc * 8) =
+        make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]), pack_bf16(acc[4], acc[5]), pack_bf16(acc[6], acc[7]));
+  }
+}
+}  // namespace kda
+
 extern "C" size_t kda_chunk_bwd_workspace_bytes(int64_t tokens, int32_t N, int32_t H, int32_t K, int32_t V, int32_t use_qk_l2norm) {
   (void)K; (void)V;
-  return kda::carve_ws(nullptr, nullptr, tokens, N, H, true, use_qk_l2norm != 0).bwd_bytes;
+  return kda::carve_ws(nullptr, nullptr, tokens, N, H, true, (use_qk_l2norm & 1) != 0, (use_qk_l2norm & 2) != 0).bwd_bytes;
 }
 
 extern "C" int kda_chunk_bwd(const kda_chunk_args* args, void* stream) {
@@ -117,13 +141,14 @@ extern "C" int kda_chunk_bwd(const kda_chunk_args* args, void* stream) {
     return KDA_OK;
   }
   const bool l2 = a.use_qk_l2norm != 0;
+  const int HQ = a.HQ > 0 ? a.HQ : a.H, grp = a.H / HQ;
   ChunkWs w = carve_ws(static_cast<unsigned char*>(a.workspace), static_cast<unsigned char*>(a.bwd_workspace), a.tokens, a.N,
-                       a.H, true, l2);
+                       a.H, true, l2, grp > 1);
   if (a.workspace_bytes < w.fwd_bytes || a.bwd_workspace_bytes < w.bwd_bytes) return KDA_E_WORKSPACE;
   cudaError_t e = set_bwd_attrs();
   if (e != cudaSuccess) return static_cast<int>(e);
   const int NTmax = static_cast<int>(a.tokens / C + a.N);
-  const long long rows = static_cast<long long>(a.tokens) * a.H;
+  const long long rows = static_cast<long long>(a.tokens) * HQ;      // rows of q and k
   const __nv_bfloat16* q = static_cast<const __nv_bfloat16*>(a.q);
   const __nv_bfloat16* k = static_cast<const __nv_bfloat16*>(a.k);
   ProfCall* prof = prof_begin(st);
@@ -149,19 +174,29 @@ extern "C" int kda_chunk_bwd(const kda_chunk_args* args, void* stream) {
   mp.q = q; mp.k = k; mp.v = static_cast<const __nv_bfloat16*>(a.v); mp.d_o = static_cast<const __nv_bfloat16*>(a.d_o);
   mp.g = a.g; mp.beta = a.beta; mp.cu = a.cu_seqlens; mp.seq_chunk_off = w.seq_chunk_off; mp.chunk_seq = w.chunk_seq;
   mp.TI = w.TI; mp.RKK = w.RKK; mp.HS = w.HS; mp.VNEWT = w.VNEWT; mp.DH = w.DH; mp.DVNEWT = w.DVNEWT;
-  mp.dv = static_cast<__nv_bfloat16*>(a.dv); mp.dq = static_cast<__nv_bfloat16*>(a.dq); mp.dk = static_cast<__nv_bfloat16*>(a.dk);
+  mp.dv = static_cast<__nv_bfloat16*>(a.dv);
+  // grouped value heads: every value head writes its own dq, dk; a second kernel sums each group
+  mp.dq = grp > 1 ? w.DQH : static_cast<__nv_bfloat16*>(a.dq);
+  mp.dk = grp > 1 ? w.DKH : static_cast<__nv_bfloat16*>(a.dk);
   mp.dbeta = a.dbeta; mp.dg = a.dg; mp.status = w.status; mp.dbg = g_dbg_clocks;
-  if (make_rows_tmap(&mp.tm_q, q, false, a.tokens, a.H, KD, KD, C, false) || make_rows_tmap(&mp.tm_k, k, false, a.tokens, a.H, KD, KD, C, false) ||
+  if (make_rows_tmap(&mp.tm_q, q, false, a.tokens, HQ, KD, KD, C, false) || make_rows_tmap(&mp.tm_k, k, false, a.tokens, HQ, KD, KD, C, false) ||
       make_rows_tmap(&mp.tm_g, a.g, true, a.tokens, a.H, KD, KD, C, false) ||
       make_rows_tmap(&mp.tm_v, a.v, false, a.tokens, a.H, VD, 64, C, true) ||
       make_rows_tmap(&mp.tm_do, a.d_o, false, a.tokens, a.H, VD, 64, C, true))
     return KDA_E_DEVICE;
-  mp.N = a.N; mp.H = a.H; mp.scale = a.scale;
+  mp.N = a.N; mp.H = a.H; mp.scale = a.scale; mp.grp = grp;
   if ((e = launch_bwd_main_tc(mp, main_grid(NTmax, a.H), st)) != cudaSuccess) return static_cast<int>(e);
+  if (grp > 1) {
+    const long long pieces = rows * (KD / 8);
+    kda_group_sum_kernel<<<static_cast<unsigned>((pieces + 255) / 256), 256, 0, st>>>(w.DQH, w.DKH, static_cast<__nv_bfloat16*>(a.dq),
+                                                                                       static_cast<__nv_bfloat16*>(a.dk), pieces, grp);
+    if ((e = cudaGetLastError()) != cudaSuccess) return static_cast<int>(e);
+  }
   prof_mark(prof, KDA_STAGE_BWD_MAIN, st);
 
   if (l2) {
-    kda_l2norm_bwd_kernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, st>>>(w.QN, w.KN, w.RSTD, mp.dq, mp.dk, rows);
+    kda_l2norm_bwd_kernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, st>>>(w.QN, w.KN, w.RSTD, static_cast<__nv_bfloat16*>(a.dq),
+                                                                                  static_cast<__nv_bfloat16*>(a.dk), rows);
     if ((e = cudaGetLastError()) != cudaSuccess) return static_cast<int>(e);
     prof_mark(prof, KDA_STAGE_L2NORM, st);
   }

@@ -18,6 +18,7 @@ struct MainParams {
   long long* dbg;
   int N, H;
   float scale;
+  int grp;          // value heads per q/k head (grouped value heads): the q, k maps have H / grp heads
   // tiled-load maps of the [tokens, H, 128] operator tensors (64-token boxes of one head)
   alignas(64) CUtensorMap tm_q, tm_k, tm_g;   // plain row-major boxes [64][128]
   alignas(64) CUtensorMap tm_v, tm_do;        // 64-column boxes in the 128-byte-swizzled operand layout

@@ -139,8 +139,8 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __g
     const int hh = static_cast<int>(idx % p.H);
     const int tk = static_cast<int>(s.ci_tok0[slot]);
     mbar_expect_tx(&s.barQ, 2 * TILE_TK + C * KD * 4);
-    tma_load_rows(s.q, &p.tm_q, 0, hh, tk, &s.barQ);
-    tma_load_rows(s.k, &p.tm_k, 0, hh, tk, &s.barQ);
+    tma_load_rows(s.q, &p.tm_q, 0, hh / p.grp, tk, &s.barQ);
+    tma_load_rows(s.k, &p.tm_k, 0, hh / p.grp, tk, &s.barQ);
     tma_load_rows(s.G, &p.tm_g, 0, hh, tk, &s.barQ);
   };
   // rows of a partial chunk beyond its length hold the next sequence's tokens after a tiled load: clear them

@@ -78,6 +78,7 @@ struct PrepParams {
   int N, H;
   int use_l2norm;
   float scale;
+  int HQ, grp;      // q/k heads and value heads per q/k head (grouped value heads); H counts value heads
 };
 
 // Sum over the 32 lanes of 32 per-lane values at once: afterwards lane L holds the total of slot L.
@@ -176,7 +177,7 @@ __global__ void __launch_bounds__(256, 2) kda_chunk_prepare_kernel(const PrepPar
     for (int i = tid; i < C * 16; i += 256) {
       const int r = i >> 4, pc = i & 15;
       const bool ok = r < len;
-      const size_t row = (static_cast<size_t>(ci.tok0 + (ok ? r : 0)) * p.H + h) * KD + pc * 8;
+      const size_t row = (static_cast<size_t>(ci.tok0 + (ok ? r : 0)) * p.HQ + h / p.grp) * KD + pc * 8;
       cp_async16(&s.q[r * QS + pc * 8], p.q + row, ok);
       cp_async16(&s.k[r * QS + pc * 8], p.k + row, ok);
     }
@@ -609,6 +610,7 @@ static cudaError_t set_attrs() {
 int validate_chunk_args(const kda_chunk_args& a, bool backward);
 int validate_chunk_args(const kda_chunk_args& a, bool backward) {
   if (a.tokens < 0 || a.N < 0 || a.H <= 0) return KDA_E_SHAPE;
+  if (a.HQ < 0 || (a.HQ > 0 && (a.HQ > a.H || a.H % a.HQ != 0))) return KDA_E_SHAPE;
   if (a.K != KD || a.V != VD) return KDA_E_SHAPE;
   if (a.io_dtype != KDA_BF16) return KDA_E_DTYPE;
   if (a.tokens / C + a.N > 0x3fffffffLL) return KDA_E_SHAPE;
@@ -674,6 +676,7 @@ extern "C" int kda_chunk_fwd(const kda_chunk_args* args, void* stream) {
   pp.seq_chunk_off = w.seq_chunk_off; pp.chunk_seq = w.chunk_seq;
   pp.W = w.W; pp.UT = w.UT; pp.KG = w.KG; pp.QG = w.QG; pp.AQK = w.AQK; pp.GL = w.GL; pp.TI = save ? w.TI : nullptr; pp.RKK = save ? w.RKK : nullptr;
   pp.dbg = g_dbg_clocks; pp.N = a.N; pp.H = a.H; pp.use_l2norm = a.use_qk_l2norm; pp.scale = a.scale;
+  pp.HQ = a.HQ > 0 ? a.HQ : a.H; pp.grp = a.H / pp.HQ;
   kda_chunk_prepare_kernel<<<dim3(NTmax, a.H), 256, sizeof(PrepSmem), st>>>(pp);
   if ((e = cudaGetLastError()) != cudaSuccess) return static_cast<int>(e);
   prof_mark(prof, KDA_STAGE_PREPARE, st);

@@ -66,6 +66,7 @@ __global__ void __launch_bounds__(REC_WARPS * 32) kda_recurrent_kernel(const kda
   const int vs = static_cast<int>(wid % nvs);
   const int h = static_cast<int>((wid / nvs) % a.H);
   const int n = static_cast<int>(wid / (static_cast<long long>(nvs) * a.H));
+  const int HQ = a.HQ > 0 ? a.HQ : a.H, grp = a.H / HQ;      // grouped value heads
   const int cg = lane % CL, rg = lane / CL;
   const int col = vs * VS + cg * 4;
 
@@ -98,12 +99,13 @@ __global__ void __launch_bounds__(REC_WARPS * 32) kda_recurrent_kernel(const kda
   IO* op = static_cast<IO*>(a.o);
 
   for (long long t = bos; t < eos; ++t) {
-    const size_t rowk = (static_cast<size_t>(t) * a.H + h) * K + lane * E;
+    const size_t rowk = (static_cast<size_t>(t) * a.H + h) * K + lane * E;        // g row (value head)
+    const size_t rowq = (static_cast<size_t>(t) * HQ + h / grp) * K + lane * E;   // q, k row (their own head count)
     float qf[E], kf[E], gf[E];
 #pragma unroll
     for (int e = 0; e < E; ++e) {
-      qf[e] = IoTraits<IO>::ld(qp + rowk + e);
-      kf[e] = IoTraits<IO>::ld(kp + rowk + e);
+      qf[e] = IoTraits<IO>::ld(qp + rowq + e);
+      kf[e] = IoTraits<IO>::ld(kp + rowq + e);
       gf[e] = __ldg(a.g + rowk + e);
     }
     float qs = a.scale;
@@ -211,6 +213,7 @@ __global__ void __launch_bounds__(REC_WARPS * 32) kda_recurrent_t_kernel(const k
   const int vs = static_cast<int>(wid % nvs);
   const int h = static_cast<int>((wid / nvs) % a.H);
   const int n = static_cast<int>(wid / (static_cast<long long>(nvs) * a.H));
+  const int HQ = a.HQ > 0 ? a.HQ : a.H, grp = a.H / HQ;      // grouped value heads
   long long bos, eos;
   if (a.cu_seqlens) {
     bos = a.cu_seqlens[n];
@@ -240,12 +243,13 @@ __global__ void __launch_bounds__(REC_WARPS * 32) kda_recurrent_t_kernel(const k
   const IO* vp = static_cast<const IO*>(a.v);
   IO* op = static_cast<IO*>(a.o);
   for (long long t = bos; t < eos; ++t) {
-    const size_t rowk = (static_cast<size_t>(t) * a.H + h) * K + lane * E;
+    const size_t rowk = (static_cast<size_t>(t) * a.H + h) * K + lane * E;        // g row (value head)
+    const size_t rowq = (static_cast<size_t>(t) * HQ + h / grp) * K + lane * E;   // q, k row (their own head count)
     float qf[E], kf[E], eg[E];
 #pragma unroll
     for (int e = 0; e < E; ++e) {
-      qf[e] = IoTraits<IO>::ld(qp + rowk + e);
-      kf[e] = IoTraits<IO>::ld(kp + rowk + e);
+      qf[e] = IoTraits<IO>::ld(qp + rowq + e);
+      kf[e] = IoTraits<IO>::ld(kp + rowq + e);
       eg[e] = expf(__ldg(a.g + rowk + e));
     }
     float qs = a.scale;
@@ -357,6 +361,7 @@ extern "C" int kda_recurrent_fwd(const kda_recurrent_args* args, void* stream) {
     return KDA_E_NULL;                                 // accepted-token counts only mean something with slots
   }
   if (a.N < 0 || a.H <= 0 || a.V <= 0 || a.V % 32 != 0 || a.tokens < 0) return KDA_E_SHAPE;
+  if (a.HQ < 0 || (a.HQ > 0 && (a.HQ > a.H || a.H % a.HQ != 0))) return KDA_E_SHAPE;
   if (a.N == 0 || a.tokens == 0) {
     // nothing to scan; with distinct h0/ht buffers the final state is the initial one
     if (a.N > 0 && a.ht && a.ht != a.h0) {

@@ -24,8 +24,8 @@ def _accepts(q, k, v, g, beta, initial_state=None, cp_context=None, **kwargs):
         return False, "kda_b200 does not implement context parallelism"
     if kwargs.get("chunk_size", 64) != 64:
         return False, "kda_b200 implements chunk_size=64"
-    if v.shape[2] != q.shape[2]:
-        return False, f"kda_b200 does not support GVA (HV={v.shape[2]} != H={q.shape[2]})"
+    if v.shape[2] % q.shape[2]:
+        return False, f"HV={v.shape[2]} is not a multiple of H={q.shape[2]}"
     if q.dtype == torch.bfloat16:
         if q.shape[-1] != 128 or v.shape[-1] != 128:
             return False, f"kda_b200 bf16 kernels need K = V = 128, got K={q.shape[-1]}, V={v.shape[-1]}"

@@ -38,8 +38,9 @@ def _check_common(q, k, v, g, beta, initial_state, cu_seqlens):
     B, T, H, K = q.shape
     assert q.shape == k.shape, f"q and k must have the same shape, got q={q.shape} vs k={k.shape}"
     HV, V = v.shape[2], v.shape[3]
-    if HV != H:
-        raise NotImplementedError("kda_b200: grouped value heads (HV > H) are not supported")
+    assert HV % H == 0, (
+        f"For GVA, num_v_heads (HV={HV}) must be evenly divisible by num_qk_heads (H={H}), "
+        f"but got HV % H = {HV % H}")
     assert K <= 256, f"Currently we only support key headdim <=256 for KDA, got {K}."
     assert g.shape == (B, T, HV, K), f"g must have shape [B, T, HV, K]={[B, T, HV, K]}, got {list(g.shape)}"
     assert beta.shape == (B, T, HV), f"beta must have shape [B, T, HV]={[B, T, HV]}, got {list(beta.shape)}"
@@ -56,7 +57,7 @@ def _check_common(q, k, v, g, beta, initial_state, cu_seqlens):
         assert initial_state.dtype == torch.float32, "initial_state must be in float32."
     if q.dtype not in _DT or k.dtype != q.dtype or v.dtype != q.dtype:
         raise NotImplementedError(f"kda_b200: q, k, v must share dtype bfloat16 or float32, got {q.dtype}")
-    return B, T, H, K, V
+    return B, T, HV, K, V      # H below always counts value heads; q and k may have fewer (grouped value heads)
 
 
 _cu_cache: dict = {}
@@ -277,7 +278,8 @@ def fused_recurrent_kda_fwd(q, k, v, g, beta, A_log=None, dt_bias=None, initial_
         q=_ptr(q), k=_ptr(k), v=_ptr(v), g=_ptr(g), beta=_ptr(beta), h0=_ptr(h0), ht=_ptr(ht), o=_ptr(o),
         cu_seqlens=_ptr(cu), state_indices=_ptr(idx), tokens=B * T, N=N, T=T, H=H, K=K, V=V,
         io_dtype=_DT[q.dtype], use_qk_l2norm=int(bool(use_qk_l2norm_in_kernel)), scale=float(scale),
-        num_accepted_tokens=_ptr(acc), state_indices_stride=stride, transpose_state=int(bool(transpose_state_layout)))
+        num_accepted_tokens=_ptr(acc), state_indices_stride=stride, transpose_state=int(bool(transpose_state_layout)),
+        HQ=q.shape[2])
     with torch.cuda.device(dev):
         _lib.check(_lib.load().kda_recurrent_fwd(C.byref(args), _stream(dev)), "kda_recurrent_fwd")
     return o, ht
@@ -313,7 +315,7 @@ def _chunk_args(q, k, v, g, beta, h0, cu, o, ht, ws, N, H, K, V, tokens, l2, sav
         q=_ptr(q), k=_ptr(k), v=_ptr(v), g=_ptr(g), beta=_ptr(beta), h0=_ptr(h0), cu_seqlens=_ptr(cu),
         o=_ptr(o), ht=_ptr(ht), workspace=_ptr(ws), workspace_bytes=ws.numel() if ws is not None else 0,
         tokens=tokens, N=N, H=H, K=K, V=V, io_dtype=_lib.KDA_BF16, use_qk_l2norm=int(l2),
-        save_for_backward=int(save), scale=float(scale))
+        save_for_backward=int(save), scale=float(scale), HQ=q.shape[-2])
     for name, t in extra.items():
         if name == "bwd_ws":
             a.bwd_workspace = _ptr(t)
@@ -330,8 +332,8 @@ class ChunkKDAFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, q, k, v, g, beta, scale, initial_state, output_final_state, use_l2norm, cu_seqlens):
-        B, T, H, K = q.shape
-        V = v.shape[-1]
+        B, T, HQ, K = q.shape
+        H, V = v.shape[-2], v.shape[-1]          # H counts value heads; q and k may have fewer (grouped value heads)
         dev = q.device
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
         g32 = g.contiguous().float()
@@ -353,13 +355,13 @@ class ChunkKDAFunction(torch.autograd.Function):
             _lib.check(lib.kda_chunk_fwd(C.byref(args), _stream(dev)), "kda_chunk_fwd")
         if need_grad:
             ctx.save_for_backward(q, k, v, g32, beta32, h0, cu, ws)
-            ctx.meta = (N, H, K, V, tokens, use_l2norm, scale, g.dtype, beta.dtype, initial_state is not None)
+            ctx.meta = (N, H, K, V, tokens, use_l2norm, scale, g.dtype, beta.dtype, initial_state is not None, HQ)
         return o, ht
 
     @staticmethod
     def backward(ctx, do, dht):
         q, k, v, g32, beta32, h0, cu, ws = ctx.saved_tensors
-        N, H, K, V, tokens, use_l2norm, scale, g_dtype, beta_dtype, has_h0 = ctx.meta
+        N, H, K, V, tokens, use_l2norm, scale, g_dtype, beta_dtype, has_h0, HQ = ctx.meta
         dev = q.device
         lib = _lib.load()
         do = do.contiguous()
@@ -368,7 +370,8 @@ class ChunkKDAFunction(torch.autograd.Function):
         dg = torch.empty_like(g32)
         dbeta = torch.empty_like(beta32)
         dh0 = torch.empty(N, H, K, V, dtype=torch.float32, device=dev) if has_h0 else None
-        bws = torch.empty(lib.kda_chunk_bwd_workspace_bytes(tokens, N, H, K, V, int(use_l2norm)), dtype=torch.uint8, device=dev)
+        flags = int(use_l2norm) | (2 if HQ != H else 0)
+        bws = torch.empty(lib.kda_chunk_bwd_workspace_bytes(tokens, N, H, K, V, flags), dtype=torch.uint8, device=dev)
         args = _chunk_args(q, k, v, g32, beta32, h0, cu, None, None, ws, N, H, K, V, tokens, use_l2norm, True, scale,
                            d_o=do, d_ht=dht, dq=dq, dk=dk, dv=dv, dg=dg, dbeta=dbeta, dh0=dh0, bwd_ws=bws)
         with torch.cuda.device(dev):
@@ -379,8 +382,8 @@ class ChunkKDAFunction(torch.autograd.Function):
 def _chunk_fwd_with_states(q, k, v, g, beta, scale, initial_state, output_final_state, use_l2norm, cu_seqlens):
     """Forward for inference engines (fla/ops/kda/chunk.py:95-98): also returns h, the state at the start of every
     chunk, [B, NT, H, K, V] bf16 (NT chunks per sequence; with cu_seqlens B = 1 and NT counts all chunks)."""
-    B, T, H, K = q.shape
-    V = v.shape[-1]
+    B, T, _, K = q.shape
+    H, V = v.shape[-2], v.shape[-1]
     dev = q.device
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     g32, beta32 = g.contiguous().float(), beta.contiguous().float()
@@ -414,8 +417,9 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
               return_intermediate_states=False, cp_context=None, transpose_state_layout=False, **kwargs):
     """Drop-in for fla.ops.kda.chunk_kda (fla/ops/kda/chunk.py:167-411).
 
-    q, k [B,T,H,K]; v [B,T,H,V]; g [B,T,H,K] log-space decay; beta [B,T,H]; initial_state [N,H,K,V] fp32;
-    cu_seqlens [N+1] with B == 1.  With `use_gate_in_kernel=True` g is the raw gate input and `A_log` [H]
+    q, k [B,T,H,K]; v [B,T,HV,V]; g [B,T,HV,K] log-space decay; beta [B,T,HV]; initial_state [N,HV,K,V] fp32;
+    cu_seqlens [N+1] with B == 1.  HV is a multiple of H (grouped value heads: value head h reads q/k head
+    h // (HV // H); dq, dk are summed over each group).  With `use_gate_in_kernel=True` g is the raw gate input and `A_log` [H]
     (and optionally `dt_bias` [H*K]) are keyword arguments: g = -exp(A_log) softplus(g + dt_bias), or, with
     `lower_bound`, lower_bound * sigmoid(exp(A_log) (g + dt_bias)); with `use_beta_sigmoid_in_kernel=True` beta
     holds logits.  Returns (o, final_state or None); differentiable w.r.t. q, k, v, g, beta, initial_state,
