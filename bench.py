@@ -16,7 +16,7 @@ events recorded by the library around each kernel during the timed steps), `cpu_
 float32 token-recurrent PyTorch restatement on the host cores, bounded sample), clocks, launches.
 
 `--impl reference` times that CPU restatement alone, on all host threads (the NVlabs/kda repository
-has no implementation of this operator).
+has no implementation of this operator to run).
 """
 from __future__ import annotations
 

@@ -2,8 +2,8 @@
 //
 // Every intermediate that travels between kernels is a per-(chunk, head) TILE that is contiguous in
 // global memory and already holds the XOR-swizzled image the consumer wants in shared memory, so a
-// consumer fetches a tile with one 1-D bulk (TMA) copy and reads it with ldmatrix without bank
-// conflicts.  Tile index = chunk * H + head.  Formats (bf16 unless noted):
+// consumer fetches a tile with one 1-D bulk (TMA) copy and hands it to tcgen05.mma as a 128-byte-swizzled
+// operand tile (the same image is conflict-free for ldmatrix).  Tile index = chunk * H + head.  Formats (bf16 unless noted):
 //   W, QG, KG : [64 tokens][128 k]   two [64 t][64 k] sub-tiles of 128-byte rows (tk_off)
 //                                    w = Tm (beta k Gam), qg = scale q Gam, kg = k exp(G_last - G)
 //   AQK, TI, RKK : [64 t][64 j]      128-byte rows      Aqk (lower incl. diagonal), Tm = (I + Akk)^-1, raw <k_t D, k_j>
