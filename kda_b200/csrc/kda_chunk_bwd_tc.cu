@@ -247,6 +247,20 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __g
     umma::fence_after_sync();
 
     KDA_DBG_CLOCK(dbg, 1);
+    // ---- sum_v h dh' (all warps, before warp 0 starts issuing) -------------------------------------------------------
+    {
+      const int kp = tid & 63, vq = tid >> 6;
+      float ax = 0.f, ay = 0.f;
+#pragma unroll 4
+      for (int vv = vq * 16; vv < vq * 16 + 16; ++vv) {
+        const float2 hh = unpack_bf16(*reinterpret_cast<const uint32_t*>(s.HS + vk_off(vv, 2 * kp)));
+        const float2 dd = unpack_bf16(*reinterpret_cast<const uint32_t*>(s.DH + vk_off(vv, 2 * kp)));
+        ax += hh.x * dd.x;
+        ay += hh.y * dd.y;
+      }
+      s.hdh_part[vq][2 * kp] = ax;
+      s.hdh_part[vq][2 * kp + 1] = ay;
+    }
     // =========================== phase A: state-dependent products ==================================================
     if (warp_u == 0 && alive) {
       const uint32_t aHS = smem_u32(s.HS), aDH = smem_u32(s.DH), aVN = smem_u32(s.VN), aDVN = smem_u32(s.DVN), aDO = smem_u32(s.dO);
@@ -269,51 +283,49 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __g
       if (lead) umma::commit(&s.barM);
     }
     KDA_DBG_CLOCK(dbg, 2);
-    // ---- meanwhile: sum_v h dh', then (q, k, g arrived during the previous tile's phase D) G = cumsum(g) log2(e) ----
-    {
-      const int kp = tid & 63, vq = tid >> 6;
-      float ax = 0.f, ay = 0.f;
-#pragma unroll 4
-      for (int vv = vq * 16; vv < vq * 16 + 16; ++vv) {
-        const float2 hh = unpack_bf16(*reinterpret_cast<const uint32_t*>(s.HS + vk_off(vv, 2 * kp)));
-        const float2 dd = unpack_bf16(*reinterpret_cast<const uint32_t*>(s.DH + vk_off(vv, 2 * kp)));
-        ax += hh.x * dd.x;
-        ay += hh.y * dd.y;
+    // ---- meanwhile, on warps 1..15 (warp 0 is held up by the issue loop; a barrier that includes it would make
+    // everybody wait for the loop's end, so these warps meet at named barrier 1 and warp 1 takes warp 0's columns):
+    // G = cumsum(g) log2(e)  (q, k, g arrived during the previous tile's phase D) ------------------------------------
+    if (warp_u != 0) {
+      if (alive && !mbar_wait(&s.barQ, it & 1)) alive = false;
+      if (len < C) {
+        for (int i = len * 16 + tid - 32; i < C * 16; i += NT - 32) {
+          reinterpret_cast<uint4*>(s.q)[i] = make_uint4(0u, 0u, 0u, 0u);
+          reinterpret_cast<uint4*>(s.k)[i] = make_uint4(0u, 0u, 0u, 0u);
+          reinterpret_cast<uint4*>(s.G)[2 * i] = make_uint4(0u, 0u, 0u, 0u);
+          reinterpret_cast<uint4*>(s.G)[2 * i + 1] = make_uint4(0u, 0u, 0u, 0u);
+        }
       }
-      s.hdh_part[vq][2 * kp] = ax;
-      s.hdh_part[vq][2 * kp + 1] = ay;
-    }
-    if (alive && !mbar_wait(&s.barQ, it & 1)) {
-      if (tid == 0) atomicOr(p.status, 32u);
-      alive = false;
-    }
-    if (len < C) {
-      for (int i = len * 16 + tid; i < C * 16; i += NT) {
-        reinterpret_cast<uint4*>(s.q)[i] = make_uint4(0u, 0u, 0u, 0u);
-        reinterpret_cast<uint4*>(s.k)[i] = make_uint4(0u, 0u, 0u, 0u);
-        reinterpret_cast<uint4*>(s.G)[2 * i] = make_uint4(0u, 0u, 0u, 0u);
-        reinterpret_cast<uint4*>(s.G)[2 * i + 1] = make_uint4(0u, 0u, 0u, 0u);
+      asm volatile("bar.sync 1, 480;" ::: "memory");
+      // item = (column, quarter of 16 rows): a thread's own, and for warp 1 also the one warp 0 would have had
+      float gv[2][16];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        if (r == 1 && warp_u != 1) break;
+        const int item = r ? tid - 32 : tid;
+        const int col = item & 127, qr = item >> 7;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) gv[r][i] = s.G[(qr * 16 + i) * KD + col];
+        float run = 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          run += gv[r][i];
+          gv[r][i] = run;
+        }
+        s.carry[qr][col] = run;
       }
-    }
-    __syncthreads();
-    {
-      const int col = tid & 127, qr = tid >> 7;        // four quarters of 16 rows
-      float gv[16];
+      asm volatile("bar.sync 1, 480;" ::: "memory");
 #pragma unroll
-      for (int i = 0; i < 16; ++i) gv[i] = s.G[(qr * 16 + i) * KD + col];
-      float run = 0.f;
+      for (int r = 0; r < 2; ++r) {
+        if (r == 1 && warp_u != 1) break;
+        const int item = r ? tid - 32 : tid;
+        const int col = item & 127, qr = item >> 7;
+        float pre = 0.f;
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        run += gv[i];
-        gv[i] = run;
+        for (int b = 0; b < 3; ++b) pre += (b < qr) ? s.carry[b][col] : 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) s.G[(qr * 16 + i) * KD + col] = (pre + gv[r][i]) * LOG2E;
       }
-      s.carry[qr][col] = run;
-      __syncthreads();
-      float pre = 0.f;
-#pragma unroll
-      for (int b = 0; b < 3; ++b) pre += (b < qr) ? s.carry[b][col] : 0.f;
-#pragma unroll
-      for (int i = 0; i < 16; ++i) s.G[(qr * 16 + i) * KD + col] = (pre + gv[i]) * LOG2E;
     }
     if (alive && !mbar_wait(&s.barM, mph & 1)) {
       if (tid == 0) atomicOr(p.status, 64u);
@@ -321,7 +333,10 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __g
     }
     ++mph;
     alive = __syncthreads_and(alive);      // also: G complete, hdh partials complete, phase A products complete for everybody
-    if (!alive) break;
+    if (!alive) {
+      if (tid == 0) atomicOr(p.status, 32u);
+      break;
+    }
     umma::fence_after_sync();
     if (tid < KD)
       s.hdh[tid] = s.hdh_part[0][tid] + s.hdh_part[1][tid] + s.hdh_part[2][tid] + s.hdh_part[3][tid] + s.hdh_part[4][tid] +
