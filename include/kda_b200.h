@@ -132,7 +132,9 @@ typedef struct kda_chunk_args {
   int32_t N, H, K, V;
   int32_t io_dtype;            /* KDA_BF16 */
   int32_t use_qk_l2norm;
-  int32_t save_for_backward;
+  int32_t save_for_backward;   /* bit 0: keep what kda_chunk_bwd reads in the workspace; bit 1 (with use_qk_l2norm): also keep
+                                  the normalised q, k there, so that the backward does not recompute them.  Pass the same
+                                  value to kda_chunk_workspace_bytes, kda_chunk_fwd and kda_chunk_bwd. */
   float scale;
   int32_t HQ;                  /* grouped value heads (GVA, fla/ops/kda/chunk.py:194-196,379-386): q, k, dq, dk have HQ heads
                                   ([tokens, HQ, K]) while v, g, beta, o, the states and their gradients have H; value head h reads
@@ -145,7 +147,8 @@ int64_t kda_chunk_max_chunks(int64_t tokens, int32_t N);
 size_t kda_chunk_workspace_bytes(int64_t tokens, int32_t N, int32_t H, int32_t K, int32_t V, int32_t save_for_backward);
 /* Bytes of the backward's own scratch (args->bwd_workspace); it need not outlive the backward call.
  * use_qk_l2norm is a flag word here: bit 0 = q/k are L2-normalised in the kernels, bit 1 = grouped value heads
- * (HQ < H), which needs room for the per-value-head dq, dk before they are summed. */
+ * (HQ < H), which needs room for the per-value-head dq, dk before they are summed, bit 2 = the forward kept the
+ * normalised q, k (save_for_backward bit 1), so the backward needs no room for them. */
 size_t kda_chunk_bwd_workspace_bytes(int64_t tokens, int32_t N, int32_t H, int32_t K, int32_t V, int32_t use_qk_l2norm);
 
 int kda_chunk_fwd(const kda_chunk_args* args, void* stream);

@@ -43,8 +43,10 @@ struct ChunkWs {
 inline size_t align_up(size_t x, size_t a = 256) { return (x + a - 1) / a * a; }
 
 // Lays the workspace out.  base may be NULL (sizes only).  bwd_base: separate backward scratch.
+// keep_qn: the forward keeps the L2-normalised q, k and their reciprocal norms in its workspace (then the backward
+// does not recompute them and they are not carved from the backward scratch).
 inline ChunkWs carve_ws(unsigned char* base, unsigned char* bwd_base, int64_t tokens, int N, int H, bool save,
-                        bool l2norm = true, bool gva = false) {
+                        bool l2norm = true, bool gva = false, bool keep_qn = false) {
   ChunkWs w{};
   const size_t NTmax = static_cast<size_t>(tokens / C + N);
   const size_t tiles = NTmax * static_cast<size_t>(H);
@@ -64,13 +66,18 @@ inline ChunkWs carve_ws(unsigned char* base, unsigned char* bwd_base, int64_t to
     w.RKK = take(tiles * TILE_TT);
     w.HS = take(tiles * TILE_VK);
     w.VNEWT = take(tiles * TILE_VT);
+    if (keep_qn) {
+      w.QN = reinterpret_cast<__nv_bfloat16*>(take(static_cast<size_t>(tokens) * H * KD * 2));
+      w.KN = reinterpret_cast<__nv_bfloat16*>(take(static_cast<size_t>(tokens) * H * KD * 2));
+      w.RSTD = reinterpret_cast<float*>(take(static_cast<size_t>(tokens) * H * 2 * 4));
+    }
   }
   w.fwd_bytes = off;
   size_t boff = 0;
   auto takeb = [&](size_t bytes) { unsigned char* p = bwd_base ? bwd_base + boff : nullptr; boff += align_up(bytes); return p; };
   w.DH = takeb(tiles * TILE_VK);
   w.DVNEWT = takeb(tiles * TILE_VT);
-  if (l2norm) {
+  if (l2norm && !(save && keep_qn)) {
     w.QN = reinterpret_cast<__nv_bfloat16*>(takeb(static_cast<size_t>(tokens) * H * KD * 2));
     w.KN = reinterpret_cast<__nv_bfloat16*>(takeb(static_cast<size_t>(tokens) * H * KD * 2));
     w.RSTD = reinterpret_cast<float*>(takeb(static_cast<size_t>(tokens) * H * 2 * 4));

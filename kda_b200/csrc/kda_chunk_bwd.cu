@@ -121,7 +121,7 @@ __global__ void __launch_bounds__(256) kda_group_sum_kernel(const __nv_bfloat16*
 
 extern "C" size_t kda_chunk_bwd_workspace_bytes(int64_t tokens, int32_t N, int32_t H, int32_t K, int32_t V, int32_t use_qk_l2norm) {
   (void)K; (void)V;
-  return kda::carve_ws(nullptr, nullptr, tokens, N, H, true, (use_qk_l2norm & 1) != 0, (use_qk_l2norm & 2) != 0).bwd_bytes;
+  return kda::carve_ws(nullptr, nullptr, tokens, N, H, true, (use_qk_l2norm & 1) != 0, (use_qk_l2norm & 2) != 0, (use_qk_l2norm & 4) != 0).bwd_bytes;
 }
 
 extern "C" int kda_chunk_bwd(const kda_chunk_args* args, void* stream) {
@@ -142,8 +142,9 @@ extern "C" int kda_chunk_bwd(const kda_chunk_args* args, void* stream) {
   }
   const bool l2 = a.use_qk_l2norm != 0;
   const int HQ = a.HQ > 0 ? a.HQ : a.H, grp = a.H / HQ;
+  const bool kept_qn = l2 && (a.save_for_backward & 2) != 0;      // the forward left the normalised q, k in its workspace
   ChunkWs w = carve_ws(static_cast<unsigned char*>(a.workspace), static_cast<unsigned char*>(a.bwd_workspace), a.tokens, a.N,
-                       a.H, true, l2, grp > 1);
+                       a.H, true, l2, grp > 1, (a.save_for_backward & 2) != 0);
   if (a.workspace_bytes < w.fwd_bytes || a.bwd_workspace_bytes < w.bwd_bytes) return KDA_E_WORKSPACE;
   cudaError_t e = set_bwd_attrs();
   if (e != cudaSuccess) return static_cast<int>(e);
@@ -153,9 +154,11 @@ extern "C" int kda_chunk_bwd(const kda_chunk_args* args, void* stream) {
   const __nv_bfloat16* k = static_cast<const __nv_bfloat16*>(a.k);
   ProfCall* prof = prof_begin(st);
   if (l2) {
-    kda_l2norm_fwd_kernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, st>>>(q, k, w.QN, w.KN, w.RSTD, rows);
-    if ((e = cudaGetLastError()) != cudaSuccess) return static_cast<int>(e);
-    prof_mark(prof, KDA_STAGE_L2NORM, st);
+    if (!kept_qn) {
+      kda_l2norm_fwd_kernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, st>>>(q, k, w.QN, w.KN, w.RSTD, rows);
+      if ((e = cudaGetLastError()) != cudaSuccess) return static_cast<int>(e);
+      prof_mark(prof, KDA_STAGE_L2NORM, st);
+    }
     q = w.QN;
     k = w.KN;
   }

@@ -65,6 +65,7 @@ struct PrepSmem {
   float Akk[C * AS];         // raw <k_t D, k_j>, then beta_t * raw, then Tm = (I + Akk)^-1
   __nv_bfloat16 Aqk[C * TS]; // scale <q_t D, k_j>, lower triangle incl. diagonal; after P5a the scratch X of P4
   float beta[C];
+  float rq[C], rk[C];        // reciprocal norms of the q, k rows (use_l2norm)
 };
 static_assert(TILE_VT + TILE_TK <= C * GS * 4, "staged tiles must fit the G buffer");
 
@@ -79,6 +80,9 @@ struct PrepParams {
   int use_l2norm;
   float scale;
   int HQ, grp;      // q/k heads and value heads per q/k head (grouped value heads); H counts value heads
+  __nv_bfloat16 *QN, *KN;   // [tokens][HQ][128]: the normalised q, k kept for the backward (use_l2norm, training), or NULL
+  float* RSTD;              // [2][tokens * HQ] reciprocal norms of q, k
+  long long qrows;          // tokens * HQ
 };
 
 // Sum over the 32 lanes of 32 per-lane values at once: afterwards lane L holds the total of slot L.
@@ -153,6 +157,8 @@ __device__ __forceinline__ void diag_decode(const int g, const int L, int& row, 
   col = 8 * u + (is_kk ? off - t - 1 : off);
 }
 
+// KEEP_QN: also leave the L2-normalised q, k and their reciprocal norms in the workspace (training with use_l2norm).
+template <bool KEEP_QN>
 __global__ void __launch_bounds__(256, 2) kda_chunk_prepare_kernel(const PrepParams p) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   PrepSmem& s = *reinterpret_cast<PrepSmem*>(smem_raw);
@@ -228,6 +234,10 @@ __global__ void __launch_bounds__(256, 2) kda_chunk_prepare_kernel(const PrepPar
       kr.x = pack_bf16(k0.x * rk, k0.y * rk); kr.y = pack_bf16(k1.x * rk, k1.y * rk);
       *reinterpret_cast<uint2*>(&s.q[r * QS + lane * 4]) = qr;
       *reinterpret_cast<uint2*>(&s.k[r * QS + lane * 4]) = kr;
+      if (KEEP_QN && lane == 0) {
+        s.rq[r] = rq;
+        s.rk[r] = rk;
+      }
     }
   }
   if (p.use_l2norm) __syncthreads();
@@ -388,10 +398,20 @@ __global__ void __launch_bounds__(256, 2) kda_chunk_prepare_kernel(const PrepPar
     KDA_DBG_CLOCK(p.dbg, 25);
     unsigned char* gQG = p.QG + tile * TILE_TK;
     unsigned char* gKG = p.KG + tile * TILE_TK;
+    const bool keep_qn = p.QN != nullptr && h % p.grp == 0;      // once per q/k head
     for (int i = tid; i < C * 16; i += 256) {
       const int r = i >> 4, pc = i & 15;
       const uint4 qr = *reinterpret_cast<const uint4*>(&s.q[r * QS + pc * 8]);
       const uint4 kr = *reinterpret_cast<const uint4*>(&s.k[r * QS + pc * 8]);
+      if (KEEP_QN && keep_qn && r < len) {      // the normalised q, k (and their reciprocal norms) stay for the backward
+        const long long grow = static_cast<long long>(ci.tok0 + r) * p.HQ + h / p.grp;
+        *reinterpret_cast<uint4*>(p.QN + grow * KD + pc * 8) = qr;
+        *reinterpret_cast<uint4*>(p.KN + grow * KD + pc * 8) = kr;
+        if (pc == 0) {
+          p.RSTD[grow] = s.rq[r];
+          p.RSTD[p.qrows + grow] = s.rk[r];
+        }
+      }
       const float4 Ga = *reinterpret_cast<const float4*>(&s.G[r * GS + pc * 8]);
       const float4 Gb = *reinterpret_cast<const float4*>(&s.G[r * GS + pc * 8 + 4]);
       const float4 La = *reinterpret_cast<const float4*>(&s.G[(C - 1) * GS + pc * 8]);
@@ -597,11 +617,11 @@ static cudaError_t g_attr_err = cudaSuccess;
 
 static cudaError_t set_attrs() {
   std::call_once(g_attr_once, [] {
-    cudaError_t e = cudaFuncSetAttribute(kda_chunk_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(sizeof(PrepSmem)));
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(kda_chunk_prepare_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
-                               cudaSharedmemCarveoutMaxShared);
+    cudaError_t e = cudaSuccess;
+    for (auto fn : {kda_chunk_prepare_kernel<false>, kda_chunk_prepare_kernel<true>}) {
+      if (e == cudaSuccess) e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(PrepSmem)));
+      if (e == cudaSuccess) e = cudaFuncSetAttribute(fn, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    }
     g_attr_err = e;
   });
   return g_attr_err;
@@ -637,7 +657,7 @@ extern "C" int64_t kda_chunk_max_chunks(int64_t tokens, int32_t N) { return toke
 
 extern "C" size_t kda_chunk_workspace_bytes(int64_t tokens, int32_t N, int32_t H, int32_t K, int32_t V, int32_t save) {
   (void)K; (void)V;
-  return kda::carve_ws(nullptr, nullptr, tokens, N, H, save != 0).fwd_bytes;
+  return kda::carve_ws(nullptr, nullptr, tokens, N, H, (save & 1) != 0, true, false, (save & 2) != 0).fwd_bytes;
 }
 
 extern "C" int kda_chunk_fwd(const kda_chunk_args* args, void* stream) {
@@ -656,8 +676,10 @@ extern "C" int kda_chunk_fwd(const kda_chunk_args* args, void* stream) {
     }
     return KDA_OK;
   }
-  const bool save = a.save_for_backward != 0;
-  ChunkWs w = carve_ws(static_cast<unsigned char*>(a.workspace), nullptr, a.tokens, a.N, a.H, save);
+  const bool save = (a.save_for_backward & 1) != 0;
+  const bool keep_qn = save && (a.save_for_backward & 2) != 0 && a.use_qk_l2norm != 0;
+  ChunkWs w = carve_ws(static_cast<unsigned char*>(a.workspace), nullptr, a.tokens, a.N, a.H, save, true, false,
+                       (a.save_for_backward & 2) != 0);
   if (a.workspace_bytes < w.fwd_bytes) return KDA_E_WORKSPACE;
   cudaError_t e = set_attrs();
   if (e != cudaSuccess) return static_cast<int>(e);
@@ -677,7 +699,10 @@ extern "C" int kda_chunk_fwd(const kda_chunk_args* args, void* stream) {
   pp.W = w.W; pp.UT = w.UT; pp.KG = w.KG; pp.QG = w.QG; pp.AQK = w.AQK; pp.GL = w.GL; pp.TI = save ? w.TI : nullptr; pp.RKK = save ? w.RKK : nullptr;
   pp.dbg = g_dbg_clocks; pp.N = a.N; pp.H = a.H; pp.use_l2norm = a.use_qk_l2norm; pp.scale = a.scale;
   pp.HQ = a.HQ > 0 ? a.HQ : a.H; pp.grp = a.H / pp.HQ;
-  kda_chunk_prepare_kernel<<<dim3(NTmax, a.H), 256, sizeof(PrepSmem), st>>>(pp);
+  pp.QN = keep_qn ? w.QN : nullptr; pp.KN = keep_qn ? w.KN : nullptr; pp.RSTD = keep_qn ? w.RSTD : nullptr;
+  pp.qrows = static_cast<long long>(a.tokens) * pp.HQ;
+  if (keep_qn) kda_chunk_prepare_kernel<true><<<dim3(NTmax, a.H), 256, sizeof(PrepSmem), st>>>(pp);
+  else kda_chunk_prepare_kernel<false><<<dim3(NTmax, a.H), 256, sizeof(PrepSmem), st>>>(pp);
   if ((e = cudaGetLastError()) != cudaSuccess) return static_cast<int>(e);
   prof_mark(prof, KDA_STAGE_PREPARE, st);
 

@@ -346,11 +346,12 @@ class ChunkKDAFunction(torch.autograd.Function):
             N = cu.numel() - 1
         tokens = B * T
         need_grad = any(ctx.needs_input_grad)
+        save = (1 | (2 if use_l2norm else 0)) if need_grad else 0      # bit 1: the forward keeps the normalised q, k
         lib = _lib.load()
-        ws = torch.empty(lib.kda_chunk_workspace_bytes(tokens, N, H, K, V, int(need_grad)), dtype=torch.uint8, device=dev)
+        ws = torch.empty(lib.kda_chunk_workspace_bytes(tokens, N, H, K, V, save), dtype=torch.uint8, device=dev)
         o = torch.empty_like(v)
         ht = torch.empty(N, H, K, V, dtype=torch.float32, device=dev) if output_final_state else None
-        args = _chunk_args(q, k, v, g32, beta32, h0, cu, o, ht, ws, N, H, K, V, tokens, use_l2norm, need_grad, scale)
+        args = _chunk_args(q, k, v, g32, beta32, h0, cu, o, ht, ws, N, H, K, V, tokens, use_l2norm, save, scale)
         with torch.cuda.device(dev):
             _lib.check(lib.kda_chunk_fwd(C.byref(args), _stream(dev)), "kda_chunk_fwd")
         if need_grad:
@@ -370,9 +371,9 @@ class ChunkKDAFunction(torch.autograd.Function):
         dg = torch.empty_like(g32)
         dbeta = torch.empty_like(beta32)
         dh0 = torch.empty(N, H, K, V, dtype=torch.float32, device=dev) if has_h0 else None
-        flags = int(use_l2norm) | (2 if HQ != H else 0)
+        flags = int(use_l2norm) | (2 if HQ != H else 0) | (4 if use_l2norm else 0)
         bws = torch.empty(lib.kda_chunk_bwd_workspace_bytes(tokens, N, H, K, V, flags), dtype=torch.uint8, device=dev)
-        args = _chunk_args(q, k, v, g32, beta32, h0, cu, None, None, ws, N, H, K, V, tokens, use_l2norm, True, scale,
+        args = _chunk_args(q, k, v, g32, beta32, h0, cu, None, None, ws, N, H, K, V, tokens, use_l2norm, 1 | (2 if use_l2norm else 0), scale,
                            d_o=do, d_ht=dht, dq=dq, dk=dk, dv=dv, dg=dg, dbeta=dbeta, dh0=dh0, bwd_ws=bws)
         with torch.cuda.device(dev):
             _lib.check(lib.kda_chunk_bwd(C.byref(args), _stream(dev)), "kda_chunk_bwd")
