@@ -235,6 +235,13 @@ int kda_gate_fwd(const kda_gate_args* args, void* stream);
 int kda_gate_bwd(const kda_gate_args* args, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * Strided host <-> device copy for the host-resident pipeline (no counterpart in the Python operator): `rows`
+ * rows of `width_bytes`, `spitch` / `dpitch` bytes apart, on `stream` (cudaMemcpy2DAsync, direction inferred from the
+ * pointers).  Lets a head range [h0, h1) of a pinned [tokens, H, D] tensor travel as one copy.
+ * ------------------------------------------------------------------------------------------------ */
+int kda_copy_rows_async(void* dst, size_t dpitch, const void* src, size_t spitch, size_t width_bytes, size_t rows, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
  * Per-kernel timing for benchmarks (no counterpart in the Python operator; fla times whole calls).
  * While enabled, kda_chunk_fwd / kda_chunk_bwd / kda_gate_fwd / kda_gate_bwd record a CUDA event on the call's stream before their
  * first kernel and after each kernel.  The events live in a fixed ring owned by the library (created

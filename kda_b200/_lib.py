@@ -58,7 +58,7 @@ EXPORTS = (
     "kda_chunk_max_chunks", "kda_chunk_workspace_bytes", "kda_chunk_bwd_workspace_bytes",
     "kda_chunk_fwd", "kda_chunk_bwd", "kda_chunk_fwd_noalloc", "kda_chunk_export_states",
     "kda_gate_bwd_workspace_bytes", "kda_gate_fwd", "kda_gate_bwd",
-    "kda_b200_profile_enable", "kda_b200_profile_read",
+    "kda_copy_rows_async", "kda_b200_profile_enable", "kda_b200_profile_read",
 )
 
 _lib = None
@@ -97,6 +97,8 @@ def load() -> C.CDLL:
         fn = getattr(lib, name)
         fn.restype = C.c_int
         fn.argtypes = [C.POINTER(GateArgs), C.c_void_p]
+    lib.kda_copy_rows_async.restype = C.c_int
+    lib.kda_copy_rows_async.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_void_p]
     lib.kda_b200_profile_enable.restype = C.c_int
     lib.kda_b200_profile_enable.argtypes = [C.c_int]
     lib.kda_b200_profile_read.restype = C.c_int

@@ -21,6 +21,13 @@ extern "C" const char* kda_b200_strerror(int code) {
   return "unknown kda_b200 error code";
 }
 
+extern "C" int kda_copy_rows_async(void* dst, size_t dpitch, const void* src, size_t spitch, size_t width_bytes, size_t rows, void* stream) {
+  if (!dst || !src) return KDA_E_NULL;
+  if (rows == 0 || width_bytes == 0) return KDA_OK;
+  if (dpitch < width_bytes || spitch < width_bytes) return KDA_E_SHAPE;
+  return static_cast<int>(cudaMemcpy2DAsync(dst, dpitch, src, spitch, width_bytes, rows, cudaMemcpyDefault, static_cast<cudaStream_t>(stream)));
+}
+
 // ---- per-kernel timing ------------------------------------------------------------------------------
 #include <mutex>
 #include <vector>

@@ -19,6 +19,8 @@ def test_host_pipeline_matches_whole_batch():
     o, ht = chunk_kda(c["q"], c["k"], c["v"], c["g"], c["beta"], initial_state=c["h0"], output_final_state=True)
     grads = torch.autograd.grad([o, ht], leaves, [c["do"], c["dht"]])
     ref = dict(o=o, ht=ht, dq=grads[0], dk=grads[1], dv=grads[2], dg=grads[3], dbeta=grads[4], dh0=grads[5])
+    out3 = chunk_kda_fwd_bwd_host(pinned, None, slices=4, head_groups=2)      # also cut along the head axis (strided copies)
     for n, r in ref.items():
         assert out2[n].is_pinned()
         assert torch.equal(out2[n], r.detach().cpu()), n
+        assert torch.equal(out3[n], r.detach().cpu()), (n, "head groups")
