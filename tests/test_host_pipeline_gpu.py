@@ -24,3 +24,21 @@ def test_host_pipeline_matches_whole_batch():
         assert out2[n].is_pinned()
         assert torch.equal(out2[n], r.detach().cpu()), n
         assert torch.equal(out3[n], r.detach().cpu()), (n, "head groups")
+
+
+def test_first_backward_on_a_worker_thread_in_a_fresh_process():
+    """The backward builds TMA tensor maps with a driver call that needs a context bound to the calling thread; the very
+    first backward of a process may run on an autograd worker thread that has none yet."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = (
+        "import torch, sys; sys.path.insert(0, %r)\n"
+        "from kda_b200.inputs import make_inputs\n"
+        "from kda_b200.host import chunk_kda_fwd_bwd_host\n"
+        "d = make_inputs(2, 100, 2, 128, 128, torch.bfloat16, seed=1, h0_std=0.02, backward=True)\n"
+        "out = chunk_kda_fwd_bwd_host({n: t.pin_memory() for n, t in d.items() if t is not None})\n"
+        "assert all(torch.isfinite(t.float()).all() for t in out.values()); print('ok')\n" % root)
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "ok" in r.stdout, r.stderr[-2000:]
