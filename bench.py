@@ -61,7 +61,7 @@ KERNEL_WORK = {
 # DRAM bytes per (token, head) that ncu measured (dram__bytes_read.sum + dram__bytes_write.sum of one launch) on a
 # small case of each kernel (B=1 T=8192, 262,144 (token, head) units; summaries under profiles/).  Traffic grows in
 # proportion to the units, so a launch's traffic is this figure times its units.
-KERNEL_TRAFFIC = {"prepare": 2528.0, "scan": 2037.0, "bwd_scan": 1807.0, "bwd_main": 4521.0, "decode": 125600.0}
+KERNEL_TRAFFIC = {"prepare": 2533.0, "scan": 2043.0, "bwd_scan": 1814.0, "bwd_main": 4577.0, "decode": 125600.0}
 
 
 def load_peaks():

@@ -92,7 +92,7 @@ def _gated_inputs(T, seed, B=1, H=2):
 @pytest.mark.parametrize("raw_dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("lb", [None, -5.0])
 def test_chunk_kda_with_gate_in_kernel(lb, raw_dtype):
-    """bf16 raw gate input: the chunk kernels apply the activation themselves; fp32: the gate kernel runs first.
+    """bf16 and fp32 raw gate input; the gate kernels run in front of the chunk kernels and behind their backward.
     The operator as the layer calls it (raw gate, beta logits, l2norm in kernel), forward and every gradient
     including A_log and dt_bias, against float64 autograd through oracle gate + oracle recurrence (bf16 mode:
     2e-2 max-normalised and cosine 0.9999; dA_log and ddt_bias are sums over all tokens of the bf16-noisy dg with
