@@ -16,7 +16,8 @@ events recorded by the library around each kernel during the timed steps), `cpu_
 float32 token-recurrent PyTorch restatement on the host cores, bounded sample), clocks, launches.
 
 `--impl reference` times that CPU restatement alone, on all host threads (the NVlabs/kda repository
-has no implementation of this operator to run).
+has no implementation of this operator to run).  `--gpu-bar` adds a `gpu_bar` object: flash-linear-attention's
+own Triton chunk_kda timed on the same GPU and inputs, when that package imports (a comparison, off by default).
 """
 from __future__ import annotations
 
@@ -164,6 +165,48 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
+def time_fla_triton(args, w, devt, cu, grad_names, tokens):
+    """The on-box GPU comparison: flash-linear-attention's own chunk_kda (Triton) on the same inputs, same step
+    definition (forward, or forward + backward with the same output gradients), CUDA events, same warm-up rule.
+    A comparison line only: nothing of it is on the product path."""
+    if args.workload == "decode" or args.gate:
+        return {"unavailable": "timed for the chunked workloads without the gate front end"}
+    try:
+        from fla.ops.kda import chunk_kda as fla_chunk_kda
+    except Exception as e:          # noqa: BLE001
+        return {"unavailable": f"fla does not import on this box: {type(e).__name__}: {e}"[:200]}
+    x = devt
+
+    def step():
+        if w.backward:
+            leaves = [x[n].detach().requires_grad_(True) for n in grad_names]
+            t = dict(zip(grad_names, leaves))
+            o, ht = fla_chunk_kda(t["q"], t["k"], t["v"], t["g"], t["beta"], initial_state=t.get("h0"),
+                                  output_final_state=True, cu_seqlens=cu)
+            return torch.autograd.grad([o, ht], leaves, [x["do"], x["dht"]])
+        with torch.no_grad():
+            return fla_chunk_kda(x["q"], x["k"], x["v"], x["g"], x["beta"], initial_state=x.get("h0"),
+                                 output_final_state=True, cu_seqlens=cu)
+    try:
+        for _ in range(args.warmup):
+            step()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n = max(1, min(args.steps, 10))
+        e0.record()
+        for _ in range(n):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / n
+    except Exception as e:          # noqa: BLE001
+        return {"unavailable": f"fla.ops.kda.chunk_kda failed on this box: {type(e).__name__}: {e}"[:300]}
+    import fla
+    import triton
+    return {"impl": f"fla.ops.kda.chunk_kda (flash-linear-attention {getattr(fla, '__version__', '?')}, Triton {triton.__version__})",
+            "value": tokens / (ms / 1e3), "unit": "tokens/s", "ms_per_step": ms, "steps": n}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -177,6 +220,9 @@ def main():
     ap.add_argument("--gate", action="store_true",
                     help="call the operator as the layer does: raw bf16 gate input + A_log + dt_bias and beta logits "
                          "(use_gate_in_kernel, use_beta_sigmoid_in_kernel); training workloads only")
+    ap.add_argument("--gpu-bar", action="store_true",
+                    help="also time fla.ops.kda.chunk_kda (the Triton kernels of flash-linear-attention, if it imports on "
+                         "this box) on the same device-resident inputs: the on-box GPU comparison; 1 GPU only")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -318,6 +364,10 @@ def main():
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": n_e2e,
                "api": "kda_b200.host.chunk_kda_fwd_bwd_host (batch slices pipelined over 3 streams)" if pipelined else "kda_b200.chunk_kda"}
 
+    gpu_bar = None
+    if args.gpu_bar:
+        gpu_bar = time_fla_triton(args, w, devt, cu, grad_names, tokens) if world == 1 else {"unavailable": "timed on 1 GPU only"}
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -379,6 +429,8 @@ def main():
         "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
         "roofline": roof, "step_roofline": whole, "kernels": kernels, "cpu_baseline": cpu,
     }
+    if gpu_bar is not None:
+        line["gpu_bar"] = gpu_bar
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

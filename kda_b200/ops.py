@@ -429,9 +429,9 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
     tensor is [.., V, K] instead of [.., K, V].
 
     bf16 inputs with K = V = 128 take the chunked tensor-core kernels.  float32 inputs take the exact
-    token-recurrent fp32 kernel (forward only).  `safe_gate` and `disable_recompute` only select
-    faster variants upstream and are accepted as no-ops (the kernels here are range-safe for any gate);
-    options that change results and are not built raise.
+    token-recurrent fp32 kernel (forward only).  `safe_gate`, `disable_recompute` and `chunk_size` (32 or 64) only
+    select variants of the same computation upstream and are accepted as no-ops (the kernels here are range-safe
+    for any gate and always tile by 64 tokens); options that change results and are not built raise.
     """
     _unsupported("cp_context", cp_context, None)
     if "use_qk_l2norm" in kwargs:
@@ -439,8 +439,11 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
     chunk_size = kwargs.pop("chunk_size", 64)
     if chunk_size not in (32, 64):
         raise ValueError(f"`chunk_size` must be either 32 or 64 for KDA, got {chunk_size}.")
-    if chunk_size != CHUNK:
-        raise NotImplementedError("kda_b200: only chunk_size=64 is implemented")
+    # chunk_size only selects how the same recurrence is tiled: o, the final state and every gradient are the same
+    # function of the inputs for 32 and 64, so both run on the 64-token tiles.  Only the intermediate states depend on
+    # it (one state per chunk).
+    if chunk_size != CHUNK and return_intermediate_states:
+        raise NotImplementedError("kda_b200: return_intermediate_states gives one state per 64 tokens; chunk_size=32 is not built for it")
     B, T, H, K, V = _check_common(q, k, v, g, beta, initial_state, cu_seqlens)
     if scale is None:
         scale = K ** -0.5

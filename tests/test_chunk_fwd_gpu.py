@@ -138,3 +138,25 @@ def test_return_intermediate_states():
     assert max_norm_err(hv[0, 2], dv["h0"][1].double()) <= 2e-2
     with pytest.raises(AssertionError, match="inference mode"):
         chunk_kda(c["q"], c["k"], c["v"], c["g"], c["beta"], return_intermediate_states=True)
+
+
+def test_chunk_size_32_is_the_same_function():
+    """fla allows chunk_size 32 or 64 (fla/ops/kda/chunk.py:365-367); it only selects the tiling, so o, the final state
+    and the gradients are those of the 64-token tiles, bit for bit here, and within tolerance of the oracle."""
+    from kda_b200 import chunk_kda
+    from oracle.kda_oracle import recurrent_kda
+    d = make_inputs(1, 150, 2, 128, 128, torch.bfloat16, seed=79, h0_std=0.02)
+    outs = []
+    for cs in (32, 64):
+        c = {n: t.cuda().requires_grad_(True) for n, t in d.items() if n in ("q", "k", "v", "g", "beta", "h0")}
+        o, ht = chunk_kda(c["q"], c["k"], c["v"], c["g"], c["beta"], initial_state=c["h0"], output_final_state=True, chunk_size=cs)
+        (o.float().sum() + ht.sum()).backward()
+        outs.append([o.detach(), ht.detach()] + [c[n].grad for n in ("q", "k", "v", "g", "beta", "h0")])
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
+    o_ref, ht_ref = recurrent_kda(d["q"], d["k"], d["v"], d["g"], d["beta"], initial_state=d["h0"], output_final_state=True)
+    assert max_norm_err(outs[0][0], o_ref) <= 2e-2 and max_norm_err(outs[0][1], ht_ref) <= 2e-2
+    with pytest.raises(ValueError, match="32 or 64"):
+        chunk_kda(*(d[n].cuda() for n in ("q", "k", "v", "g", "beta")), chunk_size=16)
+    with torch.inference_mode(), pytest.raises(NotImplementedError, match="chunk_size=32"):
+        chunk_kda(*(d[n].cuda() for n in ("q", "k", "v", "g", "beta")), chunk_size=32, return_intermediate_states=True)
