@@ -31,7 +31,7 @@ extern "C" {
 #pragma GCC visibility push(default) /* the entry points below are the library's only exports */
 #endif
 
-#define KDA_B200_ABI_VERSION 4
+#define KDA_B200_ABI_VERSION 5
 #define KDA_CHUNK 64 /* tokens per chunk of the chunked kernels */
 
 /* io_dtype of q, k, v, o and of their gradients */
@@ -89,6 +89,13 @@ typedef struct kda_recurrent_args {
 } kda_recurrent_args;
 
 int kda_recurrent_fwd(const kda_recurrent_args* args, void* stream);
+
+/* Large decode batches (one token per sequence, K = V = 128, at least four (sequence, head) units per SM) run on a
+ * kernel that moves the states with the bulk-copy engine and waits for them on barriers with a bounded number of
+ * polls.  This call copies the device status word of that kernel to *host_out and clears it (it synchronises with
+ * the device: a diagnostic, not part of the step).  0: every wait completed; bit 0: a wait gave up and the outputs
+ * of that step are incomplete. */
+int kda_recurrent_status(uint32_t* host_out);
 
 /* ------------------------------------------------------------------------------------------------
  * Chunked forward / backward (chunk = 64 tokens), bf16 tensor-core path, K = V = 128.

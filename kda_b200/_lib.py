@@ -11,7 +11,7 @@ LIB_PATH = os.path.join(PKG, "libkda_b200.so")
 
 KDA_BF16, KDA_FP32 = 0, 1
 NOALLOC_SCRATCH_BYTES = 32 << 20
-ABI_VERSION = 4
+ABI_VERSION = 5
 
 
 class RecurrentArgs(C.Structure):
@@ -54,7 +54,7 @@ class GateArgs(C.Structure):
 
 
 EXPORTS = (
-    "kda_b200_abi_version", "kda_b200_strerror", "kda_recurrent_fwd",
+    "kda_b200_abi_version", "kda_b200_strerror", "kda_recurrent_fwd", "kda_recurrent_status",
     "kda_chunk_max_chunks", "kda_chunk_workspace_bytes", "kda_chunk_bwd_workspace_bytes",
     "kda_chunk_fwd", "kda_chunk_bwd", "kda_chunk_fwd_noalloc", "kda_chunk_export_states",
     "kda_gate_bwd_workspace_bytes", "kda_gate_fwd", "kda_gate_bwd",
@@ -79,6 +79,8 @@ def load() -> C.CDLL:
     lib.kda_b200_strerror.argtypes = [C.c_int]
     lib.kda_recurrent_fwd.restype = C.c_int
     lib.kda_recurrent_fwd.argtypes = [C.POINTER(RecurrentArgs), C.c_void_p]
+    lib.kda_recurrent_status.restype = C.c_int
+    lib.kda_recurrent_status.argtypes = [C.POINTER(C.c_uint32)]
     lib.kda_chunk_max_chunks.restype = C.c_int64
     lib.kda_chunk_max_chunks.argtypes = [C.c_int64, C.c_int32]
     lib.kda_chunk_workspace_bytes.restype = C.c_size_t
@@ -124,6 +126,13 @@ STAGES = ("tables", "prepare", "scan", "bwd_scan", "bwd_main", "bwd_finish", "l2
 
 def profile_enable(on: bool) -> None:
     check(load().kda_b200_profile_enable(int(on)), "kda_b200_profile_enable")
+
+
+def recurrent_status() -> int:
+    """Status word of the bulk-copy decode kernel since the last call (0 = every bounded wait completed); synchronises."""
+    v = C.c_uint32(0)
+    check(load().kda_recurrent_status(C.byref(v)), "kda_recurrent_status")
+    return int(v.value)
 
 
 def profile_read(reset: bool = True) -> dict:

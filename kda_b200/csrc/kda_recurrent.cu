@@ -349,6 +349,9 @@ static int dispatch_rec(const kda_recurrent_args& a, cudaStream_t st) {
   }
 }
 
+bool decode_bulk_covers(const kda_recurrent_args& a);                    // kda_decode_bulk.cu
+int decode_bulk_launch(const kda_recurrent_args& a, cudaStream_t st);
+
 }  // namespace kda
 
 extern "C" int kda_recurrent_fwd(const kda_recurrent_args* args, void* stream) {
@@ -380,6 +383,7 @@ extern "C" int kda_recurrent_fwd(const kda_recurrent_args* args, void* stream) {
                          reinterpret_cast<uintptr_t>(a.ht);
   if (bits & 15u) return KDA_E_ALIGN;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (kda::decode_bulk_covers(a)) return kda::decode_bulk_launch(a, st);
   if (a.io_dtype == KDA_BF16) return kda::dispatch_rec<__nv_bfloat16>(a, st);
   if (a.io_dtype == KDA_FP32) return kda::dispatch_rec<float>(a, st);
   return KDA_E_DTYPE;

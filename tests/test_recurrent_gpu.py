@@ -79,6 +79,44 @@ def test_decode_inplace_steps_match_scan():
     assert torch.count_nonzero(pool[1]) == 0 and torch.count_nonzero(pool[3]) == 0
 
 
+@pytest.mark.parametrize("case", ["plain", "l2norm_slots_gva", "fp32"])
+def test_large_decode_batch_bulk_copy_kernel(case):
+    """640 (sequence, head) units with one token each: the step runs on the kernel that moves whole state tiles with the
+    bulk-copy engine (at least four units per SM).  o and the new states against the float64 oracle: bf16 o 2e-2,
+    fp32 o and the fp32 states 1e-4 (max-normalised); untouched slots stay untouched; the status word stays 0."""
+    from kda_b200 import _lib, fused_recurrent_kda_fwd
+    N, H = 40, 16
+    dtype = torch.float32 if case == "fp32" else torch.bfloat16
+    d = make_inputs(N, 1, H, 128, 128, dtype, seed=21, h0_std=0.05)
+    l2 = case == "l2norm_slots_gva"
+    HQ = 4 if l2 else H
+    q, k = d["q"][:, :, :HQ].contiguous(), d["k"][:, :, :HQ].contiguous()
+    if l2:
+        q, k = q * 3, k * 0.5                      # not normalised on entry
+    rep = H // HQ
+    o_ref, h_ref = recurrent_kda(q.repeat_interleave(rep, 2), k.repeat_interleave(rep, 2), d["v"], d["g"], d["beta"],
+                                 scale=0.11, initial_state=d["h0"], output_final_state=True, use_qk_l2norm=l2)
+    c = _cuda(d)
+    if l2:
+        perm = torch.randperm(N + 8, generator=torch.Generator().manual_seed(1))[:N].to(torch.int32).cuda()
+        pool = torch.full((N + 8, H, 128, 128), 7.0, device="cuda")
+        pool[perm.long()] = c["h0"]
+        o, ret = fused_recurrent_kda_fwd(q.cuda(), k.cuda(), c["v"], c["g"], c["beta"], scale=0.11, initial_state=pool,
+                                         inplace_final_state=True, ssm_state_indices=perm, use_qk_l2norm_in_kernel=True)
+        assert ret.data_ptr() == pool.data_ptr()
+        ht = pool[perm.long()]
+        rest = sorted(set(range(N + 8)) - set(perm.tolist()))
+        assert all(bool((pool[i] == 7.0).all()) for i in rest)
+    else:
+        h0_before = c["h0"].clone()
+        o, ht = fused_recurrent_kda_fwd(q.cuda(), k.cuda(), c["v"], c["g"], c["beta"], scale=0.11, initial_state=c["h0"],
+                                        inplace_final_state=False, output_final_state=True)
+        assert torch.equal(c["h0"], h0_before)
+    assert _lib.recurrent_status() == 0
+    assert max_norm_err(o, o_ref) <= (1e-4 if case == "fp32" else 2e-2) and cosine(o, o_ref) >= 0.9999
+    assert max_norm_err(ht, h_ref) <= 1e-4
+
+
 def test_speculative_decoding_state_slots():
     """Continuous batching with per-token state slots (fla/ops/kda/fused_recurrent.py:122-144,195-210): a sequence
     starts from the slot of its last accepted token and the state after draft token t lands in slot [n, t]."""
