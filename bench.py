@@ -385,7 +385,7 @@ def main():
     if args.workload == "decode":
         byt = B * H * decode_bytes_per_seq_head()
         ach = byt / (ms_step * 1e-3) / 1e9
-        roof = {"kernel": "kda_recurrent_kernel", "bound": "hbm", "achieved": ach, "peak": peaks["hbm"], "unit": "GB/s",
+        roof = {"kernel": "kda_decode_bulk_kernel", "bound": "hbm", "achieved": ach, "peak": peaks["hbm"], "unit": "GB/s",
                 "frac": ach / peaks["hbm"], "traffic": KERNEL_TRAFFIC["decode"] * B * H,
                 "traffic_source": "ncu capture of a smaller case, scaled by units", "peak_source": peaks["src"]}
         kernels = {}
