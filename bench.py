@@ -332,7 +332,20 @@ def main():
     ms_total = maxms(e0.elapsed_time(e1))
     stages = _lib.profile_read(reset=True)
     _lib.profile_enable(False)
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = None
+    if rank == 0:
+        # a timed region of a few milliseconds (decode) ends before nvidia-smi delivers: keep the same step running,
+        # untimed, until a few samples under load exist
+        extended = False
+        t_ext = time.time()
+        while len(sampler.lines) < 5 and sampler.proc is not None and time.time() - t_ext < 4.0:
+            extended = True
+            for _ in range(8):
+                step()
+            torch.cuda.synchronize()
+        clocks = sampler.stop()
+        if extended:
+            clocks["note"] = "timed region shorter than the sampling interval: sampled over untimed repeats of the same step right after it"
     ms_step = ms_total / args.steps
     value = world * tokens / (ms_step / 1e3)
 
