@@ -227,6 +227,7 @@ def main():
     ap.add_argument("--gate", action="store_true",
                     help="call the operator as the layer does: raw bf16 gate input + A_log + dt_bias and beta logits "
                          "(use_gate_in_kernel, use_beta_sigmoid_in_kernel); training workloads only")
+    ap.add_argument("--l2norm", action="store_true", help="use_qk_l2norm_in_kernel=True (chunked workloads)")
     ap.add_argument("--gpu-bar", action="store_true",
                     help="also time fla.ops.kda.chunk_kda (the Triton kernels of flash-linear-attention, if it imports on "
                          "this box) on the same device-resident inputs: the on-box GPU comparison; 1 GPU only")
@@ -299,7 +300,7 @@ def main():
             leaves = [x[n].requires_grad_(True) for n in grad_names]
             kw = dict(gate_kw, A_log=x["A_log"], dt_bias=x["dt_bias"]) if args.gate else {}
             o, ht = chunk_kda(x["q"], x["k"], x["v"], x["g"], x["beta"], initial_state=x.get("h0"),
-                              output_final_state=True, cu_seqlens=cu, **kw)
+                              output_final_state=True, cu_seqlens=cu, use_qk_l2norm_in_kernel=args.l2norm, **kw)
             grads = torch.autograd.grad([o, ht], leaves, [x["do"], x["dht"]])
             return (o, ht) + tuple(grads)
         launches_per_step = 10 if args.gate else 5      # gate: + activation, beta sigmoid; + their backward and the reduction
@@ -309,7 +310,7 @@ def main():
         def step(x=devt):
             with torch.no_grad():
                 return chunk_kda(x["q"], x["k"], x["v"], x["g"], x["beta"], initial_state=x.get("h0"),
-                                 output_final_state=True, cu_seqlens=cu)
+                                 output_final_state=True, cu_seqlens=cu, use_qk_l2norm_in_kernel=args.l2norm)
         launches_per_step = 3
 
     # ---------------- kernel-resident timing ----------------
@@ -353,7 +354,7 @@ def main():
     e2e = None
     if not args.no_e2e:
         out_host = None
-        pipelined = w.backward and cu is None and args.workload != "decode" and not args.gate
+        pipelined = w.backward and cu is None and args.workload != "decode" and not args.gate and not args.l2norm
 
         def e2e_step():
             nonlocal out_host
@@ -442,13 +443,14 @@ def main():
                          f"{reps} x (B=1 T=512 H=32 K=V=128), {spent:.1f} s"}
 
     line = {
-        "metric": METRIC if (args.workload == "train_bf16" and not args.gate) else f"KDA {args.workload}{' +gate' if args.gate else ''} tokens/s",
+        "metric": METRIC if (args.workload == "train_bf16" and not args.gate and not args.l2norm) else
+                  f"KDA {args.workload}{' +gate' if args.gate else ''}{' +l2norm' if args.l2norm else ''} tokens/s",
         "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"{args.workload} (B={B} T={T} H={H} K=V=128, chunk 64"
                                f"{', fwd+bwd' if w.backward else ''}{', packed varlen' if cu is not None else ''}"
-                               f"{', gate + beta sigmoid in kernel' if args.gate else ''})",
+                               f"{', gate + beta sigmoid in kernel' if args.gate else ''}{', q/k l2norm in kernel' if args.l2norm else ''})",
                    "per_gpu_batch": B, "l2": "inputs (>= 3 GB per step) far exceed the 126 MB L2; no flush needed",
                    "seed": "rank"},
         "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,

@@ -188,6 +188,9 @@ extern "C" int kda_chunk_bwd(const kda_chunk_args* args, void* stream) {
       make_rows_tmap(&mp.tm_do, a.d_o, false, a.tokens, a.H, VD, 64, C, true))
     return KDA_E_DEVICE;
   mp.N = a.N; mp.H = a.H; mp.scale = a.scale; mp.grp = grp;
+  // without grouped heads the normalisation's backward is applied by bwd_main's own epilogue
+  const bool fused_l2 = l2 && grp == 1;
+  mp.rstd = fused_l2 ? w.RSTD : nullptr; mp.qrows = rows;
   if ((e = launch_bwd_main_tc(mp, main_grid(NTmax, a.H), st)) != cudaSuccess) return static_cast<int>(e);
   if (grp > 1) {
     const long long pieces = rows * (KD / 8);
@@ -197,7 +200,7 @@ extern "C" int kda_chunk_bwd(const kda_chunk_args* args, void* stream) {
   }
   prof_mark(prof, KDA_STAGE_BWD_MAIN, st);
 
-  if (l2) {
+  if (l2 && !fused_l2) {
     kda_l2norm_bwd_kernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, st>>>(w.QN, w.KN, w.RSTD, static_cast<__nv_bfloat16*>(a.dq),
                                                                                   static_cast<__nv_bfloat16*>(a.dk), rows);
     if ((e = cudaGetLastError()) != cudaSuccess) return static_cast<int>(e);

@@ -19,6 +19,8 @@ struct MainParams {
   int N, H;
   float scale;
   int grp;          // value heads per q/k head (grouped value heads): the q, k maps have H / grp heads
+  const float* rstd;    // [2][qrows] reciprocal norms of the q, k rows, or NULL.  Not NULL (only with grp == 1): q, k are the
+  long long qrows;      // L2-normalised rows and the kernel applies the normalisation's backward to dq, dk before storing them
   // tiled-load maps of the [tokens, H, 128] operator tensors (64-token boxes of one head)
   alignas(64) CUtensorMap tm_q, tm_k, tm_g;   // plain row-major boxes [64][128]
   alignas(64) CUtensorMap tm_v, tm_do;        // 64-column boxes in the 128-byte-swizzled operand layout

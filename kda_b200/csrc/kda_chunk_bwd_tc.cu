@@ -90,6 +90,8 @@ __device__ __forceinline__ unsigned char* sw_piece(unsigned char* tile, int row,
 
 }  // namespace
 
+// L2: q, k are L2-normalised rows and dq, dk leave through the normalisation's backward (fla/modules/l2norm.py:190-240).
+template <bool L2>
 __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __grid_constant__ MainParams p) {
   extern __shared__ unsigned char smem_raw[];
   TcSmem& s = *reinterpret_cast<TcSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -745,6 +747,22 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __g
         }
         s.carry[blk][kk] = run;
       }
+      // L2: the normalised q, k pieces and the reciprocal norms this thread needs for its two copy-out pieces, asked
+      // for before the barrier so that they arrive behind it
+      uint4 yq2[2], yk2[2];
+      float rq2[2], rk2[2];
+      if constexpr (L2) {
+        static_assert(C * 16 == 2 * NT, "two copy-out pieces per thread");
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int i = tid + u * NT, r = i >> 4, pc = i & 15;
+          const size_t grow = static_cast<size_t>(ci.tok0 + (r < len ? r : 0)) * p.H + h;
+          yq2[u] = __ldg(reinterpret_cast<const uint4*>(p.q + grow * KD + pc * 8));
+          yk2[u] = __ldg(reinterpret_cast<const uint4*>(p.k + grow * KD + pc * 8));
+          rq2[u] = __ldg(p.rstd + grow);
+          rk2[u] = __ldg(p.rstd + p.qrows + grow);
+        }
+      }
       __syncthreads();       // block totals and the staged dq, dk are complete
       {
         float add = 0.f;             // totals of the later blocks
@@ -755,12 +773,46 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __g
         for (int i = 0; i < 16; ++i)
           if (t0 + i < len) dgp[static_cast<size_t>(i) * p.H * KD] = dGv[i] + add;
       }
-      for (int i = tid; i < C * 16; i += NT) {
-        const int r = i >> 4, pc = i & 15;
+#pragma unroll
+      for (int u = 0; u < C * 16 / NT; ++u) {
+        const int i = tid + u * NT, r = i >> 4, pc = i & 15;
+        const size_t row = (static_cast<size_t>(ci.tok0 + (r < len ? r : 0)) * p.H + h) * KD + pc * 8;
+        uint4 oq = *reinterpret_cast<const uint4*>(&stq[r * KD + pc * 8]);
+        uint4 ok = *reinterpret_cast<const uint4*>(&stk[r * KD + pc * 8]);
+        if constexpr (L2) {
+          // dx = rstd (dy - y <y, dy>) per row; sixteen consecutive lanes hold one row (y: the normalised q, k, re-read
+          // from global memory -- the tile loaded them a few microseconds ago; dy: the staged bf16 values, as the
+          // separate pass would read them)
+          const uint4 yq = yq2[u], yk = yk2[u];
+          const uint32_t dqw[4] = {oq.x, oq.y, oq.z, oq.w}, dkw[4] = {ok.x, ok.y, ok.z, ok.w};
+          const uint32_t yqw[4] = {yq.x, yq.y, yq.z, yq.w}, ykw[4] = {yk.x, yk.y, yk.z, yk.w};
+          float2 dqf[4], dkf[4], yqf[4], ykf[4];
+          float sq = 0.f, sk = 0.f;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            dqf[e] = unpack_bf16(dqw[e]); dkf[e] = unpack_bf16(dkw[e]);
+            yqf[e] = unpack_bf16(yqw[e]); ykf[e] = unpack_bf16(ykw[e]);
+            sq = fmaf(yqf[e].x, dqf[e].x, fmaf(yqf[e].y, dqf[e].y, sq));
+            sk = fmaf(ykf[e].x, dkf[e].x, fmaf(ykf[e].y, dkf[e].y, sk));
+          }
+#pragma unroll
+          for (int o = 8; o >= 1; o >>= 1) {
+            sq += __shfl_xor_sync(0xffffffffu, sq, o);
+            sk += __shfl_xor_sync(0xffffffffu, sk, o);
+          }
+          const float rq = rq2[u], rk = rk2[u];
+          uint32_t wq[4], wk[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            wq[e] = pack_bf16(rq * (dqf[e].x - yqf[e].x * sq), rq * (dqf[e].y - yqf[e].y * sq));
+            wk[e] = pack_bf16(rk * (dkf[e].x - ykf[e].x * sk), rk * (dkf[e].y - ykf[e].y * sk));
+          }
+          oq = make_uint4(wq[0], wq[1], wq[2], wq[3]);
+          ok = make_uint4(wk[0], wk[1], wk[2], wk[3]);
+        }
         if (r < len) {
-          const size_t row = (static_cast<size_t>(ci.tok0 + r) * p.H + h) * KD + pc * 8;
-          *reinterpret_cast<uint4*>(p.dq + row) = *reinterpret_cast<const uint4*>(&stq[r * KD + pc * 8]);
-          *reinterpret_cast<uint4*>(p.dk + row) = *reinterpret_cast<const uint4*>(&stk[r * KD + pc * 8]);
+          *reinterpret_cast<uint4*>(p.dq + row) = oq;
+          *reinterpret_cast<uint4*>(p.dk + row) = ok;
         }
       }
     }
@@ -781,10 +833,13 @@ cudaError_t launch_bwd_main_tc(const MainParams& p, int grid, cudaStream_t st) {
   static cudaError_t attr_err = cudaSuccess;
   const int smem = static_cast<int>(sizeof(TcSmem)) + 1024;
   std::call_once(once, [&] {
-    attr_err = cudaFuncSetAttribute(kda_chunk_bwd_main_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    attr_err = cudaFuncSetAttribute(kda_chunk_bwd_main_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (attr_err == cudaSuccess)
+      attr_err = cudaFuncSetAttribute(kda_chunk_bwd_main_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   });
   if (attr_err != cudaSuccess) return attr_err;
-  kda_chunk_bwd_main_tc_kernel<<<grid, NT, smem, st>>>(p);
+  if (p.rstd != nullptr && p.grp == 1) kda_chunk_bwd_main_tc_kernel<true><<<grid, NT, smem, st>>>(p);
+  else kda_chunk_bwd_main_tc_kernel<false><<<grid, NT, smem, st>>>(p);
   return cudaGetLastError();
 }
 
