@@ -57,6 +57,8 @@ class HostPipeline:
         self.s_in = torch.cuda.Stream(self.device)
         self.s_out = torch.cuda.Stream(self.device)
         self._stage = {}
+        self._slot_free = [None, None]      # per staging slot: the event after which its tensors may be overwritten
+        self._end = None                    # the event behind the last step's last copy-out
 
     def _staging(self, slot, name, shape, dtype):
         key = (slot, name, tuple(shape), dtype)
@@ -66,10 +68,19 @@ class HostPipeline:
             self._stage[key] = buf
         return buf
 
+    def synchronize(self) -> None:
+        """Blocks until the results of every step issued so far have landed in host memory."""
+        if self._end is not None:
+            self._end.synchronize()
+
     def fwd_bwd(self, host_in: dict, host_out: dict | None = None, slices: int | None = None, head_groups: int | None = None,
-                **kwargs) -> dict:
+                wait: bool = True, **kwargs) -> dict:
         """host_in: pinned CPU tensors q,k,v,g,beta,do (+ h0, dht); returns pinned CPU tensors
-        o, ht, dq, dk, dv, dg, dbeta (+ dh0).  Blocks until every result has landed in host memory.
+        o, ht, dq, dk, dv, dg, dbeta (+ dh0).  Blocks until every result has landed in host memory -- unless
+        `wait=False`: then the call returns as soon as the step is queued, the results are valid after `synchronize()`,
+        and the next step's copy-in overlaps this step's copy-out (a training loop over host-resident batches keeps both
+        directions of the link busy; give consecutive steps different `host_out` buffers if step i's results are read
+        while step i+1 runs).
 
         The batch is cut into `slices` along the batch axis and every slice into `head_groups` along the head axis
         (strided copies): the pipeline's fill and drain cost one piece each way, so more, smaller pieces bring the step
@@ -85,17 +96,18 @@ class HostPipeline:
         if host_out is None:
             host_out = {}
         compute = torch.cuda.current_stream(self.device)
-        start = torch.cuda.Event()
-        start.record(compute)
-        self.s_in.wait_event(start)
-        self.s_out.wait_event(start)
+        if wait:
+            start = torch.cuda.Event()
+            start.record(compute)
+            self.s_in.wait_event(start)
+            self.s_out.wait_event(start)
         done_ev = [None] * len(pieces)
         keep = []
         for s, (b0, b1, h0, h1) in enumerate(pieces):
             slot = s & 1
             with torch.cuda.stream(self.s_in):
-                if s >= 2:
-                    self.s_in.wait_event(done_ev[s - 2])          # the staging slot is free again
+                if self._slot_free[slot] is not None:
+                    self.s_in.wait_event(self._slot_free[slot])   # the staging slot is free again (also across steps)
                 dev = {}
                 for name in _IN:
                     t = host_in.get(name)
@@ -128,6 +140,7 @@ class HostPipeline:
                     dev[nm].requires_grad_(False)
             done_ev[s] = torch.cuda.Event()
             done_ev[s].record(compute)
+            self._slot_free[slot] = done_ev[s]
             with torch.cuda.stream(self.s_out):
                 self.s_out.wait_event(done_ev[s])
                 for name, t in outs.items():
@@ -146,19 +159,30 @@ class HostPipeline:
             keep.append(outs)
         end = torch.cuda.Event()
         end.record(self.s_out)
-        compute.wait_event(end)          # the caller's stream sees the step as one unit
-        end.synchronize()
+        self._end = end
+        if wait:
+            compute.wait_event(end)      # the caller's stream sees the step as one unit
+            end.synchronize()
         return host_out
 
 
 _default: dict = {}
 
 
-def chunk_kda_fwd_bwd_host(host_in: dict, host_out: dict | None = None, slices: int | None = None,
-                           head_groups: int | None = None, **kwargs) -> dict:
-    """Module-level convenience over a per-device `HostPipeline`."""
+def _pipe() -> HostPipeline:
     dev = torch.cuda.current_device()
     pipe = _default.get(dev)
     if pipe is None:
         pipe = _default[dev] = HostPipeline(torch.device("cuda", dev))
-    return pipe.fwd_bwd(host_in, host_out, slices, head_groups, **kwargs)
+    return pipe
+
+
+def chunk_kda_fwd_bwd_host(host_in: dict, host_out: dict | None = None, slices: int | None = None,
+                           head_groups: int | None = None, wait: bool = True, **kwargs) -> dict:
+    """Module-level convenience over a per-device `HostPipeline` (see `HostPipeline.fwd_bwd`)."""
+    return _pipe().fwd_bwd(host_in, host_out, slices, head_groups, wait, **kwargs)
+
+
+def host_synchronize() -> None:
+    """Waits for every step queued with `wait=False` on the current device."""
+    _pipe().synchronize()

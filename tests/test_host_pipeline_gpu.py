@@ -26,6 +26,31 @@ def test_host_pipeline_matches_whole_batch():
         assert torch.equal(out3[n], r.detach().cpu()), (n, "head groups")
 
 
+def test_host_pipeline_overlapped_steps():
+    """wait=False: three steps queued back to back on two different inputs with alternating output buffers; after
+    host_synchronize() every step's results equal those of the blocking call, bit for bit."""
+    from kda_b200.host import chunk_kda_fwd_bwd_host, host_synchronize
+    ins = []
+    for seed in (60, 61):
+        d = make_inputs(4, 130, 2, 128, 128, torch.bfloat16, seed=seed, h0_std=0.02, backward=True)
+        ins.append({n: t.pin_memory() for n, t in d.items() if t is not None})
+    ref = [{n: t.clone() for n, t in chunk_kda_fwd_bwd_host(x).items()} for x in ins]
+    outs = [None, None]
+    outs[0] = chunk_kda_fwd_bwd_host(ins[0], None, wait=False)
+    outs[1] = chunk_kda_fwd_bwd_host(ins[1], None, wait=False)
+    host_synchronize()
+    for i in range(2):
+        for n, r in ref[i].items():
+            assert torch.equal(outs[i][n], r), (i, n)
+    # a third step into the first buffer set while nothing else is pending, then a blocking step right behind an async one
+    chunk_kda_fwd_bwd_host(ins[1], outs[0], wait=False)
+    last = chunk_kda_fwd_bwd_host(ins[0], outs[1])
+    host_synchronize()
+    for n in ref[0]:
+        assert torch.equal(outs[0][n], ref[1][n]), n
+        assert torch.equal(last[n], ref[0][n]), n
+
+
 def test_first_backward_on_a_worker_thread_in_a_fresh_process():
     """The backward builds TMA tensor maps with a driver call that needs a context bound to the calling thread; the very
     first backward of a process may run on an autograd worker thread that has none yet."""
