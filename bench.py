@@ -382,7 +382,7 @@ def main():
         e2e_step()              # both output sets exist (pinned allocations stay outside the timed region)
         e2e_drain()
         barrier()
-        n_e2e = max(1, min(args.steps, 5))
+        n_e2e = max(1, min(args.steps, 10))
         e0.record()
         for _ in range(n_e2e):
             e2e_step()
