@@ -40,8 +40,29 @@ __device__ __forceinline__ void st4o(float* p, float4 x) { *reinterpret_cast<flo
 __device__ __forceinline__ void st4o(__nv_bfloat16* p, float4 x) {
   *reinterpret_cast<uint2*>(p) = make_uint2(pack_bf16(x.x, x.y), pack_bf16(x.z, x.w));
 }
+__device__ __forceinline__ void st1o(float* p, float x) { *p = x; }
+__device__ __forceinline__ void st1o(__nv_bfloat16* p, float x) { *p = __float2bfloat16_rn(x); }
 
-template <typename IO>
+// Sum over the 32 lanes of 16 per-lane values at once: afterwards lane L holds the total of v[L & 15] (31 shuffles).
+__device__ __forceinline__ float butterfly_sum16(float (&v)[16], int lane) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] += __shfl_xor_sync(0xffffffffu, v[i], 16);
+#pragma unroll
+  for (int o = 8; o >= 1; o >>= 1) {
+    const bool up = (lane & o) != 0;
+#pragma unroll
+    for (int i = 0; i < o; ++i) {
+      const float mine = up ? v[i + o] : v[i];
+      const float other = up ? v[i] : v[i + o];
+      v[i] = mine + __shfl_xor_sync(0xffffffffu, other, o);
+    }
+  }
+  return v[0];
+}
+
+// TR: the states are [slots, H, V, K] (fla's transpose_state_layout): a warp owns 16 value rows of the tile and a lane
+// four key columns, so both sums over K stay inside the warp (two butterflies) and no block-wide reduction is needed.
+template <typename IO, bool TR>
 __global__ void __launch_bounds__(DEC_THREADS, 1) kda_decode_bulk_kernel(const kda_recurrent_args a) {
   extern __shared__ unsigned char smem_raw[];
   DecSmem& s = *reinterpret_cast<DecSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
@@ -132,6 +153,32 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) kda_decode_bulk_kernel(const k
     }
     float* const tile = s.S[st];
     float4 Sr[16];
+    float o_tr = 0.f;
+    if constexpr (TR) {
+      // tile[v][k]: rows 16 warp .. of the value axis, key columns 4 lane ..
+      const float4 e4 = *reinterpret_cast<const float4*>(&s.eg[buf][4 * lane]);
+      float4 k4 = *reinterpret_cast<const float4*>(&s.kv[buf][4 * lane]);
+      float4 q4 = *reinterpret_cast<const float4*>(&s.qv[buf][4 * lane]);
+      k4.x *= rk; k4.y *= rk; k4.z *= rk; k4.w *= rk;
+      q4.x *= rq; q4.y *= rq; q4.z *= rq; q4.w *= rq;
+      float part[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        Sr[i] = *reinterpret_cast<const float4*>(&tile[(16 * warp + i) * DK + 4 * lane]);
+        Sr[i].x *= e4.x; Sr[i].y *= e4.y; Sr[i].z *= e4.z; Sr[i].w *= e4.w;
+        part[i] = fmaf(k4.x, Sr[i].x, fmaf(k4.y, Sr[i].y, fmaf(k4.z, Sr[i].z, k4.w * Sr[i].w)));
+      }
+      const float hk = butterfly_sum16(part, lane);                     // value row 16 warp + (lane & 15)
+      const float dvl = s.beta[buf] * (s.vv[buf][16 * warp + (lane & 15)] - hk);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float dvi = __shfl_sync(0xffffffffu, dvl, i);
+        Sr[i].x = fmaf(k4.x, dvi, Sr[i].x); Sr[i].y = fmaf(k4.y, dvi, Sr[i].y); Sr[i].z = fmaf(k4.z, dvi, Sr[i].z); Sr[i].w = fmaf(k4.w, dvi, Sr[i].w);
+        part[i] = fmaf(q4.x, Sr[i].x, fmaf(q4.y, Sr[i].y, fmaf(q4.z, Sr[i].z, q4.w * Sr[i].w)));
+        *reinterpret_cast<float4*>(&tile[(16 * warp + i) * DK + 4 * lane]) = Sr[i];
+      }
+      o_tr = butterfly_sum16(part, lane);
+    } else {
     float4 hk = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
@@ -162,6 +209,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) kda_decode_bulk_kernel(const k
       *reinterpret_cast<float4*>(&tile[r * DV + 4 * lane]) = Sr[i];
     }
     *reinterpret_cast<float4*>(&s.red2[warp][4 * lane]) = oa;
+    }
     if (has_next) stash_vec(buf ^ 1, x0, x1, xb);
     fence_proxy_async();          // the updated tile becomes visible to the bulk-copy engine
     alive = __syncthreads_and(alive);
@@ -185,7 +233,9 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) kda_decode_bulk_kernel(const k
         bulk_g2s(s.S[s2], a.h0 + slot_of(u2), DEC_TILE, &s.full[s2]);
       }
     }
-    if (warp == 0) {
+    if constexpr (TR) {
+      if (lane < 16) st1o(op + static_cast<size_t>(u) * DV + 16 * warp + lane, o_tr);
+    } else if (warp == 0) {
       float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
       for (int w = 0; w < 8; ++w) {
@@ -200,13 +250,13 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) kda_decode_bulk_kernel(const k
   __syncthreads();
 }
 
-template <typename IO>
+template <typename IO, bool TR>
 int launch(const kda_recurrent_args& a, cudaStream_t st) {
   const int smem = static_cast<int>(sizeof(DecSmem)) + 128;
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [&] {
-    attr_err = cudaFuncSetAttribute(kda_decode_bulk_kernel<IO>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    attr_err = cudaFuncSetAttribute(kda_decode_bulk_kernel<IO, TR>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   });
   if (attr_err != cudaSuccess) return static_cast<int>(attr_err);
   int dev = 0, sms = 0;
@@ -215,17 +265,17 @@ int launch(const kda_recurrent_args& a, cudaStream_t st) {
   if (e != cudaSuccess) return static_cast<int>(e);
   const long long total = static_cast<long long>(a.N) * a.H;
   const unsigned grid = static_cast<unsigned>(total < sms ? total : sms);
-  kda_decode_bulk_kernel<IO><<<grid, DEC_THREADS, smem, st>>>(a);
+  kda_decode_bulk_kernel<IO, TR><<<grid, DEC_THREADS, smem, st>>>(a);
   return static_cast<int>(cudaGetLastError());
 }
 
 }  // namespace
 
 // Whether the bulk-copy decode kernel covers this call: one token per sequence, K = V = 128, states carried from h0 to
-// ht in the plain layout, and enough (sequence, head) units to keep every SM's ring busy (with few units per SM the
+// ht (either layout), and enough (sequence, head) units to keep every SM's ring busy (with few units per SM the
 // per-warp kernel spreads the work more finely).
 bool decode_bulk_covers(const kda_recurrent_args& a) {
-  if (a.K != DK || a.V != DV || a.transpose_state || !a.h0 || !a.ht || a.cu_seqlens || a.T != 1 || a.num_accepted_tokens) return false;
+  if (a.K != DK || a.V != DV || !a.h0 || !a.ht || a.cu_seqlens || a.T != 1 || a.num_accepted_tokens) return false;
   if (a.io_dtype != KDA_BF16 && a.io_dtype != KDA_FP32) return false;
   int dev = 0, sms = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return false;
@@ -233,7 +283,8 @@ bool decode_bulk_covers(const kda_recurrent_args& a) {
 }
 
 int decode_bulk_launch(const kda_recurrent_args& a, cudaStream_t st) {
-  return a.io_dtype == KDA_BF16 ? launch<__nv_bfloat16>(a, st) : launch<float>(a, st);
+  if (a.transpose_state) return a.io_dtype == KDA_BF16 ? launch<__nv_bfloat16, true>(a, st) : launch<float, true>(a, st);
+  return a.io_dtype == KDA_BF16 ? launch<__nv_bfloat16, false>(a, st) : launch<float, false>(a, st);
 }
 
 }  // namespace kda

@@ -79,7 +79,7 @@ def test_decode_inplace_steps_match_scan():
     assert torch.count_nonzero(pool[1]) == 0 and torch.count_nonzero(pool[3]) == 0
 
 
-@pytest.mark.parametrize("case", ["plain", "l2norm_slots_gva", "fp32"])
+@pytest.mark.parametrize("case", ["plain", "l2norm_slots_gva", "fp32", "transposed", "transposed_l2norm_slots_gva"])
 def test_large_decode_batch_bulk_copy_kernel(case):
     """640 (sequence, head) units with one token each: the step runs on the kernel that moves whole state tiles with the
     bulk-copy engine (at least four units per SM).  o and the new states against the float64 oracle: bf16 o 2e-2,
@@ -88,7 +88,8 @@ def test_large_decode_batch_bulk_copy_kernel(case):
     N, H = 40, 16
     dtype = torch.float32 if case == "fp32" else torch.bfloat16
     d = make_inputs(N, 1, H, 128, 128, dtype, seed=21, h0_std=0.05)
-    l2 = case == "l2norm_slots_gva"
+    l2 = case.endswith("l2norm_slots_gva")
+    tr = case.startswith("transposed")          # states [.., V, K]
     HQ = 4 if l2 else H
     q, k = d["q"][:, :, :HQ].contiguous(), d["k"][:, :, :HQ].contiguous()
     if l2:
@@ -97,12 +98,15 @@ def test_large_decode_batch_bulk_copy_kernel(case):
     o_ref, h_ref = recurrent_kda(q.repeat_interleave(rep, 2), k.repeat_interleave(rep, 2), d["v"], d["g"], d["beta"],
                                  scale=0.11, initial_state=d["h0"], output_final_state=True, use_qk_l2norm=l2)
     c = _cuda(d)
+    if tr:
+        c["h0"] = c["h0"].transpose(-1, -2).contiguous()
     if l2:
         perm = torch.randperm(N + 8, generator=torch.Generator().manual_seed(1))[:N].to(torch.int32).cuda()
         pool = torch.full((N + 8, H, 128, 128), 7.0, device="cuda")
         pool[perm.long()] = c["h0"]
         o, ret = fused_recurrent_kda_fwd(q.cuda(), k.cuda(), c["v"], c["g"], c["beta"], scale=0.11, initial_state=pool,
-                                         inplace_final_state=True, ssm_state_indices=perm, use_qk_l2norm_in_kernel=True)
+                                         inplace_final_state=True, ssm_state_indices=perm, use_qk_l2norm_in_kernel=True,
+                                         transpose_state_layout=tr)
         assert ret.data_ptr() == pool.data_ptr()
         ht = pool[perm.long()]
         rest = sorted(set(range(N + 8)) - set(perm.tolist()))
@@ -110,8 +114,10 @@ def test_large_decode_batch_bulk_copy_kernel(case):
     else:
         h0_before = c["h0"].clone()
         o, ht = fused_recurrent_kda_fwd(q.cuda(), k.cuda(), c["v"], c["g"], c["beta"], scale=0.11, initial_state=c["h0"],
-                                        inplace_final_state=False, output_final_state=True)
+                                        inplace_final_state=False, output_final_state=True, transpose_state_layout=tr)
         assert torch.equal(c["h0"], h0_before)
+    if tr:
+        ht = ht.transpose(-1, -2)
     assert _lib.recurrent_status() == 0
     assert max_norm_err(o, o_ref) <= (1e-4 if case == "fp32" else 2e-2) and cosine(o, o_ref) >= 0.9999
     assert max_norm_err(ht, h_ref) <= 1e-4
