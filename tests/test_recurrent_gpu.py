@@ -123,6 +123,32 @@ def test_large_decode_batch_bulk_copy_kernel(case):
     assert max_norm_err(ht, h_ref) <= 1e-4
 
 
+@pytest.mark.parametrize("N", [4, 40])
+def test_decode_step_replays_from_a_cuda_graph(N):
+    """Serving loops capture the decode step in a CUDA graph: the C entry point makes no synchronising call and takes the
+    capturing stream, so a captured in-place step (per-warp kernel for N = 4, bulk-copy kernel for N = 40) replays to the
+    same states and outputs as eager calls, bit for bit."""
+    from kda_b200 import fused_recurrent_kda_fwd
+    H = 16
+    c = _cuda(make_inputs(N, 1, H, 128, 128, torch.bfloat16, seed=31, h0_std=0.05))
+    args = (c["q"], c["k"], c["v"], c["g"], c["beta"])
+    eager_state, graph_state, scratch = c["h0"].clone(), c["h0"].clone(), c["h0"].clone()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):           # first call outside the capture (one-time attribute setting)
+        fused_recurrent_kda_fwd(*args, initial_state=scratch, inplace_final_state=True, use_qk_l2norm_in_kernel=True)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        o_graph, _ = fused_recurrent_kda_fwd(*args, initial_state=graph_state, inplace_final_state=True, use_qk_l2norm_in_kernel=True)
+    for step in range(3):
+        graph.replay()
+        o_eager, _ = fused_recurrent_kda_fwd(*args, initial_state=eager_state, inplace_final_state=True, use_qk_l2norm_in_kernel=True)
+        torch.cuda.synchronize()
+        assert torch.equal(o_graph, o_eager), step
+        assert torch.equal(graph_state, eager_state), step
+
+
 def test_speculative_decoding_state_slots():
     """Continuous batching with per-token state slots (fla/ops/kda/fused_recurrent.py:122-144,195-210): a sequence
     starts from the slot of its last accepted token and the state after draft token t lands in slot [n, t]."""
