@@ -160,3 +160,32 @@ def test_chunk_size_32_is_the_same_function():
         chunk_kda(*(d[n].cuda() for n in ("q", "k", "v", "g", "beta")), chunk_size=16)
     with torch.inference_mode(), pytest.raises(NotImplementedError, match="chunk_size=32"):
         chunk_kda(*(d[n].cuda() for n in ("q", "k", "v", "g", "beta")), chunk_size=32, return_intermediate_states=True)
+
+
+def test_prefill_forward_replays_from_a_cuda_graph():
+    """The forward entry point neither synchronises nor allocates: a captured prefill (packed variable-length batch, final
+    states kept) replays to the eager result, bit for bit, also after the inputs have been overwritten in place."""
+    from kda_b200 import chunk_kda
+    cu = torch.tensor([0, 70, 200], dtype=torch.int32).cuda()
+    d = make_inputs(1, 200, 2, 128, 128, torch.bfloat16, seed=90, h0_std=0.02, n_states=2)
+    d2 = make_inputs(1, 200, 2, 128, 128, torch.bfloat16, seed=91, h0_std=0.02, n_states=2)
+    c = {n: t.cuda() for n, t in d.items() if t is not None}
+
+    def run():
+        with torch.no_grad():
+            return chunk_kda(c["q"], c["k"], c["v"], c["g"], c["beta"], initial_state=c["h0"], output_final_state=True, cu_seqlens=cu)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        run()                                   # one-time attribute setting outside the capture
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        o_g, ht_g = run()
+    for src in (d, d2):
+        for n in c:
+            c[n].copy_(src[n])
+        graph.replay()
+        o_e, ht_e = run()
+        torch.cuda.synchronize()
+        assert torch.equal(o_g, o_e) and torch.equal(ht_g, ht_e)
