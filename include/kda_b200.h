@@ -31,7 +31,7 @@ extern "C" {
 #pragma GCC visibility push(default) /* the entry points below are the library's only exports */
 #endif
 
-#define KDA_B200_ABI_VERSION 5
+#define KDA_B200_ABI_VERSION 6
 #define KDA_CHUNK 64 /* tokens per chunk of the chunked kernels */
 
 /* io_dtype of q, k, v, o and of their gradients */
@@ -86,6 +86,17 @@ typedef struct kda_recurrent_args {
                                          K in {64, 128} */
   int32_t HQ;                         /* grouped value heads (GVA): q and k have HQ heads, [tokens, HQ, K], and value head h reads
                                          q/k head h / (H / HQ); 0 or H: no grouping.  H must be a multiple of HQ. */
+  /* Gate front end inside the kernel (USE_GATE_IN_KERNEL / APPLY_BETA_SIGMOID of fla/ops/kda/fused_recurrent.py:31-225),
+   * all zero / NULL: g and beta are the activated fp32 values as described above. */
+  const float* A_log;                 /* [H] or NULL.  Not NULL: `g` points to the RAW gate input [tokens, H, K] of dtype
+                                         g_raw_dtype and the kernel uses g = -exp(A_log[h]) softplus(x + dt_bias[h, k]), or with
+                                         use_lower_bound g = lower_bound sigmoid(exp(A_log[h]) (x + dt_bias[h, k])) */
+  const float* dt_bias;               /* [H * K] or NULL */
+  float lower_bound;
+  int32_t use_lower_bound;
+  int32_t g_raw_dtype;                /* KDA_BF16 or KDA_FP32; read only with A_log */
+  int32_t beta_sigmoid;               /* nonzero: `beta` points to logits [tokens, H] of dtype beta_raw_dtype */
+  int32_t beta_raw_dtype;             /* KDA_BF16 or KDA_FP32; read only with beta_sigmoid */
 } kda_recurrent_args;
 
 int kda_recurrent_fwd(const kda_recurrent_args* args, void* stream);

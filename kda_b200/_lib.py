@@ -11,7 +11,7 @@ LIB_PATH = os.path.join(PKG, "libkda_b200.so")
 
 KDA_BF16, KDA_FP32 = 0, 1
 NOALLOC_SCRATCH_BYTES = 32 << 20
-ABI_VERSION = 5
+ABI_VERSION = 6
 
 
 class RecurrentArgs(C.Structure):
@@ -23,6 +23,8 @@ class RecurrentArgs(C.Structure):
         ("V", C.c_int32), ("io_dtype", C.c_int32), ("use_qk_l2norm", C.c_int32), ("scale", C.c_float),
         ("num_accepted_tokens", C.c_void_p), ("state_indices_stride", C.c_int32), ("transpose_state", C.c_int32),
         ("HQ", C.c_int32),
+        ("A_log", C.c_void_p), ("dt_bias", C.c_void_p), ("lower_bound", C.c_float), ("use_lower_bound", C.c_int32),
+        ("g_raw_dtype", C.c_int32), ("beta_sigmoid", C.c_int32), ("beta_raw_dtype", C.c_int32),
     ]
 
 

@@ -36,6 +36,28 @@ __device__ __forceinline__ float warp_sum(float x) {
   return x;
 }
 
+// ---- gate front end of the recurrent kernels: activated log-decay and beta from the raw layer outputs -------------
+__device__ __forceinline__ float sigmoid_fast(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
+// softplus(x) = log(1 + e^x); identity above 20; below -15 the sum would round e^x away and log(1 + e) = e to fp32 accuracy
+__device__ __forceinline__ float softplus_fast(float x) {
+  const float e = __expf(fminf(x, 20.f));
+  return x > 20.f ? x : (x < -15.f ? e : __logf(1.f + e));
+}
+__device__ __forceinline__ float load_raw(const void* p, size_t i, int dtype) {      // dtype: KDA_BF16 or KDA_FP32
+  return dtype == KDA_BF16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]) : __ldg(static_cast<const float*>(p) + i);
+}
+// log-decay of (token row `row` = token * H + h, key column k) as the kernels use it
+__device__ __forceinline__ float recurrent_log_decay(const kda_recurrent_args& a, size_t row, int h, int k, int K) {
+  if (!a.A_log) return __ldg(a.g + row * K + k);
+  float x = load_raw(a.g, row * K + k, a.g_raw_dtype);
+  if (a.dt_bias) x += __ldg(a.dt_bias + static_cast<size_t>(h) * K + k);
+  const float al = __expf(__ldg(a.A_log + h));
+  return a.use_lower_bound ? a.lower_bound * sigmoid_fast(al * x) : -al * softplus_fast(x);
+}
+__device__ __forceinline__ float recurrent_beta(const kda_recurrent_args& a, size_t row) {
+  return a.beta_sigmoid ? sigmoid_fast(load_raw(a.beta, row, a.beta_raw_dtype)) : __ldg(a.beta + row);
+}
+
 // ---- tensor-core primitives (warp-level, bf16 in / fp32 accumulate) ------------------------------
 // D(16x8) += A(16x16, row) * B(16x8, col).  Fragment ownership (gid = lane/4, tig = lane%4):
 //   a0:(gid, 2tig..+1) a1:(gid+8, 2tig..) a2:(gid, 2tig+8..) a3:(gid+8, 2tig+8..)

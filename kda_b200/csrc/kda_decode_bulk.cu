@@ -90,10 +90,10 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) kda_decode_bulk_kernel(const k
       x0 = ld1(qp + row);
       x1 = ld1(kp + row);
     } else {
-      x0 = __ldg(a.g + (static_cast<size_t>(n) * a.H + h) * DK + (tid - DK));
+      x0 = recurrent_log_decay(a, static_cast<size_t>(n) * a.H + h, h, tid - DK, DK);
       x1 = ld1(vp + (static_cast<size_t>(n) * a.H + h) * DV + (tid - DK));
     }
-    if (tid == 0) b = __ldg(a.beta + static_cast<size_t>(n) * a.H + h);
+    if (tid == 0) b = recurrent_beta(a, static_cast<size_t>(n) * a.H + h);
   };
   auto stash_vec = [&](int buf, float x0, float x1, float b) {
     if (tid < DK) {

@@ -99,14 +99,13 @@ __global__ void __launch_bounds__(REC_WARPS * 32) kda_recurrent_kernel(const kda
   IO* op = static_cast<IO*>(a.o);
 
   for (long long t = bos; t < eos; ++t) {
-    const size_t rowk = (static_cast<size_t>(t) * a.H + h) * K + lane * E;        // g row (value head)
     const size_t rowq = (static_cast<size_t>(t) * HQ + h / grp) * K + lane * E;   // q, k row (their own head count)
     float qf[E], kf[E], gf[E];
 #pragma unroll
     for (int e = 0; e < E; ++e) {
       qf[e] = IoTraits<IO>::ld(qp + rowq + e);
       kf[e] = IoTraits<IO>::ld(kp + rowq + e);
-      gf[e] = __ldg(a.g + rowk + e);
+      gf[e] = recurrent_log_decay(a, static_cast<size_t>(t) * a.H + h, h, lane * E + e, K);
     }
     float qs = a.scale;
     if (a.use_qk_l2norm) {
@@ -129,7 +128,7 @@ __global__ void __launch_bounds__(REC_WARPS * 32) kda_recurrent_kernel(const kda
       s_q[warp][lane * E + e] = qf[e] * qs;
       s_eg[warp][lane * E + e] = expf(gf[e]);
     }
-    const float beta = __ldg(a.beta + static_cast<size_t>(t) * a.H + h);
+    const float beta = recurrent_beta(a, static_cast<size_t>(t) * a.H + h);
     const float4 vt = IoTraits<IO>::ld4(vp + (static_cast<size_t>(t) * a.H + h) * a.V + col);
     __syncwarp();
 
@@ -243,14 +242,13 @@ __global__ void __launch_bounds__(REC_WARPS * 32) kda_recurrent_t_kernel(const k
   const IO* vp = static_cast<const IO*>(a.v);
   IO* op = static_cast<IO*>(a.o);
   for (long long t = bos; t < eos; ++t) {
-    const size_t rowk = (static_cast<size_t>(t) * a.H + h) * K + lane * E;        // g row (value head)
     const size_t rowq = (static_cast<size_t>(t) * HQ + h / grp) * K + lane * E;   // q, k row (their own head count)
     float qf[E], kf[E], eg[E];
 #pragma unroll
     for (int e = 0; e < E; ++e) {
       qf[e] = IoTraits<IO>::ld(qp + rowq + e);
       kf[e] = IoTraits<IO>::ld(kp + rowq + e);
-      eg[e] = expf(__ldg(a.g + rowk + e));
+      eg[e] = expf(recurrent_log_decay(a, static_cast<size_t>(t) * a.H + h, h, lane * E + e, K));
     }
     float qs = a.scale;
     if (a.use_qk_l2norm) {
@@ -269,7 +267,7 @@ __global__ void __launch_bounds__(REC_WARPS * 32) kda_recurrent_t_kernel(const k
     }
 #pragma unroll
     for (int e = 0; e < E; ++e) qf[e] *= qs;
-    const float beta = __ldg(a.beta + static_cast<size_t>(t) * a.H + h);
+    const float beta = recurrent_beta(a, static_cast<size_t>(t) * a.H + h);
     const float vt = IoTraits<IO>::ld(vp + (static_cast<size_t>(t) * a.H + h) * a.V + vs * 32 + lane);      // value row `lane`
     float part[32];
 #pragma unroll

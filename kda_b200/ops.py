@@ -235,14 +235,30 @@ def fused_recurrent_kda_fwd(q, k, v, g, beta, A_log=None, dt_bias=None, initial_
     if scale is None:
         scale = K ** -0.5
     dev = q.device
-    with torch.no_grad():
-        if use_gate_in_kernel:
-            assert A_log is not None, "A_log must be provided when use_gate_in_kernel=True."
-        g, beta = _gate_front_end(g, beta, use_gate_in_kernel, use_beta_sigmoid_in_kernel, False, lower_bound,
-                                  {"A_log": A_log, "dt_bias": dt_bias} if use_gate_in_kernel else {})
+    # the gate activation and the beta sigmoid run inside the recurrent kernels (no separate pass over g and beta)
+    gate_kw = {}
+    if use_gate_in_kernel:
+        assert A_log is not None, "A_log must be provided when use_gate_in_kernel=True."
+        if g.dtype not in _DT:
+            g = g.float()
+        a_log = A_log.detach().to(device=dev, dtype=torch.float32).contiguous()
+        bias = dt_bias.detach().to(device=dev, dtype=torch.float32).contiguous() if dt_bias is not None else None
+        if a_log.numel() != H or (bias is not None and bias.numel() != H * K):
+            raise ValueError(f"A_log must have {H} elements and dt_bias {H * K}")
+        gate_kw.update(A_log=_ptr(a_log), dt_bias=_ptr(bias), g_raw_dtype=_DT[g.dtype],
+                       lower_bound=float(lower_bound) if lower_bound is not None else 0.0,
+                       use_lower_bound=int(lower_bound is not None))
+        g = g.detach().contiguous()
+    else:
+        g = g.contiguous().float()
+    if use_beta_sigmoid_in_kernel:
+        if beta.dtype not in _DT:
+            beta = beta.float()
+        gate_kw.update(beta_sigmoid=1, beta_raw_dtype=_DT[beta.dtype])
+        beta = beta.detach().contiguous()
+    else:
+        beta = beta.contiguous().float()
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
-    g = g.contiguous().float()
-    beta = beta.contiguous().float()
     N = B if cu_seqlens is None else len(cu_seqlens) - 1
     cu = _as_i32(cu_seqlens, dev) if cu_seqlens is not None else None
     h0 = initial_state.contiguous() if initial_state is not None else None
@@ -279,7 +295,7 @@ def fused_recurrent_kda_fwd(q, k, v, g, beta, A_log=None, dt_bias=None, initial_
         cu_seqlens=_ptr(cu), state_indices=_ptr(idx), tokens=B * T, N=N, T=T, H=H, K=K, V=V,
         io_dtype=_DT[q.dtype], use_qk_l2norm=int(bool(use_qk_l2norm_in_kernel)), scale=float(scale),
         num_accepted_tokens=_ptr(acc), state_indices_stride=stride, transpose_state=int(bool(transpose_state_layout)),
-        HQ=q.shape[2])
+        HQ=q.shape[2], **gate_kw)
     with torch.cuda.device(dev):
         _lib.check(_lib.load().kda_recurrent_fwd(C.byref(args), _stream(dev)), "kda_recurrent_fwd")
     return o, ht

@@ -149,6 +149,33 @@ def test_decode_step_replays_from_a_cuda_graph(N):
         assert torch.equal(graph_state, eager_state), step
 
 
+@pytest.mark.parametrize("N,tr,lb", [(3, False, None), (3, True, -5.0), (40, False, -5.0), (40, True, None)])
+def test_decode_with_the_gate_front_end_in_kernel(N, tr, lb):
+    """The layer's decode call (fla/layers/kda.py:282-296): raw bf16 gate input with A_log, dt_bias (optionally the
+    lower-bound form), beta logits, l2norm -- all inside the recurrent kernel, no pass over g and beta in front of it.
+    Per-warp kernels (N = 3) and bulk-copy kernel (N = 40), both state layouts; o 2e-2, states 1e-4 against the oracle."""
+    from kda_b200 import fused_recurrent_kda
+    from oracle.kda_oracle import beta_sigmoid, kda_gate
+    H = 16
+    d = make_inputs(N, 1, H, 128, 128, torch.bfloat16, seed=33, h0_std=0.05)
+    gen = torch.Generator().manual_seed(34)
+    g_raw = torch.randn(N, 1, H, 128, generator=gen).bfloat16()
+    beta_raw = torch.randn(N, 1, H, generator=gen).bfloat16()
+    A_log = torch.log(torch.empty(H).uniform_(1, 16, generator=gen))
+    dt_bias = torch.randn(H * 128, generator=gen) * 0.5
+    o_ref, h_ref = recurrent_kda(d["q"], d["k"], d["v"], kda_gate(g_raw, A_log, dt_bias, lower_bound=lb), beta_sigmoid(beta_raw),
+                                 initial_state=d["h0"], output_final_state=True, use_qk_l2norm=True)
+    h0 = d["h0"].cuda()
+    o, ht = fused_recurrent_kda(d["q"].cuda(), d["k"].cuda(), d["v"].cuda(), g_raw.cuda(), beta_raw.cuda(), A_log=A_log.cuda(),
+                                dt_bias=dt_bias.cuda(), initial_state=h0.transpose(-1, -2).contiguous() if tr else h0,
+                                output_final_state=True, use_qk_l2norm_in_kernel=True, use_gate_in_kernel=True,
+                                use_beta_sigmoid_in_kernel=True, lower_bound=lb, transpose_state_layout=tr)
+    if tr:
+        ht = ht.transpose(-1, -2)
+    assert max_norm_err(o, o_ref) <= 2e-2 and cosine(o, o_ref) >= 0.9999
+    assert max_norm_err(ht, h_ref) <= 1e-4
+
+
 def test_speculative_decoding_state_slots():
     """Continuous batching with per-token state slots (fla/ops/kda/fused_recurrent.py:122-144,195-210): a sequence
     starts from the slot of its last accepted token and the state after draft token t lands in slot [n, t]."""
