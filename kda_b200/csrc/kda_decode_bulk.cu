@@ -62,7 +62,8 @@ __device__ __forceinline__ float butterfly_sum16(float (&v)[16], int lane) {
 
 // TR: the states are [slots, H, V, K] (fla's transpose_state_layout): a warp owns 16 value rows of the tile and a lane
 // four key columns, so both sums over K stay inside the warp (two butterflies) and no block-wide reduction is needed.
-template <typename IO, bool TR>
+// GATE: g and / or beta are the raw layer outputs and are activated here (see kda_recurrent_args::A_log, beta_sigmoid).
+template <typename IO, bool TR, bool GATE>
 __global__ void __launch_bounds__(DEC_THREADS, 1) kda_decode_bulk_kernel(const kda_recurrent_args a) {
   extern __shared__ unsigned char smem_raw[];
   DecSmem& s = *reinterpret_cast<DecSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
@@ -90,10 +91,14 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) kda_decode_bulk_kernel(const k
       x0 = ld1(qp + row);
       x1 = ld1(kp + row);
     } else {
-      x0 = recurrent_log_decay(a, static_cast<size_t>(n) * a.H + h, h, tid - DK, DK);
+      if constexpr (GATE) x0 = recurrent_log_decay(a, static_cast<size_t>(n) * a.H + h, h, tid - DK, DK);
+      else x0 = __ldg(a.g + (static_cast<size_t>(n) * a.H + h) * DK + (tid - DK));
       x1 = ld1(vp + (static_cast<size_t>(n) * a.H + h) * DV + (tid - DK));
     }
-    if (tid == 0) b = recurrent_beta(a, static_cast<size_t>(n) * a.H + h);
+    if (tid == 0) {
+      if constexpr (GATE) b = recurrent_beta(a, static_cast<size_t>(n) * a.H + h);
+      else b = __ldg(a.beta + static_cast<size_t>(n) * a.H + h);
+    }
   };
   auto stash_vec = [&](int buf, float x0, float x1, float b) {
     if (tid < DK) {
@@ -250,13 +255,13 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) kda_decode_bulk_kernel(const k
   __syncthreads();
 }
 
-template <typename IO, bool TR>
+template <typename IO, bool TR, bool GATE>
 int launch(const kda_recurrent_args& a, cudaStream_t st) {
   const int smem = static_cast<int>(sizeof(DecSmem)) + 128;
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [&] {
-    attr_err = cudaFuncSetAttribute(kda_decode_bulk_kernel<IO, TR>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    attr_err = cudaFuncSetAttribute(kda_decode_bulk_kernel<IO, TR, GATE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   });
   if (attr_err != cudaSuccess) return static_cast<int>(attr_err);
   int dev = 0, sms = 0;
@@ -265,7 +270,7 @@ int launch(const kda_recurrent_args& a, cudaStream_t st) {
   if (e != cudaSuccess) return static_cast<int>(e);
   const long long total = static_cast<long long>(a.N) * a.H;
   const unsigned grid = static_cast<unsigned>(total < sms ? total : sms);
-  kda_decode_bulk_kernel<IO, TR><<<grid, DEC_THREADS, smem, st>>>(a);
+  kda_decode_bulk_kernel<IO, TR, GATE><<<grid, DEC_THREADS, smem, st>>>(a);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -283,8 +288,18 @@ bool decode_bulk_covers(const kda_recurrent_args& a) {
 }
 
 int decode_bulk_launch(const kda_recurrent_args& a, cudaStream_t st) {
-  if (a.transpose_state) return a.io_dtype == KDA_BF16 ? launch<__nv_bfloat16, true>(a, st) : launch<float, true>(a, st);
-  return a.io_dtype == KDA_BF16 ? launch<__nv_bfloat16, false>(a, st) : launch<float, false>(a, st);
+  const bool gate = a.A_log != nullptr || a.beta_sigmoid != 0;
+  const int which = (a.io_dtype == KDA_BF16 ? 0 : 4) + (a.transpose_state ? 2 : 0) + (gate ? 1 : 0);
+  switch (which) {
+    case 0: return launch<__nv_bfloat16, false, false>(a, st);
+    case 1: return launch<__nv_bfloat16, false, true>(a, st);
+    case 2: return launch<__nv_bfloat16, true, false>(a, st);
+    case 3: return launch<__nv_bfloat16, true, true>(a, st);
+    case 4: return launch<float, false, false>(a, st);
+    case 5: return launch<float, false, true>(a, st);
+    case 6: return launch<float, true, false>(a, st);
+    default: return launch<float, true, true>(a, st);
+  }
 }
 
 }  // namespace kda
