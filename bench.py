@@ -226,7 +226,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--gate", action="store_true",
                     help="call the operator as the layer does: raw bf16 gate input + A_log + dt_bias and beta logits "
-                         "(use_gate_in_kernel, use_beta_sigmoid_in_kernel); training workloads only")
+                         "(use_gate_in_kernel, use_beta_sigmoid_in_kernel); training workloads and decode")
     ap.add_argument("--l2norm", action="store_true", help="use_qk_l2norm_in_kernel=True (chunked workloads)")
     ap.add_argument("--gpu-bar", action="store_true",
                     help="also time fla.ops.kda.chunk_kda (the Triton kernels of flash-linear-attention, if it imports on "
@@ -254,8 +254,8 @@ def main():
     host = make_workload(args.workload, seed=rank, scale_down=args.scale_down)
     cu_host = host.pop("cu_seqlens")
     if args.gate:
-        if not w.backward:
-            raise SystemExit("--gate needs a forward+backward workload")
+        if not w.backward and args.workload != "decode":
+            raise SystemExit("--gate needs a forward+backward workload or the decode workload")
         gen = torch.Generator().manual_seed(1000 + rank)
         host["g"] = torch.randn(host["g"].shape, generator=gen).bfloat16()                      # raw gate input
         host["beta"] = torch.randn(host["beta"].shape, generator=gen).bfloat16()                # beta logits
@@ -287,9 +287,13 @@ def main():
         state = devt["h0"].clone()
         scale = 128 ** -0.5
 
+        dec_kw = dict(use_qk_l2norm_in_kernel=args.l2norm)
+        if args.gate:       # the layer's decode call: raw gate input, beta logits; activated inside the one kernel
+            dec_kw.update(use_gate_in_kernel=True, use_beta_sigmoid_in_kernel=True, A_log=devt["A_log"], dt_bias=devt["dt_bias"])
+
         def step(x=devt):
             return fused_recurrent_kda_fwd(x["q"], x["k"], x["v"], x["g"], x["beta"], scale=scale, initial_state=state,
-                                           inplace_final_state=True)
+                                           inplace_final_state=True, **dec_kw)
         launches_per_step = 1
         grad_names = []
     elif w.backward:

@@ -82,26 +82,49 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) kda_decode_bulk_kernel(const k
     const long long slot = a.state_indices ? a.state_indices[static_cast<size_t>(n) * a.state_indices_stride] : n;
     return (static_cast<size_t>(slot) * a.H + h) * (DK * DV);
   };
-  // a thread fetches two elements of the unit's vectors: q, k (threads 0..127) or g, v (threads 128..255)
-  auto load_vec = [&](long long u, float& x0, float& x1, float& b) {
+  // A thread fetches two elements of the unit's vectors: q, k (threads 0..127) or g, v (threads 128..255).  The loaded
+  // bits stay untouched in registers until stash_vec: an instruction that depends on a load makes the thread wait for it
+  // right there, and a small load takes longer than a unit's update when the memory system is saturated.
+  struct Raw { uint32_t x0, x1, b, al, bias; };
+  auto ld_bits = [&](const void* p, size_t i, bool bf16) -> uint32_t {
+    if (bf16) return static_cast<const unsigned short*>(p)[i];
+    return __float_as_uint(__ldg(static_cast<const float*>(p) + i));
+  };
+  auto to_float = [&](uint32_t bits, bool bf16) -> float { return __uint_as_float(bf16 ? bits << 16 : bits); };
+  constexpr bool IO16 = sizeof(IO) == 2;
+  auto load_vec = [&](long long u, Raw& r) {
     const long long n = u / a.H;
     const int h = static_cast<int>(u % a.H);
+    const size_t rowv = static_cast<size_t>(n) * a.H + h;
     if (tid < DK) {
       const size_t row = (static_cast<size_t>(n) * HQ + h / grp) * DK + tid;
-      x0 = ld1(qp + row);
-      x1 = ld1(kp + row);
+      r.x0 = ld_bits(qp, row, IO16);
+      r.x1 = ld_bits(kp, row, IO16);
     } else {
-      if constexpr (GATE) x0 = recurrent_log_decay(a, static_cast<size_t>(n) * a.H + h, h, tid - DK, DK);
-      else x0 = __ldg(a.g + (static_cast<size_t>(n) * a.H + h) * DK + (tid - DK));
-      x1 = ld1(vp + (static_cast<size_t>(n) * a.H + h) * DV + (tid - DK));
+      const int kk = tid - DK;
+      if constexpr (GATE) {
+        if (a.A_log) {
+          r.x0 = ld_bits(a.g, rowv * DK + kk, a.g_raw_dtype == KDA_BF16);
+          r.al = __float_as_uint(__ldg(a.A_log + h));
+          r.bias = a.dt_bias ? __float_as_uint(__ldg(a.dt_bias + static_cast<size_t>(h) * DK + kk)) : 0u;
+        } else {
+          r.x0 = __float_as_uint(__ldg(a.g + rowv * DK + kk));
+        }
+      } else {
+        r.x0 = __float_as_uint(__ldg(a.g + rowv * DK + kk));
+      }
+      r.x1 = ld_bits(vp, rowv * DV + kk, IO16);
     }
     if (tid == 0) {
-      if constexpr (GATE) b = recurrent_beta(a, static_cast<size_t>(n) * a.H + h);
-      else b = __ldg(a.beta + static_cast<size_t>(n) * a.H + h);
+      if constexpr (GATE) r.b = a.beta_sigmoid ? ld_bits(a.beta, rowv, a.beta_raw_dtype == KDA_BF16) : __float_as_uint(__ldg(a.beta + rowv));
+      else r.b = __float_as_uint(__ldg(a.beta + rowv));
     }
   };
-  auto stash_vec = [&](int buf, float x0, float x1, float b) {
+  auto stash_vec = [&](int buf, const Raw& r) {
+    const float x1 = to_float(r.x1, IO16);
+    float b = __uint_as_float(r.b);
     if (tid < DK) {
+      const float x0 = to_float(r.x0, IO16);
       s.qv[buf][tid] = x0;
       s.kv[buf][tid] = x1;
       if (a.use_qk_l2norm) {
@@ -112,8 +135,19 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) kda_decode_bulk_kernel(const k
         }
       }
     } else {
-      s.eg[buf][tid - DK] = __expf(x0);
+      float g = __uint_as_float(r.x0);
+      if constexpr (GATE) {
+        if (a.A_log) {
+          const float x = to_float(r.x0, a.g_raw_dtype == KDA_BF16) + __uint_as_float(r.bias);
+          const float al = __expf(__uint_as_float(r.al));
+          g = a.use_lower_bound ? a.lower_bound * sigmoid_fast(al * x) : -al * softplus_fast(x);
+        }
+      }
+      s.eg[buf][tid - DK] = __expf(g);
       s.vv[buf][tid - DK] = x1;
+    }
+    if constexpr (GATE) {
+      if (a.beta_sigmoid) b = sigmoid_fast(to_float(r.b, a.beta_raw_dtype == KDA_BF16));
     }
     if (tid == 0) s.beta[buf] = b;
   };
@@ -134,10 +168,14 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) kda_decode_bulk_kernel(const k
       }
     }
   }
+  // The vectors travel two units ahead of their use, in registers: under a saturated memory system a small load takes
+  // longer than one unit's update, and a thread that waits for it holds up the whole ring.
+  Raw rx = {0u, 0u, 0u, 0u, 0u};                    // unit it + 1
   {
-    float x0, x1, b = 0.f;
-    load_vec(u0, x0, x1, b);
-    stash_vec(0, x0, x1, b);
+    Raw rf = {0u, 0u, 0u, 0u, 0u};
+    load_vec(u0, rf);
+    if (u0 + step < total) load_vec(u0 + step, rx);
+    stash_vec(0, rf);
   }
   __syncthreads();
 
@@ -145,10 +183,9 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) kda_decode_bulk_kernel(const k
   int it = 0;
   for (long long u = u0; u < total; u += step, ++it) {
     const int st = it % DEC_STAGES, buf = it & 1;
-    const long long un = u + step;
-    const bool has_next = un < total;
-    float x0 = 0.f, x1 = 0.f, xb = 0.f;
-    if (has_next) load_vec(un, x0, x1, xb);        // in flight behind the tile's update
+    const bool has_next = u + step < total;
+    Raw ry = {0u, 0u, 0u, 0u, 0u};                  // unit it + 2
+    if (u + 2 * step < total) load_vec(u + 2 * step, ry);
 
     if (!mbar_wait(&s.full[st], static_cast<unsigned>(it / DEC_STAGES) & 1u)) alive = false;
     float rq = a.scale, rk = 1.f;
@@ -215,7 +252,8 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) kda_decode_bulk_kernel(const k
     }
     *reinterpret_cast<float4*>(&s.red2[warp][4 * lane]) = oa;
     }
-    if (has_next) stash_vec(buf ^ 1, x0, x1, xb);
+    if (has_next) stash_vec(buf ^ 1, rx);
+    rx = ry;
     fence_proxy_async();          // the updated tile becomes visible to the bulk-copy engine
     alive = __syncthreads_and(alive);
     if (!alive) {
