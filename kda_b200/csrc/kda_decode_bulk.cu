@@ -16,6 +16,9 @@ namespace {
 
 constexpr int DK = 128, DV = 128;
 constexpr int DEC_STAGES = 3;
+#ifndef KDA_DECODE_BULK_MIN_UNITS_PER_SM
+#define KDA_DECODE_BULK_MIN_UNITS_PER_SM 4      // fewer (sequence, head) units per SM: the per-warp kernel is used
+#endif
 constexpr int DEC_THREADS = 256;                 // 8 warps: warp w owns the 16 state rows 16 w .., a lane 4 value columns
 constexpr unsigned DEC_TILE = DK * DV * 4;       // bytes of one state tile
 
@@ -322,7 +325,7 @@ bool decode_bulk_covers(const kda_recurrent_args& a) {
   if (a.io_dtype != KDA_BF16 && a.io_dtype != KDA_FP32) return false;
   int dev = 0, sms = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return false;
-  return static_cast<long long>(a.N) * a.H >= 4LL * sms;
+  return static_cast<long long>(a.N) * a.H >= static_cast<long long>(KDA_DECODE_BULK_MIN_UNITS_PER_SM) * sms;
 }
 
 int decode_bulk_launch(const kda_recurrent_args& a, cudaStream_t st) {
