@@ -56,6 +56,7 @@ __global__ void __launch_bounds__(RNT, 1) kda_chunk_bwd_scan_tc_kernel(const __g
   const int seq = blockIdx.x / p.H, h = blockIdx.x % p.H;
   const int c_begin = p.seq_chunk_off[seq], c_end = p.seq_chunk_off[seq + 1];
   const int nchunks = c_end - c_begin;
+  const long long seq_tok0 = p.cu[seq];
   const int v = 32 * q4 + lane;
 
   if (tid == 0) {
@@ -75,15 +76,15 @@ __global__ void __launch_bounds__(RNT, 1) kda_chunk_bwd_scan_tc_kernel(const __g
     TcRScanStage& d = s.st[i & 1];
     const int c = c_end - 1 - i;
     const size_t tile = static_cast<size_t>(c) * p.H + h;
-    const ChunkInfo cn = chunk_info(p.seq_chunk_off, p.chunk_seq, p.cu, c);
+    const long long tok0 = seq_tok0 + static_cast<long long>(c - c_begin) * C;      // the CTA's one sequence: no table look-up
     mbar_expect_tx(&s.full[i & 1], TC_RSTAGE_TX);
     bulk_g2s(d.W, p.W + tile * TILE_TK, TILE_TK, &s.full[i & 1]);
     bulk_g2s(d.QG, p.QG + tile * TILE_TK, TILE_TK, &s.full[i & 1]);
     bulk_g2s(d.KG, p.KG + tile * TILE_TK, TILE_TK, &s.full[i & 1]);
     bulk_g2s(d.AQK, p.AQK + tile * TILE_TT, TILE_TT, &s.full[i & 1]);
     bulk_g2s(d.GL, p.GL + tile * TILE_GL, TILE_GL, &s.full[i & 1]);
-    tma_load_rows(d.dO, &p.tm_do, 0, h, static_cast<int>(cn.tok0), &s.full[i & 1]);
-    tma_load_rows(d.dO + 8192, &p.tm_do, 64, h, static_cast<int>(cn.tok0), &s.full[i & 1]);
+    tma_load_rows(d.dO, &p.tm_do, 0, h, static_cast<int>(tok0), &s.full[i & 1]);
+    tma_load_rows(d.dO + 8192, &p.tm_do, 64, h, static_cast<int>(tok0), &s.full[i & 1]);
   };
   if (tid == 0) {
     if (nchunks > 0) issue_load(0);

@@ -59,6 +59,7 @@ __global__ void __launch_bounds__(SNT, 1) kda_chunk_scan_tc_kernel(const ScanPar
   const int seq = blockIdx.x / p.H, h = blockIdx.x % p.H;
   const int c_begin = p.seq_chunk_off[seq], c_end = p.seq_chunk_off[seq + 1];
   const int nchunks = c_end - c_begin;
+  const long long seq_tok0 = p.cu[seq], seq_tok1 = p.cu[seq + 1];
   const int v = 32 * q4 + lane;                       // this thread's value column = TMEM lane
 
   if (tid == 0) {
@@ -114,7 +115,11 @@ __global__ void __launch_bounds__(SNT, 1) kda_chunk_scan_tc_kernel(const ScanPar
   for (int i = 0; i < nchunks && alive; ++i) {
     TcScanStage& d = s.st[i & 1];
     const int c = c_begin + i;
-    const ChunkInfo ci = chunk_info(p.seq_chunk_off, p.chunk_seq, p.cu, c);
+    // every chunk of this CTA belongs to its one sequence: first token and length by arithmetic (a table look-up would
+    // be three dependent loads on the chunk-to-chunk chain)
+    struct { long long tok0; int len; } ci;
+    ci.tok0 = seq_tok0 + static_cast<long long>(i) * C;
+    ci.len = static_cast<int>(seq_tok1 - ci.tok0 < C ? seq_tok1 - ci.tok0 : C);
     const size_t tile = static_cast<size_t>(c) * p.H + h;
     const uint32_t to = C_O + 64 * (i & 1);
 
