@@ -20,7 +20,9 @@ namespace kda {
 
 namespace {
 
-constexpr int SNT = 256;     // 8 warps: TMEM lane quadrant = warp & 3, column half = warp >> 2
+constexpr int SCT = 256;     // 8 compute warps: TMEM lane quadrant = warp & 3, column half = warp >> 2
+constexpr int SNT = SCT + 32;  // + one warp whose first lane issues every MMA, bulk copy and bulk store: the time it spends issuing
+                             // (about 75 cycles per product, 760 cycles for a stage refill) stays off the compute warps' path
 
 struct TcScanStage {
   unsigned char W[TILE_TK], QG[TILE_TK], KG[TILE_TK], AQK[TILE_TT], UT[TILE_VT];
@@ -75,7 +77,7 @@ __global__ void __launch_bounds__(SNT, 1) kda_chunk_scan_tc_kernel(const ScanPar
   const uint32_t tb = s.tmem_slot;
   const uint32_t tq = tb + (static_cast<uint32_t>(32 * q4) << 16);
 
-  auto issue_load = [&](int i) {                      // thread 0: operand tiles of the sequence's chunk i
+  auto issue_load = [&](int i) {                      // issuing thread: operand tiles of the sequence's chunk i
     TcScanStage& d = s.st[i & 1];
     const size_t tile = static_cast<size_t>(c_begin + i) * p.H + h;
     mbar_expect_tx(&s.full[i & 1], TC_STAGE_TX);
@@ -86,13 +88,14 @@ __global__ void __launch_bounds__(SNT, 1) kda_chunk_scan_tc_kernel(const ScanPar
     bulk_g2s(d.UT, p.UT + tile * TILE_VT, TILE_VT, &s.full[i & 1]);
     bulk_g2s(d.GL, p.GL + tile * TILE_GL, TILE_GL, &s.full[i & 1]);
   };
-  if (tid == 0) {
+  const bool issuer = warp == 8, lead = issuer && lane == 0;
+  if (lead) {
     if (nchunks > 0) issue_load(0);
     if (nchunks > 1) issue_load(1);
   }
 
   // initial state -> TMEM: lane v, columns k = 64 half .. +63
-  {
+  if (!issuer) {
     const size_t sb = (static_cast<size_t>(seq) * p.H + h) * KD * VD;
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
@@ -112,7 +115,7 @@ __global__ void __launch_bounds__(SNT, 1) kda_chunk_scan_tc_kernel(const ScanPar
 
   uint32_t mph = 0;
   bool alive = true;
-  for (int i = 0; i < nchunks && alive; ++i) {
+  for (int i = 0; i < nchunks; ++i) {       // a failed wait leaves through the uniform vote at the top of the next iteration
     TcScanStage& d = s.st[i & 1];
     const int c = c_begin + i;
     // every chunk of this CTA belongs to its one sequence: first token and length by arithmetic (a table look-up would
@@ -125,7 +128,7 @@ __global__ void __launch_bounds__(SNT, 1) kda_chunk_scan_tc_kernel(const ScanPar
 
     if (!mbar_wait(&s.full[i & 1], (i >> 1) & 1)) alive = false;
     // the previous chunk's bulk stores must have read Hb / VNT before they are rewritten
-    if (tid == 0) bulk_wait_read<0>();
+    if (lead) bulk_wait_read<0>();
     alive = __syncthreads_and(alive);
     if (!alive) {
       if (tid == 0) atomicOr(p.status, 1u);
@@ -133,25 +136,28 @@ __global__ void __launch_bounds__(SNT, 1) kda_chunk_scan_tc_kernel(const ScanPar
     }
 
     // ---- state pass: bf16 copy of hT for the products, hT *= Gam_last in TMEM ----------------------------------
+    if (!issuer) {
 #pragma unroll
-    for (int g = 0; g < 4; ++g) {
-      float x[16];
-      umma::tmem_ld16(tq + C_H + 64 * half + 16 * g, x);
-      umma::tmem_ld_wait();
-      *reinterpret_cast<uint4*>(swp(s.Hb + half * 16384, v, 2 * g)) = pack8f(&x[0]);
-      *reinterpret_cast<uint4*>(swp(s.Hb + half * 16384, v, 2 * g + 1)) = pack8f(&x[8]);
+      for (int g = 0; g < 4; ++g) {
+        float x[16];
+        umma::tmem_ld16(tq + C_H + 64 * half + 16 * g, x);
+        umma::tmem_ld_wait();
+        *reinterpret_cast<uint4*>(swp(s.Hb + half * 16384, v, 2 * g)) = pack8f(&x[0]);
+        *reinterpret_cast<uint4*>(swp(s.Hb + half * 16384, v, 2 * g + 1)) = pack8f(&x[8]);
 #pragma unroll
-      for (int e = 0; e < 16; ++e) x[e] *= d.GL[64 * half + 16 * g + e];
-      umma::tmem_st16(tq + C_H + 64 * half + 16 * g, x);
+        for (int e = 0; e < 16; ++e) x[e] *= d.GL[64 * half + 16 * g + e];
+        umma::tmem_st16(tq + C_H + 64 * half + 16 * g, x);
+      }
+      umma::tmem_st_wait();
+      fence_proxy_async();
     }
-    umma::tmem_st_wait();
-    fence_proxy_async();
     umma::fence_before_sync();
     __syncthreads();
     umma::fence_after_sync();
 
-    // ---- products 1 ---------------------------------------------------------------------------------------------------
-    if (tid == 0) {
+    // ---- products 1: the chain from chunk to chunk runs through v_part only; it goes first with its own commit, the
+    // products for o execute behind it while the compute warps already turn v_part into v_new
+    if (lead) {
       const uint32_t aHb = smem_u32(s.Hb), aW = smem_u32(d.W), aQG = smem_u32(d.QG);
       constexpr uint32_t id1 = umma::instr_desc(128, 64, false, false);
       const uint64_t dH0 = umma::desc_kmajor(aHb, 0), dH1 = umma::desc_kmajor(aHb + 16384, 0);
@@ -160,42 +166,48 @@ __global__ void __launch_bounds__(SNT, 1) kda_chunk_scan_tc_kernel(const ScanPar
 #pragma unroll
       for (int sK = 0; sK < 8; ++sK) {
         const uint64_t o2 = static_cast<uint64_t>(sK & 3) * 2u;
-        const uint64_t dA = ((sK >> 2) ? dH1 : dH0) + o2;
-        umma::mma_ss(tb + C_VN, dA, ((sK >> 2) ? dW1 : dW0) + o2, id1, sK > 0);      // v_part^T = hT w^T
-        umma::mma_ss(tb + to, dA, ((sK >> 2) ? dQ1 : dQ0) + o2, id1, sK > 0);        // o^T = hT qg^T
+        umma::mma_ss(tb + C_VN, ((sK >> 2) ? dH1 : dH0) + o2, ((sK >> 2) ? dW1 : dW0) + o2, id1, sK > 0);      // v_part^T = hT w^T
       }
       umma::commit(&s.barM);
+#pragma unroll
+      for (int sK = 0; sK < 8; ++sK) {
+        const uint64_t o2 = static_cast<uint64_t>(sK & 3) * 2u;
+        umma::mma_ss(tb + to, ((sK >> 2) ? dH1 : dH0) + o2, ((sK >> 2) ? dQ1 : dQ0) + o2, id1, sK > 0);        // o^T = hT qg^T
+      }
       if (p.HS) {                                       // training: the bf16 state image is the chunk's HS tile
         bulk_s2g(p.HS + tile * TILE_VK, s.Hb, TILE_VK);
         bulk_commit();
       }
     }
-    if (!mbar_wait(&s.barM, mph & 1)) alive = false;
-    ++mph;
-    umma::fence_after_sync();
+    __syncwarp();
 
     // ---- epilogue 1: v_new^T = u^T - v_part^T -> bf16 tile --------------------------------------------------------------
-    if (alive) {
-      float x[16], y[16];
-      umma::tmem_ld16(tq + C_VN + 32 * half, x);
-      umma::tmem_ld16(tq + C_VN + 32 * half + 16, y);
-      umma::tmem_ld_wait();
+    if (!issuer) {
+      if (!mbar_wait(&s.barM, mph & 1)) alive = false;
+      umma::fence_after_sync();
+      if (alive) {
+        float x[16], y[16];
+        umma::tmem_ld16(tq + C_VN + 32 * half, x);
+        umma::tmem_ld16(tq + C_VN + 32 * half + 16, y);
+        umma::tmem_ld_wait();
 #pragma unroll
-      for (int cix = 0; cix < 4; ++cix) {
-        const uint4 u4 = *reinterpret_cast<const uint4*>(swp(d.UT, v, 4 * half + cix));
-        const uint32_t uw[4] = {u4.x, u4.y, u4.z, u4.w};
-        float* src = (cix < 2) ? &x[8 * cix] : &y[8 * (cix - 2)];
-        float r[8];
+        for (int cix = 0; cix < 4; ++cix) {
+          const uint4 u4 = *reinterpret_cast<const uint4*>(swp(d.UT, v, 4 * half + cix));
+          const uint32_t uw[4] = {u4.x, u4.y, u4.z, u4.w};
+          float* src = (cix < 2) ? &x[8 * cix] : &y[8 * (cix - 2)];
+          float r[8];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 uu = unpack_bf16(uw[e]);
-          r[2 * e] = uu.x - src[2 * e];
-          r[2 * e + 1] = uu.y - src[2 * e + 1];
+          for (int e = 0; e < 4; ++e) {
+            const float2 uu = unpack_bf16(uw[e]);
+            r[2 * e] = uu.x - src[2 * e];
+            r[2 * e + 1] = uu.y - src[2 * e + 1];
+          }
+          *reinterpret_cast<uint4*>(swp(s.VNT, v, 4 * half + cix)) = pack8f(r);
         }
-        *reinterpret_cast<uint4*>(swp(s.VNT, v, 4 * half + cix)) = pack8f(r);
       }
+      fence_proxy_async();
     }
-    fence_proxy_async();
+    ++mph;
     umma::fence_before_sync();
     alive = __syncthreads_and(alive);
     if (!alive) {
@@ -205,7 +217,7 @@ __global__ void __launch_bounds__(SNT, 1) kda_chunk_scan_tc_kernel(const ScanPar
     umma::fence_after_sync();
 
     // ---- products 2 ---------------------------------------------------------------------------------------------------
-    if (tid == 0) {
+    if (lead) {
       const uint32_t aVN = smem_u32(s.VNT), aKG = smem_u32(d.KG), aAQ = smem_u32(d.AQK);
       constexpr uint32_t idH = umma::instr_desc(128, 128, false, true);      // B = kg as MN-major: rows t, two spans of 64 k
       constexpr uint32_t idO = umma::instr_desc(128, 64, false, false);
@@ -221,13 +233,18 @@ __global__ void __launch_bounds__(SNT, 1) kda_chunk_scan_tc_kernel(const ScanPar
         bulk_commit();
       }
     }
+    __syncwarp();
     if (!mbar_wait(&s.barM, mph & 1)) alive = false;
     ++mph;
     umma::fence_after_sync();
-    // this stage's operand tiles are free: fetch chunk i + 2 into it
-    if (tid == 0 && alive && i + 2 < nchunks) issue_load(i + 2);
+    if (issuer) {
+      // this stage's operand tiles are free: fetch chunk i + 2 into it (the compute warps do not wait for this)
+      if (lead && alive && i + 2 < nchunks) issue_load(i + 2);
+      __syncwarp();
+      continue;
+    }
 
-    // ---- epilogue 2: o^T -> bf16 -> staged [t][v] -> coalesced rows ------------------------------------------------------
+    // ---- epilogue 2 (compute warps): o^T -> bf16 -> staged [t][v] -> coalesced rows --------------------------------------
     if (alive) {
       float x[16], y[16];
       umma::tmem_ld16(tq + to + 32 * half, x);
@@ -240,12 +257,8 @@ __global__ void __launch_bounds__(SNT, 1) kda_chunk_scan_tc_kernel(const ScanPar
       }
     }
     umma::fence_before_sync();
-    alive = __syncthreads_and(alive);
-    if (!alive) {
-      if (tid == 0) atomicOr(p.status, 2u);
-      break;
-    }
-    for (int e = tid; e < C * 16; e += SNT) {
+    asm volatile("bar.sync 1, 256;" ::: "memory");      // the eight compute warps only
+    for (int e = tid; e < C * 16; e += SCT) {
       const int r = e >> 4, pc = e & 15;
       if (r < ci.len)
         *reinterpret_cast<uint4*>(p.o + (static_cast<size_t>(ci.tok0 + r) * p.H + h) * VD + pc * 8) =
@@ -253,9 +266,10 @@ __global__ void __launch_bounds__(SNT, 1) kda_chunk_scan_tc_kernel(const ScanPar
     }
     // (the next iteration's first barrier orders these reads of oS before it is rewritten)
   }
+  alive = __syncthreads_and(alive);
 
   // final state
-  if (alive && p.ht) {
+  if (alive && p.ht && !issuer) {
     umma::fence_after_sync();
     const size_t sb = (static_cast<size_t>(seq) * p.H + h) * KD * VD;
 #pragma unroll
@@ -267,7 +281,7 @@ __global__ void __launch_bounds__(SNT, 1) kda_chunk_scan_tc_kernel(const ScanPar
       for (int e = 0; e < 16; ++e) p.ht[sb + static_cast<size_t>(64 * half + 16 * g + e) * VD + v] = x[e];
     }
   }
-  if (tid == 0) bulk_wait<0>();          // outstanding bulk stores read shared memory that dies with the CTA
+  if (lead) bulk_wait<0>();              // outstanding bulk stores read shared memory that dies with the CTA
   umma::fence_before_sync();
   __syncthreads();
   if (warp == 0) umma::tmem_dealloc(tb, 512);
