@@ -1,23 +1,37 @@
 #!/usr/bin/env python
 """Benchmark of the KDA hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference] [--weak]
 
 Default workload `train_bf16`: bf16 chunk_kda forward+backward, B=8 T=8192 H=32 d_k=d_v=128, chunk 64,
 seeded synthetic inputs (kda_b200/inputs.py).  One step = one forward+backward over that batch.
-With N > 1 (launched by torchrun, one rank per GPU) every rank runs its own batch of the same shape
-(independent (batch, head) shards, no collective on the data path): weak scaling, value = all ranks'
-tokens / max-over-ranks time.
 
-Prints ONE JSON line: metric/value (inputs resident in HBM), `e2e` (same step through the public
-operator with pinned HOST buffers: host->device copies of every input and device->host copies of
-every output inside the timed region), `roofline` of the dominant kernel (per-kernel times from CUDA
-events recorded by the library around each kernel during the timed steps), `cpu_baseline` (the
-float32 token-recurrent PyTorch restatement on the host cores, bounded sample), clocks, launches.
+With N > 1 (launched by torchrun, one rank per GPU) the stated batch is SHARDED: the (batch, head) recurrences
+are independent, so rank r takes the batch rows `kda_b200.shard.batch_slice(B, r, N)` (B/N rows each), there is
+no collective on the data path, and value = the whole batch's tokens / max-over-ranks time ("scaling":
+"strong").  `--weak` runs N full replicas instead (every rank its own batch of the full shape).
 
-`--impl reference` times that CPU restatement alone, on all host threads (the NVlabs/kda repository
-has no implementation of this operator to run).  `--gpu-bar` adds a `gpu_bar` object: flash-linear-attention's
-own Triton chunk_kda timed on the same GPU and inputs, when that package imports (a comparison, off by default).
+Prints ONE JSON line:
+  metric / value      tokens/s with the inputs resident in HBM (CUDA events, max over ranks);
+  e2e                 the same step through the public host-resident API with pinned HOST buffers: host->device
+                      copies of every input and device->host copies of every output inside the timed region;
+  roofline            the kernel with the largest share of the step: ALGORITHMIC bytes (the operator-boundary
+                      tensors that kernel must read and write: q, k, v, g, beta, o, dO and the gradients) per
+                      launch / its average launch time (CUDA events recorded by the library around each kernel
+                      during the timed steps) / the measured HBM copy bandwidth.  Beside it `design_bytes_per_launch`
+                      (boundary tensors + the tiles this design exchanges between its kernels), `dram_efficiency`
+                      (that figure / time / peak: how well the kernel streams what it does move), `traffic` (ncu DRAM
+                      bytes of a smaller case scaled by units) and `wasted_traffic_ratio` = traffic / algorithmic;
+  step_roofline       the whole step against both roofs (4,364 B and 559,787 FLOP per (token, head));
+  workloads           (N = 1, default run) the other stated workloads, each timed on its own after the headline:
+                      prefill forward, packed varlen forward+backward, decode (256 consecutive steps, GB/s against the
+                      measured copy bandwidth and against the nominal 8 TB/s), and `gpu_bar`: flash-linear-attention's
+                      own Triton kernels on the same GPU and shapes (a comparison; nothing of it is on the product path);
+  cpu_baseline        the float32 token-recurrent PyTorch restatement on the host cores, bounded sample;
+  clocks, gpu_launches, checks (outputs finite, device status words 0).
+
+`--impl reference` times the CPU restatement alone, on all host threads (the NVlabs/kda repository has no
+implementation of this operator to run).
 """
 from __future__ import annotations
 
@@ -38,26 +52,29 @@ import torch  # noqa: E402
 
 from kda_b200.inputs import (WORKLOADS, decode_bytes_per_seq_head, flops_per_token_head, make_inputs,  # noqa: E402
                              make_workload, min_hbm_bytes_per_token_head)
+from kda_b200.shard import balance_sequences, batch_head_block, batch_slice, take_sequences  # noqa: E402
 
 METRIC = "KDA fwd+bwd tokens/s (H=32,d=128,bf16)"
+NOMINAL_HBM_GBS = 8000.0
 
-# Algorithmic work of each kernel per (token, head): C=64, K=V=128; GEMM = 2mnk, triangular products
-# counted full, the 64x64 inverse as (2/3) C^2 per token; bytes = the tensors the kernel must read and
-# write at the operator boundary plus the tiles it exchanges with the neighbouring kernels.
 K_, V_, C_ = 128, 128, 64
-_IN = 2 * K_ + 2 * K_ + 2 * V_ + 4 * K_ + 4                      # q,k,v bf16 + g fp32 + beta
+_IN = 2 * K_ + 2 * K_ + 2 * V_ + 4 * K_ + 4                      # q,k,v bf16 + g fp32 + beta = 1,284 B
+_GRADS = 2 * K_ + 2 * K_ + 2 * V_ + 4 * K_ + 4                   # dq,dk,dv bf16 + dg fp32 + dbeta = 1,284 B
 _TK, _TT, _VK = 2 * K_, 2 * C_, 2 * K_ * V_ / C_                 # bytes per token of a [64x128], [64x64], [128x128] bf16 tile
+# Per kernel and per (token, head): (FLOPs, ALGORITHMIC bytes, DESIGN bytes).
+#   algorithmic = the operator-boundary tensors the kernel must touch.  Forward 1,540 B = prepare 1,284 (q,k,v,g,beta)
+#                 + scan 256 (o).  Backward 2,824 B = q,k,v,g,beta,dO read + dq,dk,dv,dg,dbeta written, all of it by
+#                 bwd_main; the reverse scan reads dO (256 B) a second time, which is its only boundary tensor.
+#   design      = algorithmic + the per-chunk tiles this design moves between its kernels through HBM.
+# GEMM = 2mnk, triangular products counted full, the 64x64 inverse as (2/3) C^2 per token.
 KERNEL_WORK = {
-    # name: (flops, bytes) per (token, head)
-    "prepare": (2 * C_ * (3 * K_ + V_) + (2.0 / 3.0) * C_ * C_, _IN + 4 * _TK + _TT + 2 * _TT + 8),
-    "scan": (6 * K_ * V_ + 2 * C_ * V_, 4 * _TK + _TT + 8 + 2 * V_ + _VK + _TK),
-    "bwd_scan": (6 * K_ * V_ + 2 * C_ * V_, 3 * _TK + _TT + 8 + 2 * V_ + _VK + _TK),
-    "bwd_main": (6 * K_ * V_ + 12 * C_ * K_ + 6 * C_ * V_ + 4 * C_ * C_,
-                 _IN + 2 * V_ + 2 * _TT + 2 * _VK + 2 * _TK + (2 * K_ + 2 * K_ + 2 * V_ + 4 * K_ + 4)),   # = 4,616 B
-    # gate front end with bf16 raw inputs: fwd reads g_raw, beta logits, writes g, beta (fp32);
-    # bwd reads dg, dbeta (fp32), g_raw, beta logits, writes dg_raw, dbeta_raw (bf16)
-    "gate_fwd": (12 * K_, 2 * K_ + 4 * K_ + 2 + 4),                # = 774 B
-    "gate_bwd": (20 * K_, 4 * K_ + 2 * K_ + 2 * K_ + 4 + 2 + 2),   # = 1,032 B
+    "prepare": (2 * C_ * (3 * K_ + V_) + (2.0 / 3.0) * C_ * C_, _IN, _IN + 4 * _TK + _TT + 2 * _TT + 8),
+    "scan": (6 * K_ * V_ + 2 * C_ * V_, 2 * V_, 4 * _TK + _TT + 8 + 2 * V_ + _VK + _TK),
+    "bwd_scan": (6 * K_ * V_ + 2 * C_ * V_, 2 * V_, 3 * _TK + _TT + 8 + 2 * V_ + _VK + _TK),
+    "bwd_main": (6 * K_ * V_ + 12 * C_ * K_ + 6 * C_ * V_ + 4 * C_ * C_, _IN + 2 * V_ + _GRADS,
+                 _IN + 2 * V_ + 2 * _TT + 2 * _VK + 2 * _TK + _GRADS),
+    "gate_fwd": (12 * K_, 2 * K_ + 4 * K_ + 2 + 4, 2 * K_ + 4 * K_ + 2 + 4),
+    "gate_bwd": (20 * K_, 4 * K_ + 2 * K_ + 2 * K_ + 4 + 2 + 2, 4 * K_ + 2 * K_ + 2 * K_ + 4 + 2 + 2),
 }
 # DRAM bytes per (token, head) that ncu measured (dram__bytes_read.sum + dram__bytes_write.sum of one launch) on a
 # small case of each kernel (B=1 T=8192, 262,144 (token, head) units; summaries under profiles/).  Traffic grows in
@@ -154,8 +171,8 @@ def run_reference(args, rank):
     value = T / (ms / 1e3)
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f32", "data": "synthetic",
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak" if args.weak else "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "train_bf16 (B=8 T=8192 H=32 K=V=128 fwd+bwd)",
                    "sample": f"B=1 T={T} H=32 K=V=128 per step"},
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port",
@@ -165,53 +182,203 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
-def time_fla_triton(args, w, devt, cu, grad_names, tokens):
-    """The on-box GPU comparison: flash-linear-attention's own chunk_kda (Triton) on the same inputs, same step
-    definition (forward, or forward + backward with the same output gradients), CUDA events, same warm-up rule.
-    A comparison line only: nothing of it is on the product path."""
-    if args.gate:
-        return {"unavailable": "timed without the gate front end"}
+# =====================================================================================================================
+# steps of the workloads on device-resident inputs
+# =====================================================================================================================
+
+def make_step(workload: str, x: dict, cu, gate: bool = False, l2: bool = False):
+    """Returns (step function over a dict of device tensors, kernel launches per step, names that get gradients)."""
+    from kda_b200 import chunk_kda, fused_recurrent_kda_fwd
+    w = WORKLOADS[workload]
+    if workload == "decode":
+        state = x["h0"].clone()
+        dec_kw = dict(use_qk_l2norm_in_kernel=l2)
+        if gate:       # the layer's decode call: raw gate input, beta logits; activated inside the one kernel
+            dec_kw.update(use_gate_in_kernel=True, use_beta_sigmoid_in_kernel=True, A_log=x["A_log"], dt_bias=x["dt_bias"])
+
+        def step(x=x):
+            return fused_recurrent_kda_fwd(x["q"], x["k"], x["v"], x["g"], x["beta"], scale=128 ** -0.5, initial_state=state,
+                                           inplace_final_state=True, **dec_kw)
+        return step, 1, []
+    if w.backward:
+        grad_names = ["q", "k", "v", "g", "beta"] + (["h0"] if x.get("h0") is not None else []) + (["A_log", "dt_bias"] if gate else [])
+        gate_kw = dict(use_gate_in_kernel=True, use_beta_sigmoid_in_kernel=True) if gate else {}
+
+        def step(x=x):
+            leaves = [x[n].requires_grad_(True) for n in grad_names]
+            kw = dict(gate_kw, A_log=x["A_log"], dt_bias=x["dt_bias"]) if gate else {}
+            o, ht = chunk_kda(x["q"], x["k"], x["v"], x["g"], x["beta"], initial_state=x.get("h0"),
+                              output_final_state=True, cu_seqlens=cu, use_qk_l2norm_in_kernel=l2, **kw)
+            grads = torch.autograd.grad([o, ht], leaves, [x["do"], x["dht"]])
+            return (o, ht) + tuple(grads)
+        return step, (10 if gate else 5), grad_names      # gate: + activation, beta sigmoid; + their backward and the reduction
+
+    def step(x=x):
+        with torch.no_grad():
+            return chunk_kda(x["q"], x["k"], x["v"], x["g"], x["beta"], initial_state=x.get("h0"),
+                             output_final_state=True, cu_seqlens=cu, use_qk_l2norm_in_kernel=l2)
+    return step, 3, []
+
+
+def time_steps(step, steps: int, warmup: int) -> float:
+    """Milliseconds per step: CUDA events on the current stream, after `warmup` untimed steps, synchronised both sides."""
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def other_workloads(peaks, dev) -> dict:
+    """The stated workloads beside the headline one, each timed on its own on device-resident inputs that are
+    drawn on the device (seeded).  Inputs exceed L2 by far in every case, so no flush between steps."""
+    from kda_b200 import _lib
+    out = {}
+    for name, steps in (("prefill_bf16", 20), ("varlen_bf16", 5), ("decode", 256)):
+        w = WORKLOADS[name]
+        try:
+            x = make_workload(name, seed=0, device=dev, generate_on_device=True)
+            cu = x.pop("cu_seqlens")
+            step, launches, _ = make_step(name, x, cu)
+            ms = time_steps(step, steps, 3)
+            B, T, H = x["q"].shape[:3]
+            tokens, th = B * T, B * T * H
+            rec = {"config": f"B={B} T={T} H={H} K=V=128" + (f", {cu.numel() - 1} packed sequences" if cu is not None else ""),
+                   "ms_per_step": ms, "steps": steps, "value": tokens / (ms / 1e3), "unit": "tokens/s",
+                   "gpu_launches": launches * steps}
+            if name == "decode":
+                byt = B * H * decode_bytes_per_seq_head()
+                gbs = byt / (ms * 1e-3) / 1e9
+                rec.update({"hbm_gbs": gbs, "hbm_frac_of_measured": gbs / peaks["hbm"], "hbm_frac_of_nominal_8tbs": gbs / NOMINAL_HBM_GBS,
+                            "algorithmic_bytes_per_step": byt, "status": _lib.recurrent_status()})
+            else:
+                by = min_hbm_bytes_per_token_head(backward=w.backward) * th
+                fl = flops_per_token_head(backward=w.backward) * th
+                rec.update({"hbm_frac_min_traffic": by / (ms * 1e-3) / 1e9 / peaks["hbm"],
+                            "tensor_frac_sustained": fl / (ms * 1e-3) / 1e12 / peaks["tf_sust"]})
+            out[name] = rec
+            del x, step
+        except Exception as e:          # noqa: BLE001   (a workload that does not fit must not lose the headline line)
+            out[name] = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
+        torch.cuda.empty_cache()
+    return out
+
+
+# =====================================================================================================================
+# the on-box GPU comparison: flash-linear-attention's Triton kernels, in a child process with a deadline
+# =====================================================================================================================
+
+def gpu_bar_child():
+    """Runs in a child process: times fla.ops.kda on train / prefill / decode shapes and prints one JSON line per
+    workload as soon as it is measured (so that a deadline in the parent keeps what finished)."""
     try:
+        import fla
+        import triton
         from fla.ops.kda import chunk_kda as fla_chunk_kda
         from fla.ops.kda import fused_recurrent_kda as fla_recurrent_kda
     except Exception as e:          # noqa: BLE001
-        return {"unavailable": f"fla does not import on this box: {type(e).__name__}: {e}"[:200]}
-    x = devt
-    name = "fused_recurrent_kda" if args.workload == "decode" else "chunk_kda"
+        print(json.dumps({"workload": "*", "unavailable": f"unavailable on this box: {type(e).__name__}: {e}"[:300]}), flush=True)
+        return
+    impl = f"flash-linear-attention {getattr(fla, '__version__', '?')}, Triton {triton.__version__}"
+    dev = torch.device("cuda", 0)
+    for name, steps in (("train_bf16", 5), ("prefill_bf16", 10), ("decode", 64)):
+        w = WORKLOADS[name]
+        try:
+            x = make_workload(name, seed=0, device=dev, generate_on_device=True)
+            x.pop("cu_seqlens")
+            grad_names = ["q", "k", "v", "g", "beta", "h0"]
 
-    def step():
-        if args.workload == "decode":
-            # fla's public entry point returns the new state in a second buffer (same bytes moved as in place)
-            with torch.no_grad():
-                return fla_recurrent_kda(x["q"], x["k"], x["v"], x["g"], x["beta"], scale=128 ** -0.5,
-                                         initial_state=x["h0"], output_final_state=True)
-        if w.backward:
-            leaves = [x[n].detach().requires_grad_(True) for n in grad_names]
-            t = dict(zip(grad_names, leaves))
-            o, ht = fla_chunk_kda(t["q"], t["k"], t["v"], t["g"], t["beta"], initial_state=t.get("h0"),
-                                  output_final_state=True, cu_seqlens=cu)
-            return torch.autograd.grad([o, ht], leaves, [x["do"], x["dht"]])
-        with torch.no_grad():
-            return fla_chunk_kda(x["q"], x["k"], x["v"], x["g"], x["beta"], initial_state=x.get("h0"),
-                                 output_final_state=True, cu_seqlens=cu)
+            def step():
+                if name == "decode":      # fla's public entry point returns the new state in a second buffer (same bytes moved)
+                    with torch.no_grad():
+                        return fla_recurrent_kda(x["q"], x["k"], x["v"], x["g"], x["beta"], scale=128 ** -0.5,
+                                                 initial_state=x["h0"], output_final_state=True)
+                if w.backward:
+                    leaves = [x[n].detach().requires_grad_(True) for n in grad_names]
+                    t = dict(zip(grad_names, leaves))
+                    o, ht = fla_chunk_kda(t["q"], t["k"], t["v"], t["g"], t["beta"], initial_state=t["h0"], output_final_state=True)
+                    return torch.autograd.grad([o, ht], leaves, [x["do"], x["dht"]])
+                with torch.no_grad():
+                    return fla_chunk_kda(x["q"], x["k"], x["v"], x["g"], x["beta"], initial_state=x["h0"], output_final_state=True)
+            ms = time_steps(step, steps, 3)
+            B, T = x["q"].shape[:2]
+            print(json.dumps({"workload": name, "impl": f"fla.ops.kda ({impl})", "ms_per_step": ms, "steps": steps,
+                              "value": B * T / (ms / 1e3), "unit": "tokens/s"}), flush=True)
+            del x
+            torch.cuda.empty_cache()
+        except Exception as e:          # noqa: BLE001
+            print(json.dumps({"workload": name, "unavailable": f"unavailable on this box: {type(e).__name__}: {e}"[:300]}), flush=True)
+
+
+def gpu_bar(deadline_s: float) -> dict:
+    """Runs gpu_bar_child() in a child process (Triton compiles for a minute or more) and keeps what it measured
+    before the deadline."""
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES=os.environ.get("CUDA_VISIBLE_DEVICES", "0").split(",")[0])
+    for k in ("RANK", "LOCAL_RANK", "WORLD_SIZE", "MASTER_ADDR", "MASTER_PORT"):
+        env.pop(k, None)
+    out = {}
     try:
-        for _ in range(args.warmup):
-            step()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        n = max(1, min(args.steps, 10))
-        e0.record()
-        for _ in range(n):
-            step()
-        e1.record()
-        torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1) / n
-    except Exception as e:          # noqa: BLE001
-        return {"unavailable": f"fla.ops.kda.{name} failed on this box: {type(e).__name__}: {e}"[:300]}
-    import fla
-    import triton
-    return {"impl": f"fla.ops.kda.{name} (flash-linear-attention {getattr(fla, '__version__', '?')}, Triton {triton.__version__})",
-            "value": tokens / (ms / 1e3), "unit": "tokens/s", "ms_per_step": ms, "steps": n}
+        p = subprocess.Popen([sys.executable, os.path.abspath(__file__), "--gpu-bar-child"], stdout=subprocess.PIPE,
+                             stderr=subprocess.DEVNULL, text=True, env=env)
+    except OSError as e:
+        return {"unavailable": f"unavailable on this box: {e}"}
+    try:
+        stdout, _ = p.communicate(timeout=deadline_s)
+    except subprocess.TimeoutExpired:
+        p.kill()                         # the exact child started above
+        stdout, _ = p.communicate()
+        out["note"] = f"stopped at the {deadline_s:.0f} s deadline; workloads not listed were not reached"
+    for ln in (stdout or "").splitlines():
+        try:
+            rec = json.loads(ln)
+        except ValueError:
+            continue
+        out[rec.pop("workload", "?")] = rec
+    if not out:
+        out["unavailable"] = "unavailable on this box: the comparison process printed nothing"
+    return out
+
+
+# =====================================================================================================================
+
+def shard_inputs(args, w, rank, world, dev):
+    """This rank's share of the workload as host tensors (headline workload: CPU generator, one seed per batch row,
+    so that the union over ranks is the same batch for every N) or device tensors (the others)."""
+    B = max(1, w.B // args.scale_down)
+    if args.workload == "train_bf16" and not w.n_seqs:
+        rows = range(B) if (args.weak or world == 1) else range(B)[batch_slice(B, rank, world)]
+        seed0 = rank * 1000 if args.weak else 0
+        parts = [make_inputs(1, w.T, w.H, w.K, w.V, w.dtype, seed=seed0 + r, h0_std=w.h0_std, backward=True) for r in rows]
+        host = {n: torch.cat([p[n] for p in parts], 0) for n in parts[0] if parts[0][n] is not None}
+        return host, None, B * w.T * (world if args.weak else 1)
+    # other workloads: drawn on the device, then this rank's share is cut out
+    x = make_workload(args.workload, seed=(rank if args.weak else 0), device=dev, scale_down=args.scale_down, generate_on_device=True)
+    cu = x.pop("cu_seqlens")
+    x = {n: t for n, t in x.items() if t is not None}
+    total = x["q"].shape[0] * x["q"].shape[1]
+    if args.weak or world == 1:
+        return x, cu, total * world
+    if cu is not None:                                   # whole sequences, balanced by token count
+        lens = (cu[1:] - cu[:-1]).tolist()
+        mine = balance_sequences(lens, world)[rank]
+        cul = cu.tolist()
+        y = {}
+        for n, t in x.items():
+            if n in ("h0", "dht"):
+                y[n] = t[mine].contiguous()
+            else:
+                y[n], new_cu = take_sequences(t, cul, mine)
+        return y, new_cu.to(dev), total
+    if args.workload == "decode":
+        sl = batch_slice(x["q"].shape[0], rank, world)
+        return {n: t[sl].contiguous() for n, t in x.items()}, None, total
+    b0, b1, h0, h1 = batch_head_block(x["q"].shape[0], w.H, rank, world)      # (batch x head) units, contiguous block
+    return {n: (t[b0:b1, h0:h1] if n in ("h0", "dht") else t[b0:b1, :, h0:h1]).contiguous() for n, t in x.items()}, None, total
 
 
 def main():
@@ -221,18 +388,22 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="train_bf16", choices=sorted(WORKLOADS))
+    ap.add_argument("--weak", action="store_true", help="N > 1: every rank runs its own full batch (replicas) instead of a shard")
     ap.add_argument("--scale-down", type=int, default=1, help="divide the batch (smaller case for profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-workloads", action="store_true", help="skip the other workloads and the Triton comparison")
     ap.add_argument("--gate", action="store_true",
                     help="call the operator as the layer does: raw bf16 gate input + A_log + dt_bias and beta logits "
                          "(use_gate_in_kernel, use_beta_sigmoid_in_kernel); training workloads and decode")
     ap.add_argument("--l2norm", action="store_true", help="use_qk_l2norm_in_kernel=True (chunked workloads)")
-    ap.add_argument("--gpu-bar", action="store_true",
-                    help="also time fla.ops.kda.chunk_kda (the Triton kernels of flash-linear-attention, if it imports on "
-                         "this box) on the same device-resident inputs: the on-box GPU comparison; 1 GPU only")
+    ap.add_argument("--gpu-bar-deadline", type=float, default=240.0, help="seconds the Triton comparison may take (0: skip it)")
+    ap.add_argument("--gpu-bar-child", action="store_true", help=argparse.SUPPRESS)
     args = ap.parse_args()
 
+    if args.gpu_bar_child:
+        gpu_bar_child()
+        return
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -248,25 +419,24 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    from kda_b200 import _lib, chunk_kda, fused_recurrent_kda_fwd
+    from kda_b200 import _lib
     w = WORKLOADS[args.workload]
     peaks = load_peaks()
-    host = make_workload(args.workload, seed=rank, scale_down=args.scale_down)
-    cu_host = host.pop("cu_seqlens")
+    mine, cu, job_tokens = shard_inputs(args, w, rank, world, dev)
     if args.gate:
         if not w.backward and args.workload != "decode":
             raise SystemExit("--gate needs a forward+backward workload or the decode workload")
         gen = torch.Generator().manual_seed(1000 + rank)
-        host["g"] = torch.randn(host["g"].shape, generator=gen).bfloat16()                      # raw gate input
-        host["beta"] = torch.randn(host["beta"].shape, generator=gen).bfloat16()                # beta logits
-        host["A_log"] = torch.log(torch.empty(w.H).uniform_(1, 16, generator=gen))
-        host["dt_bias"] = torch.randn(w.H * w.K, generator=gen)
-    names = [n for n, t in host.items() if t is not None]
-    pinned = {n: host[n].pin_memory() for n in names}
-    devt = {n: pinned[n].to(dev, non_blocking=True) for n in names}
-    cu = cu_host.to(dev) if cu_host is not None else None
+        mine["g"] = torch.randn(mine["g"].shape, generator=gen).bfloat16().to(mine["g"].device)            # raw gate input
+        mine["beta"] = torch.randn(mine["beta"].shape, generator=gen).bfloat16().to(mine["beta"].device)   # beta logits
+        mine["A_log"] = torch.log(torch.empty(w.H).uniform_(1, 16, generator=gen))
+        mine["dt_bias"] = torch.randn(w.H * w.K, generator=gen)
+    names = list(mine)
+    host_resident = not mine["q"].is_cuda
+    pinned = {n: mine[n].pin_memory() for n in names} if host_resident else None
+    devt = {n: (pinned[n].to(dev, non_blocking=True) if host_resident else mine[n].to(dev)) for n in names}
     B, T, H = devt["q"].shape[:3]
-    tokens = B * T
+    tokens = B * T                                       # this rank's tokens per step
     torch.cuda.synchronize()
 
     def barrier():
@@ -282,40 +452,7 @@ def main():
             return float(t.item())
         return ms
 
-    launches_per_step = 0
-    if args.workload == "decode":
-        state = devt["h0"].clone()
-        scale = 128 ** -0.5
-
-        dec_kw = dict(use_qk_l2norm_in_kernel=args.l2norm)
-        if args.gate:       # the layer's decode call: raw gate input, beta logits; activated inside the one kernel
-            dec_kw.update(use_gate_in_kernel=True, use_beta_sigmoid_in_kernel=True, A_log=devt["A_log"], dt_bias=devt["dt_bias"])
-
-        def step(x=devt):
-            return fused_recurrent_kda_fwd(x["q"], x["k"], x["v"], x["g"], x["beta"], scale=scale, initial_state=state,
-                                           inplace_final_state=True, **dec_kw)
-        launches_per_step = 1
-        grad_names = []
-    elif w.backward:
-        grad_names = ["q", "k", "v", "g", "beta"] + (["h0"] if "h0" in devt else []) + (["A_log", "dt_bias"] if args.gate else [])
-        gate_kw = dict(use_gate_in_kernel=True, use_beta_sigmoid_in_kernel=True) if args.gate else {}
-
-        def step(x=devt):
-            leaves = [x[n].requires_grad_(True) for n in grad_names]
-            kw = dict(gate_kw, A_log=x["A_log"], dt_bias=x["dt_bias"]) if args.gate else {}
-            o, ht = chunk_kda(x["q"], x["k"], x["v"], x["g"], x["beta"], initial_state=x.get("h0"),
-                              output_final_state=True, cu_seqlens=cu, use_qk_l2norm_in_kernel=args.l2norm, **kw)
-            grads = torch.autograd.grad([o, ht], leaves, [x["do"], x["dht"]])
-            return (o, ht) + tuple(grads)
-        launches_per_step = 10 if args.gate else 5      # gate: + activation, beta sigmoid; + their backward and the reduction
-    else:
-        grad_names = []
-
-        def step(x=devt):
-            with torch.no_grad():
-                return chunk_kda(x["q"], x["k"], x["v"], x["g"], x["beta"], initial_state=x.get("h0"),
-                                 output_final_state=True, cu_seqlens=cu, use_qk_l2norm_in_kernel=args.l2norm)
-        launches_per_step = 3
+    step, launches_per_step, grad_names = make_step(args.workload, devt, cu, args.gate, args.l2norm)
 
     # ---------------- kernel-resident timing ----------------
     sampler = ClockSampler(local_rank if os.environ.get("CUDA_VISIBLE_DEVICES") is None else
@@ -331,12 +468,16 @@ def main():
     barrier()
     e0.record()
     for _ in range(args.steps):
-        step()
+        outs = step()
     e1.record()
     barrier()
     ms_total = maxms(e0.elapsed_time(e1))
     stages = _lib.profile_read(reset=True)
     _lib.profile_enable(False)
+    # what was timed is checked: every output finite, no bounded wait gave up, cu_seqlens accepted
+    checks = {"outputs_finite": all(bool(torch.isfinite(t.float()).all()) for t in outs if isinstance(t, torch.Tensor)),
+              "decode_status": _lib.recurrent_status()}
+    del outs
     clocks = None
     if rank == 0:
         # a timed region of a few milliseconds (decode) ends before nvidia-smi delivers: keep the same step running,
@@ -352,13 +493,14 @@ def main():
         if extended:
             clocks["note"] = "timed region shorter than the sampling interval: sampled over untimed repeats of the same step right after it"
     ms_step = ms_total / args.steps
-    value = world * tokens / (ms_step / 1e3)
+    value = job_tokens / (ms_step / 1e3)
 
     # ---------------- end to end: pinned host buffers in, every output back out ----------------
     e2e = None
-    if not args.no_e2e:
+    if not args.no_e2e and host_resident:
         out_host = None
         pipelined = w.backward and cu is None and args.workload != "decode" and not args.gate and not args.l2norm
+        head_groups = 4 if (pipelined and B < 4) else None      # few batch rows: cut the pieces along the heads as well
 
         def e2e_step():
             nonlocal out_host
@@ -367,16 +509,17 @@ def main():
                 # steps are queued without waiting (two alternating sets of pinned output buffers), so step i+1's
                 # copy-in runs under step i's copy-out; the timed region ends after the last result has landed
                 from kda_b200.host import chunk_kda_fwd_bwd_host
-                out_sets[e2e_count[0] & 1] = out_host = chunk_kda_fwd_bwd_host(pinned, out_sets[e2e_count[0] & 1], wait=False)
+                out_sets[e2e_count[0] & 1] = out_host = chunk_kda_fwd_bwd_host(pinned, out_sets[e2e_count[0] & 1], wait=False,
+                                                                              head_groups=head_groups)
                 e2e_count[0] += 1
                 return
             x = {n: pinned[n].to(dev, non_blocking=True) for n in names}
-            outs = step(x)
-            outs = [t for t in outs if t is not None]
+            res = [t for t in step(x) if t is not None]
             if out_host is None:
-                out_host = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True) for t in outs]
-            for hbuf, t in zip(out_host, outs):
+                out_host = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True) for t in res]
+            for hbuf, t in zip(out_host, res):
                 hbuf.copy_(t, non_blocking=True)
+
         def e2e_drain():
             if pipelined:
                 from kda_b200.host import host_synchronize
@@ -396,14 +539,10 @@ def main():
         ms_e2e = maxms(e0.elapsed_time(e1)) / n_e2e
         h2d = sum(pinned[n].numel() * pinned[n].element_size() for n in names)
         d2h = sum(t.numel() * t.element_size() for t in (out_host.values() if isinstance(out_host, dict) else out_host))
-        e2e = {"value": world * tokens / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
-               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": n_e2e,
+        e2e = {"value": job_tokens / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "bytes": "per rank", "steps": n_e2e,
                "api": "kda_b200.host.chunk_kda_fwd_bwd_host(wait=False) + host_synchronize (batch slices pipelined over 3 streams, "
                       "consecutive steps overlapped, results of all steps in host memory before the clock stops)" if pipelined else "kda_b200.chunk_kda"}
-
-    gpu_bar = None
-    if args.gpu_bar:
-        gpu_bar = time_fla_triton(args, w, devt, cu, grad_names, tokens) if world == 1 else {"unavailable": "timed on 1 GPU only"}
 
     if rank != 0:
         if world > 1:
@@ -411,21 +550,24 @@ def main():
         return
 
     # ---------------- roofline of the dominant kernel ----------------
-    th = tokens * H
+    th = tokens * H                                      # (token, head) units one launch of this rank processes
     if args.workload == "decode":
         byt = B * H * decode_bytes_per_seq_head()
         ach = byt / (ms_step * 1e-3) / 1e9
         roof = {"kernel": "kda_decode_bulk_kernel", "bound": "hbm", "achieved": ach, "peak": peaks["hbm"], "unit": "GB/s",
-                "frac": ach / peaks["hbm"], "traffic": KERNEL_TRAFFIC["decode"] * B * H,
+                "frac": ach / peaks["hbm"], "frac_of_nominal_8tbs": ach / NOMINAL_HBM_GBS, "traffic": KERNEL_TRAFFIC["decode"] * B * H,
                 "traffic_source": "ncu capture of a smaller case, scaled by units", "peak_source": peaks["src"]}
         kernels = {}
     else:
         kernels = {s: {"ms_per_launch": (ms / n), "launches": n} for s, (ms, n) in stages.items() if n > 0}
-        for s_, kv in kernels.items():          # every kernel against the HBM roof at its algorithmic bytes ("of measured")
+        for s_, kv in kernels.items():
             if s_ in KERNEL_WORK:
-                kv["hbm_frac"] = KERNEL_WORK[s_][1] * th / (kv["ms_per_launch"] * 1e-3) / 1e9 / peaks["hbm"]
+                sec_ = kv["ms_per_launch"] * 1e-3
+                kv["hbm_frac"] = KERNEL_WORK[s_][1] * th / sec_ / 1e9 / peaks["hbm"]          # algorithmic bytes, "of measured"
+                kv["dram_efficiency"] = KERNEL_WORK[s_][2] * th / sec_ / 1e9 / peaks["hbm"]   # design bytes (boundary + tiles)
+                kv["tensor_frac_sustained"] = KERNEL_WORK[s_][0] * th / sec_ / 1e12 / peaks["tf_sust"]
         dom = max((s for s in kernels if s in KERNEL_WORK), key=lambda s: kernels[s]["ms_per_launch"] * kernels[s]["launches"])
-        fl, by = KERNEL_WORK[dom]
+        fl, by, design = KERNEL_WORK[dom]
         sec = kernels[dom]["ms_per_launch"] * 1e-3
         ridge = peaks["tf_sust"] * 1e12 / (peaks["hbm"] * 1e9)
         if fl / by >= ridge:
@@ -436,10 +578,14 @@ def main():
             ach = by * th / sec / 1e9
             roof = {"kernel": dom, "bound": "hbm", "achieved": ach, "peak": peaks["hbm"], "unit": "GB/s",
                     "frac": ach / peaks["hbm"]}
-        roof.update({"traffic": KERNEL_TRAFFIC[dom] * th if dom in KERNEL_TRAFFIC else None, "traffic_source": "ncu capture of a smaller case, scaled by units",
+        traffic = KERNEL_TRAFFIC[dom] * th if dom in KERNEL_TRAFFIC else None
+        roof.update({"traffic": traffic, "traffic_source": "ncu capture of a smaller case, scaled by units",
+                     "wasted_traffic_ratio": (traffic / (by * th)) if traffic else None,
                      "peak_source": peaks["src"], "ms_per_launch": kernels[dom]["ms_per_launch"],
-                     "algorithmic_flops_per_launch": fl * th, "algorithmic_bytes_per_launch": by * th})
-    # whole-step roofline fractions (both bounds), for context
+                     "algorithmic_flops_per_launch": fl * th, "algorithmic_bytes_per_launch": by * th,
+                     "design_bytes_per_launch": design * th, "dram_efficiency": design * th / sec / 1e9 / peaks["hbm"],
+                     "tensor_frac_sustained": fl * th / sec / 1e12 / peaks["tf_sust"]})
+    # whole-step roofline fractions (both bounds) of this rank's share
     fl_step = flops_per_token_head(backward=w.backward) * th
     by_step = min_hbm_bytes_per_token_head(backward=w.backward) * th
     whole = {"tensor_frac_sustained": fl_step / (ms_step * 1e-3) / 1e12 / peaks["tf_sust"],
@@ -458,22 +604,39 @@ def main():
                "sample": f"token-recurrent float32 PyTorch {'forward+backward' if w.backward else 'forward'}, "
                          f"{reps} x (B=1 T=512 H=32 K=V=128), {spent:.1f} s"}
 
+    workloads = None
+    default_run = args.workload == "train_bf16" and not args.gate and not args.l2norm and args.scale_down == 1
+    if default_run and world == 1 and not args.no_workloads:
+        del devt, step
+        torch.cuda.empty_cache()
+        workloads = other_workloads(peaks, dev)
+        workloads["gpu_bar"] = gpu_bar(args.gpu_bar_deadline) if args.gpu_bar_deadline > 0 else {"unavailable": "skipped (--gpu-bar-deadline 0)"}
+        ours = {"train_bf16": ms_step, "prefill_bf16": workloads.get("prefill_bf16", {}).get("ms_per_step"),
+                "decode": workloads.get("decode", {}).get("ms_per_step")}
+        for n, rec in workloads["gpu_bar"].items():
+            if isinstance(rec, dict) and rec.get("ms_per_step") and ours.get(n):
+                rec["kda_b200_ms_per_step"] = ours[n]
+                rec["speedup_over_it"] = rec["ms_per_step"] / ours[n]
+
+    strong = world > 1 and not args.weak
     line = {
         "metric": METRIC if (args.workload == "train_bf16" and not args.gate and not args.l2norm) else
                   f"KDA {args.workload}{' +gate' if args.gate else ''}{' +l2norm' if args.l2norm else ''} tokens/s",
         "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"{args.workload} (B={B} T={T} H={H} K=V=128, chunk 64"
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak" if (args.weak and world > 1) else "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"{args.workload} (B={B * (world if strong else 1)} T={T} H={H} K=V=128, chunk 64"
                                f"{', fwd+bwd' if w.backward else ''}{', packed varlen' if cu is not None else ''}"
                                f"{', gate + beta sigmoid in kernel' if args.gate else ''}{', q/k l2norm in kernel' if args.l2norm else ''})",
-                   "per_gpu_batch": B, "l2": "inputs (>= 3 GB per step) far exceed the 126 MB L2; no flush needed",
-                   "seed": "rank"},
-        "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
+                   "per_gpu_batch": B, "sharding": ("batch rows over ranks, no collective on the data path" if strong else
+                                                    ("replicas" if world > 1 else "one GPU")),
+                   "l2": "inputs of a step far exceed the 126 MB L2; no flush needed",
+                   "seed": "one per batch row" if host_resident else "0 (drawn on the device)"},
+        "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks, "checks": checks,
         "roofline": roof, "step_roofline": whole, "kernels": kernels, "cpu_baseline": cpu,
     }
-    if gpu_bar is not None:
-        line["gpu_bar"] = gpu_bar
+    if workloads is not None:
+        line["workloads"] = workloads
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

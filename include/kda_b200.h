@@ -31,7 +31,7 @@ extern "C" {
 #pragma GCC visibility push(default) /* the entry points below are the library's only exports */
 #endif
 
-#define KDA_B200_ABI_VERSION 6
+#define KDA_B200_ABI_VERSION 7
 #define KDA_CHUNK 64 /* tokens per chunk of the chunked kernels */
 
 /* io_dtype of q, k, v, o and of their gradients */
@@ -45,8 +45,9 @@ extern "C" {
 #define KDA_E_DTYPE (-3)       /* unsupported io_dtype for this entry point */
 #define KDA_E_ALIGN (-4)       /* a pointer is not 16-byte aligned */
 #define KDA_E_WORKSPACE (-5)   /* workspace too small */
-#define KDA_E_DEVICE (-6)      /* the current device is not sm_100 */
+#define KDA_E_DEVICE (-6)      /* the current device is not sm_100 (compute capability 10.x) */
 #define KDA_E_LIMIT (-7)       /* size beyond a documented fixed maximum */
+#define KDA_E_TMAP (-8)        /* the driver refused to encode a TMA tensor map for one of the tensors */
 
 int kda_b200_abi_version(void);
 /* Text for a return code of this library (negative: argument error; positive: cudaGetErrorString). */
@@ -172,6 +173,22 @@ size_t kda_chunk_bwd_workspace_bytes(int64_t tokens, int32_t N, int32_t H, int32
 int kda_chunk_fwd(const kda_chunk_args* args, void* stream);
 int kda_chunk_bwd(const kda_chunk_args* args, void* stream);
 
+/* Status word of the chunked kernels (diagnostic; no counterpart in fla, whose Triton kernels have no bounded waits).
+ * Every device-side wait of these kernels (on a bulk copy or on a tensor-core product) polls a bounded number of
+ * times; a wait that runs out makes its CTA stop and sets a bit, and the outputs of that call are then incomplete.
+ * kda_chunk_fwd clears the word at its start and also reports an inconsistent cu_seqlens there; kda_chunk_bwd adds
+ * its bits to the word of the forward whose workspace it is given.  This call copies the word to *host_out; it waits
+ * for the device (cudaMemcpy), so it is a check to make after a step, not part of one.  workspace == NULL reads the
+ * word of the fixed array kda_chunk_fwd_noalloc uses on the current device.  0: nothing to report. */
+#define KDA_STATUS_SCAN_LOAD_WAIT 0x1u      /* forward scan: operand tiles of a chunk did not arrive */
+#define KDA_STATUS_SCAN_MMA_WAIT 0x2u       /* forward scan: a product did not complete */
+#define KDA_STATUS_BWD_SCAN_LOAD_WAIT 0x4u  /* reverse scan: operand tiles of a chunk did not arrive */
+#define KDA_STATUS_BWD_SCAN_MMA_WAIT 0x8u   /* reverse scan: a product did not complete */
+#define KDA_STATUS_BWD_MAIN_LOAD_WAIT 0x20u /* per-chunk backward: a tile's loads did not arrive */
+#define KDA_STATUS_BWD_MAIN_MMA_WAIT 0x40u  /* per-chunk backward: a product did not complete */
+#define KDA_STATUS_BAD_CU_SEQLENS 0x100u    /* cu_seqlens is not a non-decreasing sequence within [0, tokens]: nothing was computed */
+int kda_chunk_status(const void* workspace, uint32_t* host_out);
+
 /* ------------------------------------------------------------------------------------------------
  * Forward for callers that must not allocate.  It has no counterpart in the reference or in fla: their
  * host functions always allocate their intermediates with torch.empty.
@@ -192,7 +209,8 @@ int kda_chunk_bwd(const kda_chunk_args* args, void* stream);
  *    caches it; make that first call during start-up, before any stream capture begins;
  *  - all calls on a device share the one array: two calls that overlap on the GPU (different streams)
  *    race, so keep them on one stream or order them with events.  Nothing in the array has to start
- *    at zero: each call rewrites the tables, the status word and every tile it reads.
+ *    at zero: each call rewrites the tables, the status word and every tile it reads
+ *    (kda_chunk_status(NULL, ..) reads that status word).
  *  - it calls no cudaMalloc / cudaFree and no allocating library routine.
  * ------------------------------------------------------------------------------------------------ */
 #define KDA_NOALLOC_SCRATCH_BYTES (32u << 20)
@@ -272,11 +290,10 @@ int kda_copy_rows_async(void* dst, size_t dpitch, const void* src, size_t spitch
 #define KDA_STAGE_SCAN 2
 #define KDA_STAGE_BWD_SCAN 3
 #define KDA_STAGE_BWD_MAIN 4
-#define KDA_STAGE_BWD_FINISH 5 /* unused: the per-chunk backward is one kernel */
-#define KDA_STAGE_L2NORM 6
-#define KDA_STAGE_GATE_FWD 7
-#define KDA_STAGE_GATE_BWD 8
-#define KDA_NUM_STAGES 9
+#define KDA_STAGE_L2NORM 5
+#define KDA_STAGE_GATE_FWD 6
+#define KDA_STAGE_GATE_BWD 7
+#define KDA_NUM_STAGES 8
 int kda_b200_profile_enable(int on);
 int kda_b200_profile_read(float* stage_ms, int* stage_launches, int reset);
 

@@ -11,7 +11,7 @@ LIB_PATH = os.path.join(PKG, "libkda_b200.so")
 
 KDA_BF16, KDA_FP32 = 0, 1
 NOALLOC_SCRATCH_BYTES = 32 << 20
-ABI_VERSION = 6
+ABI_VERSION = 7
 
 
 class RecurrentArgs(C.Structure):
@@ -58,7 +58,7 @@ class GateArgs(C.Structure):
 EXPORTS = (
     "kda_b200_abi_version", "kda_b200_strerror", "kda_recurrent_fwd", "kda_recurrent_status",
     "kda_chunk_max_chunks", "kda_chunk_workspace_bytes", "kda_chunk_bwd_workspace_bytes",
-    "kda_chunk_fwd", "kda_chunk_bwd", "kda_chunk_fwd_noalloc", "kda_chunk_export_states",
+    "kda_chunk_fwd", "kda_chunk_bwd", "kda_chunk_status", "kda_chunk_fwd_noalloc", "kda_chunk_export_states",
     "kda_gate_bwd_workspace_bytes", "kda_gate_fwd", "kda_gate_bwd",
     "kda_copy_rows_async", "kda_b200_profile_enable", "kda_b200_profile_read",
 )
@@ -93,6 +93,8 @@ def load() -> C.CDLL:
         fn = getattr(lib, name)
         fn.restype = C.c_int
         fn.argtypes = [C.POINTER(ChunkArgs), C.c_void_p]
+    lib.kda_chunk_status.restype = C.c_int
+    lib.kda_chunk_status.argtypes = [C.c_void_p, C.POINTER(C.c_uint32)]
     lib.kda_chunk_export_states.restype = C.c_int
     lib.kda_chunk_export_states.argtypes = [C.c_void_p, C.c_size_t, C.c_int64, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]
     lib.kda_gate_bwd_workspace_bytes.restype = C.c_size_t
@@ -123,7 +125,7 @@ def check(code: int, what: str) -> None:
         raise KdaError(f"{what} failed with code {code}: {msg}")
 
 
-STAGES = ("tables", "prepare", "scan", "bwd_scan", "bwd_main", "bwd_finish", "l2norm", "gate_fwd", "gate_bwd")
+STAGES = ("tables", "prepare", "scan", "bwd_scan", "bwd_main", "l2norm", "gate_fwd", "gate_bwd")
 
 
 def profile_enable(on: bool) -> None:
@@ -135,6 +137,28 @@ def recurrent_status() -> int:
     v = C.c_uint32(0)
     check(load().kda_recurrent_status(C.byref(v)), "kda_recurrent_status")
     return int(v.value)
+
+
+STATUS_BITS = {0x1: "forward scan: operand tiles did not arrive", 0x2: "forward scan: a product did not complete",
+               0x4: "reverse scan: operand tiles did not arrive", 0x8: "reverse scan: a product did not complete",
+               0x20: "per-chunk backward: a tile's loads did not arrive", 0x40: "per-chunk backward: a product did not complete",
+               0x100: "cu_seqlens is inconsistent with the number of tokens: nothing was computed"}
+
+
+def chunk_status(workspace_ptr=None) -> int:
+    """Status word of the chunked kernels for the workspace at `workspace_ptr` (None: the fixed array of
+    kda_chunk_fwd_noalloc on the current device); 0 = nothing to report.  Synchronises with the device."""
+    v = C.c_uint32(0)
+    check(load().kda_chunk_status(C.c_void_p(workspace_ptr or 0), C.byref(v)), "kda_chunk_status")
+    return int(v.value)
+
+
+def check_chunk_status(workspace_ptr, what: str) -> None:
+    """Raises KdaError when the chunked kernels reported a problem for this workspace."""
+    v = chunk_status(workspace_ptr)
+    if v:
+        why = "; ".join(t for b, t in STATUS_BITS.items() if v & b) or "unknown bits"
+        raise KdaError(f"{what}: device status 0x{v:x} ({why}); the outputs of this call are incomplete")
 
 
 def profile_read(reset: bool = True) -> dict:

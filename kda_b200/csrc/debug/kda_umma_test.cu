@@ -1,6 +1,6 @@
-// Development check of the tcgen05 primitives in kda_umma.cuh: one CTA computes D[128 x N] = A[128 x 128] * B[N x 128]^T
+// Development check of the tcgen05 primitives in kda_umma.cuh (built into libkda_b200_debug.so, not into the product library): one CTA computes D[128 x N] = A[128 x 128] * B[N x 128]^T
 // with the operands placed in shared memory K-major or MN-major.  Reached through an exported debug entry
-// (not part of the public header); tests/test_umma_gpu.py compares it with a plain matrix product.
+// (not part of the public header, not in libkda_b200.so); tests/test_umma_gpu.py compares it with a plain matrix product.
 #include "kda_umma.cuh"
 
 namespace kda {
@@ -72,14 +72,14 @@ __global__ void __launch_bounds__(128, 1) umma_test_kernel(const __nv_bfloat16* 
 
 }  // namespace kda
 
-// D[M x N] (fp32) = A[M x 128] * B[n_off : n_off+N, 128]^T (optionally with B negated); M in {64, 128}, N in {16, 64, 128};
+// D[M x N] (fp32) = A[M x 128] * B[n_off : n_off+N, 128]^T (optionally with B negated); M in {64, 128}, N in {16, 32, 64, 128};
 // B has NB rows in shared memory and the instruction reads N of them starting at row n_off.
 // a_mn / b_mn select the shared-memory placement (0 = K-major, 1 = MN-major).  status: device word, nonzero if a
 // bounded wait gave up.
 extern "C" __attribute__((visibility("default"))) int kda_b200_debug_umma_gemm(const void* A, const void* B, float* D, int N, int a_mn,
                                                                                int b_mn, int neg_b, unsigned* status, void* stream, int M, int NB, int n_off) {
   if (!A || !B || !D || !status) return KDA_E_NULL;
-  if ((N != 16 && N != 64 && N != 128) || (M != 64 && M != 128) || NB < N + n_off || NB > 128) return KDA_E_SHAPE;
+  if ((N != 16 && N != 32 && N != 64 && N != 128) || (M != 64 && M != 128) || NB < N + n_off || NB > 128) return KDA_E_SHAPE;
   const int smem = 65536 + 64 + 1024;
   cudaError_t e = cudaFuncSetAttribute(kda::umma_test_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return static_cast<int>(e);

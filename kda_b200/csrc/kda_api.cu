@@ -13,8 +13,9 @@ extern "C" const char* kda_b200_strerror(int code) {
     case KDA_E_DTYPE: return "unsupported io_dtype for this entry point";
     case KDA_E_ALIGN: return "a pointer is not 16-byte aligned";
     case KDA_E_WORKSPACE: return "workspace too small";
-    case KDA_E_DEVICE: return "the current device is not sm_100";
+    case KDA_E_DEVICE: return "the current device is not sm_100 (compute capability 10.x)";
     case KDA_E_LIMIT: return "size beyond a documented fixed maximum";
+    case KDA_E_TMAP: return "the driver refused to encode a TMA tensor map";
     default: break;
   }
   if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));
@@ -114,7 +115,10 @@ extern "C" int kda_b200_profile_read(float* stage_ms, int* stage_launches, int r
   return KDA_OK;
 }
 
-// development aid (not part of the public header): device buffer of >= 64 long long for phase clocks
+#ifdef KDA_PHASE_CLOCKS
+// development aid, only in builds made with `python -m kda_b200.build --clocks` (not part of the public header): device
+// buffer of >= 64 long long for the phase clocks
 extern "C" __attribute__((visibility("default"))) void kda_b200_debug_clocks(void* device_buffer) {
   kda::g_dbg_clocks = static_cast<long long*>(device_buffer);
 }
+#endif

@@ -30,7 +30,7 @@ constexpr size_t TILE_GL = size_t(KD) * 4;        // 512 B
 struct ChunkWs {
   int* seq_chunk_off;   // [N+1] first chunk of each sequence; [N] = total chunks
   int* chunk_seq;       // [max_chunks] sequence of each chunk
-  unsigned* status;     // [4] device status word(s): nonzero = a bounded wait gave up
+  unsigned* status;     // [4] device status word (first bytes of the workspace): KDA_STATUS_* bits, 0 = nothing to report
   unsigned char *W, *UT, *KG, *QG, *AQK, *GL;          // always
   unsigned char *TI, *RKK, *HS, *VNEWT;                // save_for_backward only
   unsigned char *DH, *DVNEWT;                          // backward scratch (bf16 tiles)
@@ -52,9 +52,9 @@ inline ChunkWs carve_ws(unsigned char* base, unsigned char* bwd_base, int64_t to
   const size_t tiles = NTmax * static_cast<size_t>(H);
   size_t off = 0;
   auto take = [&](size_t bytes) { unsigned char* p = base ? base + off : nullptr; off += align_up(bytes); return p; };
+  w.status = reinterpret_cast<unsigned*>(take(16));      // first, so that its address does not depend on the sizes
   w.seq_chunk_off = reinterpret_cast<int*>(take(sizeof(int) * (static_cast<size_t>(N) + 1)));
   w.chunk_seq = reinterpret_cast<int*>(take(sizeof(int) * (NTmax + 1)));
-  w.status = reinterpret_cast<unsigned*>(take(16));
   w.W = take(tiles * TILE_TK);
   w.UT = take(tiles * TILE_VT);
   w.KG = take(tiles * TILE_TK);

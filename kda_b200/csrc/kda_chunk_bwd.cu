@@ -18,8 +18,6 @@
 //   dk- = dkg exp(G_last - G) + sum_t D[t,j] (scale dAqk[t,j] q_t + beta_t dAkk[t,j] k_t)   (k_j / Gam_j)
 //   dk = dk+ + dk-;   dG = q dq + k (dk+ - dk-);   dG_last += sum_j k_j dk_end_j + Gam_last sum_v h dh'
 //   dg = reverse cumsum of dG inside the chunk.
-#include <mutex>
-
 #include "kda_chunk.cuh"
 #include "kda_chunk_bwd.cuh"
 
@@ -83,16 +81,6 @@ static int main_grid(int max_chunks, int H) {
   return static_cast<int>(tiles < sms ? (tiles > 0 ? tiles : 1) : sms);
 }
 
-static std::once_flag g_battr_once;
-static cudaError_t g_battr_err = cudaSuccess;
-static cudaError_t set_bwd_attrs() {
-  std::call_once(g_battr_once, [] {
-    cudaError_t e = cudaSuccess;
-    g_battr_err = e;
-  });
-  return g_battr_err;
-}
-
 }  // namespace kda
 
 namespace kda {
@@ -146,8 +134,7 @@ extern "C" int kda_chunk_bwd(const kda_chunk_args* args, void* stream) {
   ChunkWs w = carve_ws(static_cast<unsigned char*>(a.workspace), static_cast<unsigned char*>(a.bwd_workspace), a.tokens, a.N,
                        a.H, true, l2, grp > 1, (a.save_for_backward & 2) != 0);
   if (a.workspace_bytes < w.fwd_bytes || a.bwd_workspace_bytes < w.bwd_bytes) return KDA_E_WORKSPACE;
-  cudaError_t e = set_bwd_attrs();
-  if (e != cudaSuccess) return static_cast<int>(e);
+  cudaError_t e = cudaSuccess;
   const int NTmax = static_cast<int>(a.tokens / C + a.N);
   const long long rows = static_cast<long long>(a.tokens) * HQ;      // rows of q and k
   const __nv_bfloat16* q = static_cast<const __nv_bfloat16*>(a.q);
@@ -169,8 +156,8 @@ extern "C" int kda_chunk_bwd(const kda_chunk_args* args, void* stream) {
   rp.DH = w.DH; rp.DVNEWT = w.DVNEWT;
   rp.d_o = static_cast<const __nv_bfloat16*>(a.d_o); rp.d_ht = a.d_ht; rp.dh0 = a.dh0; rp.status = w.status;
   rp.N = a.N; rp.H = a.H;
-  if (make_rows_tmap(&rp.tm_do, a.d_o, false, a.tokens, a.H, VD, 64, C, true)) return KDA_E_DEVICE;
-  if ((e = launch_bwd_scan_tc(rp, a.N * a.H, st)) != cudaSuccess) return static_cast<int>(e);
+  if (make_rows_tmap(&rp.tm_do, a.d_o, false, a.tokens, a.H, VD, 64, C, true)) return KDA_E_TMAP;
+  if ((rc = launch_bwd_scan_tc(rp, a.N * a.H, st)) != KDA_OK) return rc;
   prof_mark(prof, KDA_STAGE_BWD_SCAN, st);
 
   MainParams mp{};
@@ -186,12 +173,12 @@ extern "C" int kda_chunk_bwd(const kda_chunk_args* args, void* stream) {
       make_rows_tmap(&mp.tm_g, a.g, true, a.tokens, a.H, KD, KD, C, false) ||
       make_rows_tmap(&mp.tm_v, a.v, false, a.tokens, a.H, VD, 64, C, true) ||
       make_rows_tmap(&mp.tm_do, a.d_o, false, a.tokens, a.H, VD, 64, C, true))
-    return KDA_E_DEVICE;
+    return KDA_E_TMAP;
   mp.N = a.N; mp.H = a.H; mp.scale = a.scale; mp.grp = grp;
   // without grouped heads the normalisation's backward is applied by bwd_main's own epilogue
   const bool fused_l2 = l2 && grp == 1;
   mp.rstd = fused_l2 ? w.RSTD : nullptr; mp.qrows = rows;
-  if ((e = launch_bwd_main_tc(mp, main_grid(NTmax, a.H), st)) != cudaSuccess) return static_cast<int>(e);
+  if ((rc = launch_bwd_main_tc(mp, main_grid(NTmax, a.H), st)) != KDA_OK) return rc;
   if (grp > 1) {
     const long long pieces = rows * (KD / 8);
     kda_group_sum_kernel<<<static_cast<unsigned>((pieces + 255) / 256), 256, 0, st>>>(w.DQH, w.DKH, static_cast<__nv_bfloat16*>(a.dq),

@@ -39,9 +39,10 @@ struct RScanParams {
   alignas(64) CUtensorMap tm_do;   // 64-column boxes of dO in the 128-byte-swizzled operand layout
 };
 
-cudaError_t launch_bwd_scan_tc(const RScanParams& p, int blocks, cudaStream_t st);
+int launch_bwd_scan_tc(const RScanParams& p, int blocks, cudaStream_t st);
 
+// both return KDA_OK, a negative KDA_E_* or a positive cudaError_t
 // tcgen05 / TMEM version of the per-chunk backward kernel (kda_chunk_bwd_tc.cu)
-cudaError_t launch_bwd_main_tc(const MainParams& p, int grid, cudaStream_t st);
+int launch_bwd_main_tc(const MainParams& p, int grid, cudaStream_t st);
 
 }  // namespace kda

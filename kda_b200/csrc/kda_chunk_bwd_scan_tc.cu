@@ -9,9 +9,8 @@
 //   products 2   dhT += dO^T qg - dv_new^T w                                            (M=128 v, N=128 k, K=64 tokens)
 // dO arrives by TMA tiled loads (two boxes of 64 value columns, 128-byte swizzled) together with the W, QG, KG, AQK,
 // GL tiles of the chunk through a 2-stage mbarrier ring.
-#include <mutex>
-
 #include "kda_chunk_bwd.cuh"
+#include "kda_device.cuh"
 #include "kda_umma.cuh"
 
 namespace kda {
@@ -111,7 +110,7 @@ __global__ void __launch_bounds__(RNT, 1) kda_chunk_bwd_scan_tc_kernel(const __g
 
   uint32_t mph = 0;
   bool alive = true;
-  for (int i = 0; i < nchunks && alive; ++i) {
+  for (int i = 0; i < nchunks; ++i) {       // a failed wait leaves through the uniform vote at the top of the next iteration
     TcRScanStage& d = s.st[i & 1];
     const int c = c_end - 1 - i;
     const size_t tile = static_cast<size_t>(c) * p.H + h;
@@ -208,6 +207,7 @@ __global__ void __launch_bounds__(RNT, 1) kda_chunk_bwd_scan_tc_kernel(const __g
     if (tid == 0 && alive && i + 2 < nchunks) issue_load(i + 2);      // this stage's tiles are free again
   }
 
+  alive = __syncthreads_and(alive);      // uniform: either every thread writes dh0 or none does
   if (alive && p.dh0) {
     umma::fence_after_sync();
     const size_t sb = (static_cast<size_t>(seq) * p.H + h) * KD * VD;
@@ -226,16 +226,13 @@ __global__ void __launch_bounds__(RNT, 1) kda_chunk_bwd_scan_tc_kernel(const __g
   if (warp == 0) umma::tmem_dealloc(tb, 256);
 }
 
-cudaError_t launch_bwd_scan_tc(const RScanParams& p, int blocks, cudaStream_t st) {
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
+int launch_bwd_scan_tc(const RScanParams& p, int blocks, cudaStream_t st) {
+  static DeviceOnce once;
   const int smem = static_cast<int>(sizeof(TcRScanSmem)) + 1024;
-  std::call_once(once, [&] {
-    attr_err = cudaFuncSetAttribute(kda_chunk_bwd_scan_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-  });
-  if (attr_err != cudaSuccess) return attr_err;
+  const int rc = once.run([&] { return cudaFuncSetAttribute(kda_chunk_bwd_scan_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); });
+  if (rc != KDA_OK) return rc;
   kda_chunk_bwd_scan_tc_kernel<<<blocks, RNT, smem, st>>>(p);
-  return cudaGetLastError();
+  return static_cast<int>(cudaGetLastError());
 }
 
 }  // namespace kda

@@ -19,9 +19,8 @@
 //       Cn^T (reference = last row of j's block)                       (M=128 kk, N=16, K=16..48)
 //   D   per key column: diagonal blocks pairwise with running products of 2^(g), dG = q dq + k (dk+ - dk-),
 //       dg = reverse cumsum, final dq, dk, dg;  dbeta from  <Tm, dTm_raw> + <dAkk, raw kk>.
-#include <mutex>
-
 #include "kda_chunk_bwd.cuh"
+#include "kda_device.cuh"
 #include "kda_umma.cuh"
 
 namespace kda {
@@ -828,19 +827,18 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_bwd_main_tc_kernel(const __g
   if (warp == 0) umma::tmem_dealloc(tb, 512);
 }
 
-cudaError_t launch_bwd_main_tc(const MainParams& p, int grid, cudaStream_t st) {
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
+int launch_bwd_main_tc(const MainParams& p, int grid, cudaStream_t st) {
+  static DeviceOnce once;
   const int smem = static_cast<int>(sizeof(TcSmem)) + 1024;
-  std::call_once(once, [&] {
-    attr_err = cudaFuncSetAttribute(kda_chunk_bwd_main_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (attr_err == cudaSuccess)
-      attr_err = cudaFuncSetAttribute(kda_chunk_bwd_main_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  const int rc = once.run([&] {
+    cudaError_t e = cudaFuncSetAttribute(kda_chunk_bwd_main_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(kda_chunk_bwd_main_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    return e;
   });
-  if (attr_err != cudaSuccess) return attr_err;
+  if (rc != KDA_OK) return rc;
   if (p.rstd != nullptr && p.grp == 1) kda_chunk_bwd_main_tc_kernel<true><<<grid, NT, smem, st>>>(p);
   else kda_chunk_bwd_main_tc_kernel<false><<<grid, NT, smem, st>>>(p);
-  return cudaGetLastError();
+  return static_cast<int>(cudaGetLastError());
 }
 
 }  // namespace kda

@@ -10,6 +10,7 @@
 #include <mutex>
 
 #include "kda_chunk.cuh"
+#include "kda_device.cuh"
 #include "kda_scan.cuh"
 
 namespace kda {
@@ -17,24 +18,43 @@ namespace kda {
 // =================================================================================================
 // chunk tables
 // =================================================================================================
-__global__ void __launch_bounds__(1024) kda_chunk_tables_kernel(const int* __restrict__ cu, int N, int* __restrict__ seq_chunk_off,
-                                                                int* __restrict__ chunk_seq, unsigned* __restrict__ status) {
+// A cu_seqlens that does not describe `tokens` tokens (a negative first entry, a negative length, more tokens than the
+// tensors hold, or more chunks than the workspace was sized for) would send every later kernel past the end of the
+// workspace.  The tables kernel checks it on the device: it then sets KDA_STATUS_BAD_CU_SEQLENS in the status word
+// and writes empty tables (zero chunks for every sequence), so that prepare, the scans and the backward kernels do
+// nothing; no device->host synchronisation is needed for the check.
+__global__ void __launch_bounds__(1024) kda_chunk_tables_kernel(const int* __restrict__ cu, int N, long long tokens, int max_chunks,
+                                                                int* __restrict__ seq_chunk_off, int* __restrict__ chunk_seq,
+                                                                unsigned* __restrict__ status) {
   __shared__ int part[1024];
   const int tid = threadIdx.x;
   const int per = (N + 1023) / 1024;
   const int n0 = min(N, tid * per), n1 = min(N, n0 + per);
   int sum = 0;
+  bool bad = (tid == 0) && (cu[0] < 0 || static_cast<long long>(cu[N]) > tokens);
   for (int n = n0; n < n1; ++n) {
     const int len = cu[n + 1] - cu[n];
-    sum += (len > 0) ? (len + C - 1) / C : 0;
+    bad |= len < 0;
+    // a partial sum that would overflow is certainly beyond max_chunks; saturate instead of wrapping
+    const int nc = (len > 0) ? (len + C - 1) / C : 0;
+    sum = (sum > max_chunks || nc > max_chunks) ? max_chunks + 1 : sum + nc;
   }
   part[tid] = sum;
   __syncthreads();
-  for (int off = 1; off < 1024; off <<= 1) {   // inclusive Hillis-Steele scan
+  for (int off = 1; off < 1024; off <<= 1) {   // inclusive Hillis-Steele scan (saturating)
     int x = (tid >= off) ? part[tid - off] : 0;
     __syncthreads();
-    part[tid] += x;
+    const int y = part[tid] + x;
+    part[tid] = (y > max_chunks || y < 0) ? max_chunks + 1 : y;
     __syncthreads();
+  }
+  bad |= part[tid] > max_chunks;
+  bad = __syncthreads_or(bad) != 0;
+  if (tid < 4) status[tid] = (tid == 0 && bad) ? KDA_STATUS_BAD_CU_SEQLENS : 0u;
+  if (bad) {
+    for (int n = n0; n < n1; ++n) seq_chunk_off[n] = 0;
+    if (tid == 1023) seq_chunk_off[N] = 0;
+    return;
   }
   int run = part[tid] - sum;   // exclusive prefix
   for (int n = n0; n < n1; ++n) {
@@ -45,7 +65,6 @@ __global__ void __launch_bounds__(1024) kda_chunk_tables_kernel(const int* __res
     run += nc;
   }
   if (tid == 1023) seq_chunk_off[N] = part[1023];
-  if (tid < 4) status[tid] = 0u;
 }
 
 // =================================================================================================
@@ -612,19 +631,17 @@ __global__ void __launch_bounds__(256, 2) kda_chunk_prepare_kernel(const PrepPar
   }
 }
 
-static std::once_flag g_attr_once;
-static cudaError_t g_attr_err = cudaSuccess;
+static DeviceOnce g_prepare_once;
 
-static cudaError_t set_attrs() {
-  std::call_once(g_attr_once, [] {
+static int set_attrs() {      // KDA_OK, a negative KDA_E_* or a positive cudaError_t
+  return g_prepare_once.run([] {
     cudaError_t e = cudaSuccess;
     for (auto fn : {kda_chunk_prepare_kernel<false>, kda_chunk_prepare_kernel<true>}) {
       if (e == cudaSuccess) e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(PrepSmem)));
       if (e == cudaSuccess) e = cudaFuncSetAttribute(fn, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     }
-    g_attr_err = e;
+    return e;
   });
-  return g_attr_err;
 }
 
 int validate_chunk_args(const kda_chunk_args& a, bool backward);
@@ -681,12 +698,13 @@ extern "C" int kda_chunk_fwd(const kda_chunk_args* args, void* stream) {
   ChunkWs w = carve_ws(static_cast<unsigned char*>(a.workspace), nullptr, a.tokens, a.N, a.H, save, true, false,
                        (a.save_for_backward & 2) != 0);
   if (a.workspace_bytes < w.fwd_bytes) return KDA_E_WORKSPACE;
-  cudaError_t e = set_attrs();
-  if (e != cudaSuccess) return static_cast<int>(e);
+  rc = set_attrs();
+  if (rc != KDA_OK) return rc;
+  cudaError_t e = cudaSuccess;
   const int NTmax = static_cast<int>(a.tokens / C + a.N);
 
   ProfCall* prof = prof_begin(st);
-  kda_chunk_tables_kernel<<<1, 1024, 0, st>>>(a.cu_seqlens, a.N, w.seq_chunk_off, w.chunk_seq, w.status);
+  kda_chunk_tables_kernel<<<1, 1024, 0, st>>>(a.cu_seqlens, a.N, a.tokens, NTmax, w.seq_chunk_off, w.chunk_seq, w.status);
   if ((e = cudaGetLastError()) != cudaSuccess) return static_cast<int>(e);
   prof_mark(prof, KDA_STAGE_TABLES, st);
 
@@ -712,7 +730,7 @@ extern "C" int kda_chunk_fwd(const kda_chunk_args* args, void* stream) {
   sp.HS = save ? w.HS : nullptr; sp.VNEWT = save ? w.VNEWT : nullptr;
   sp.h0 = a.h0; sp.ht = a.ht; sp.o = static_cast<__nv_bfloat16*>(a.o); sp.status = w.status;
   sp.N = a.N; sp.H = a.H;
-  if ((e = launch_scan_tc(sp, a.N * a.H, st)) != cudaSuccess) return static_cast<int>(e);
+  if ((rc = launch_scan_tc(sp, a.N * a.H, st)) != KDA_OK) return rc;
   prof_mark(prof, KDA_STAGE_SCAN, st);
   return KDA_OK;
 }
@@ -725,7 +743,7 @@ extern "C" int kda_chunk_fwd(const kda_chunk_args* args, void* stream) {
 static __device__ __align__(256) unsigned char g_noalloc_scratch[KDA_NOALLOC_SCRATCH_BYTES];
 
 namespace {
-constexpr int kMaxDevices = 64;
+constexpr int kMaxDevices = kda::kMaxDeviceOrdinals;
 std::mutex g_noalloc_mu;
 unsigned char* g_noalloc_addr[kMaxDevices] = {};   // device address of g_noalloc_scratch, per device ordinal
 }  // namespace
@@ -763,4 +781,26 @@ extern "C" int kda_chunk_fwd_noalloc(const kda_chunk_args* args, void* stream) {
   a.bwd_workspace = nullptr;
   a.bwd_workspace_bytes = 0;
   return kda_chunk_fwd(&a, stream);
+}
+
+// Status word of the chunked kernels (see the header): copies it to the host, which waits for the device.
+extern "C" int kda_chunk_status(const void* workspace, uint32_t* host_out) {
+  if (!host_out) return KDA_E_NULL;
+  *host_out = 0;
+  const unsigned char* base = static_cast<const unsigned char*>(workspace);
+  if (!base) {      // the array kda_chunk_fwd_noalloc uses on the current device; never used there: nothing to report
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (dev < 0 || dev >= kMaxDevices) return KDA_E_LIMIT;
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
+    base = g_noalloc_addr[dev];
+    if (!base) return KDA_OK;
+  }
+  const kda::ChunkWs w = kda::carve_ws(const_cast<unsigned char*>(base), nullptr, 0, 0, 1, false);
+  unsigned v = 0;
+  const cudaError_t e = cudaMemcpy(&v, w.status, sizeof(v), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  *host_out = v;
+  return KDA_OK;
 }

@@ -10,9 +10,8 @@
 //   products 2   hT += v_new^T kg,   o^T += v_new^T Aqk^T                              (K = 64 tokens)
 //   epilogue 2   o^T -> bf16 -> staged in shared memory -> coalesced stores of o[t][v].
 // Operand tiles (W, QG, KG, AQK, UT, GL of the chunk) arrive through a 2-stage TMA bulk-copy / mbarrier ring.
-#include <mutex>
-
 #include "kda_chunk.cuh"
+#include "kda_device.cuh"
 #include "kda_scan.cuh"
 #include "kda_umma.cuh"
 
@@ -287,16 +286,13 @@ __global__ void __launch_bounds__(SNT, 1) kda_chunk_scan_tc_kernel(const ScanPar
   if (warp == 0) umma::tmem_dealloc(tb, 512);
 }
 
-cudaError_t launch_scan_tc(const ScanParams& p, int blocks, cudaStream_t st) {
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
+int launch_scan_tc(const ScanParams& p, int blocks, cudaStream_t st) {
+  static DeviceOnce once;
   const int smem = static_cast<int>(sizeof(TcScanSmem)) + 1024;
-  std::call_once(once, [&] {
-    attr_err = cudaFuncSetAttribute(kda_chunk_scan_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-  });
-  if (attr_err != cudaSuccess) return attr_err;
+  const int rc = once.run([&] { return cudaFuncSetAttribute(kda_chunk_scan_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); });
+  if (rc != KDA_OK) return rc;
   kda_chunk_scan_tc_kernel<<<blocks, SNT, smem, st>>>(p);
-  return cudaGetLastError();
+  return static_cast<int>(cudaGetLastError());
 }
 
 }  // namespace kda

@@ -112,10 +112,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
       : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
   return ok != 0;
 }
-// Waits for the phase with the given parity.  Gives up after a bounded number of polls (about a second)
-// and returns false; the caller then records an error and leaves its loop instead of spinning forever.
+// Waits for the phase with the given parity.  Gives up after a bounded number of polls and returns false; the
+// caller then records an error and leaves its loop instead of spinning forever.  One poll (a try_wait that the
+// hardware suspends for a short while, plus the sleep) takes about 4 microseconds on B200, so 2^18 polls are
+// about one second -- four orders of magnitude above the longest wait of a healthy run.
+constexpr unsigned MBAR_WAIT_POLLS = 1u << 18;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity) {
-  for (unsigned i = 0; i < (1u << 22); ++i) {
+  for (unsigned i = 0; i < MBAR_WAIT_POLLS; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if (i > 64) __nanosleep(64);
   }

@@ -9,6 +9,7 @@
 #include <mutex>
 
 #include "kda_common.cuh"
+#include "kda_device.cuh"
 
 namespace kda {
 
@@ -299,12 +300,11 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) kda_decode_bulk_kernel(const k
 template <typename IO, bool TR, bool GATE>
 int launch(const kda_recurrent_args& a, cudaStream_t st) {
   const int smem = static_cast<int>(sizeof(DecSmem)) + 128;
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [&] {
-    attr_err = cudaFuncSetAttribute(kda_decode_bulk_kernel<IO, TR, GATE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  static DeviceOnce once;      // per template variant, per device
+  const int rc = once.run([&] {
+    return cudaFuncSetAttribute(kda_decode_bulk_kernel<IO, TR, GATE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   });
-  if (attr_err != cudaSuccess) return static_cast<int>(attr_err);
+  if (rc != KDA_OK) return rc;
   int dev = 0, sms = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);

@@ -17,7 +17,7 @@ struct ScanParams {
   int N, H;
 };
 
-// tcgen05 / TMEM version (kda_chunk_scan_tc.cu)
-cudaError_t launch_scan_tc(const ScanParams& p, int blocks, cudaStream_t st);
+// tcgen05 / TMEM version (kda_chunk_scan_tc.cu); returns KDA_OK, a negative KDA_E_* or a positive cudaError_t
+int launch_scan_tc(const ScanParams& p, int blocks, cudaStream_t st);
 
 }  // namespace kda

@@ -58,45 +58,51 @@ def cu_seqlens_from_lengths(lengths) -> torch.Tensor:
 
 
 def make_inputs(B, T, H, K, V, dtype=torch.bfloat16, seed=0, h0_std=0.0, n_states=None,
-                backward=False, device="cpu"):
-    """Returns a dict with q,k,v,g,beta,(h0),(do,dht).  q/k/v/do in `dtype`; g, beta, h0, dht fp32."""
-    gen = torch.Generator().manual_seed(seed)
-    q = torch.randn(B, T, H, K, generator=gen)
-    k = torch.randn(B, T, H, K, generator=gen)
-    q = q / q.norm(dim=-1, keepdim=True)
-    k = k / k.norm(dim=-1, keepdim=True)
-    v = torch.randn(B, T, H, V, generator=gen)
-    beta = torch.sigmoid(torch.randn(B, T, H, generator=gen))
-    a = torch.log(1.0 + 15.0 * torch.rand(H, generator=gen))            # a_h = log U(1,16)
-    x = torch.randn(B, T, H, K, generator=gen)
-    g = -torch.exp(a).view(1, 1, H, 1) * torch.nn.functional.softplus(x)
-    out = dict(q=q.to(dtype), k=k.to(dtype), v=v.to(dtype), g=g.float(), beta=beta.float())
+                backward=False, device="cpu", generate_on_device=False):
+    """Returns a dict with q,k,v,g,beta,(h0),(do,dht).  q/k/v/do in `dtype`; g, beta, h0, dht fp32.
+
+    By default the values come from a CPU generator (the same tensors on every machine) and are then moved to
+    `device`.  `generate_on_device=True` draws them on `device` from that device's own seeded generator instead:
+    the same distributions, a different (still seeded) stream -- for the largest workloads, whose float32
+    staging tensors would need tens of GB of host memory and minutes of CPU time."""
+    gdev = device if generate_on_device else "cpu"
+    gen = torch.Generator(device=gdev).manual_seed(seed)
+    rn = lambda *shape: torch.randn(*shape, generator=gen, device=gdev)      # noqa: E731
+    q = rn(B, T, H, K)
+    q = (q / q.norm(dim=-1, keepdim=True)).to(dtype)
+    k = rn(B, T, H, K)
+    k = (k / k.norm(dim=-1, keepdim=True)).to(dtype)
+    v = rn(B, T, H, V).to(dtype)
+    beta = torch.sigmoid(rn(B, T, H))
+    a = torch.log(1.0 + 15.0 * torch.rand(H, generator=gen, device=gdev))            # a_h = log U(1,16)
+    g = -torch.exp(a).view(1, 1, H, 1) * torch.nn.functional.softplus(rn(B, T, H, K))
+    out = dict(q=q, k=k, v=v, g=g.float(), beta=beta.float())
     N = B if n_states is None else n_states
     if h0_std > 0:
-        out["h0"] = (torch.randn(N, H, K, V, generator=gen) * h0_std).float()
+        out["h0"] = (rn(N, H, K, V) * h0_std).float()
     else:
         out["h0"] = None
     if backward:
-        out["do"] = torch.randn(B, T, H, V, generator=gen).to(dtype)
-        out["dht"] = (torch.randn(N, H, K, V, generator=gen) * 0.01).float()
-    if device != "cpu":
+        out["do"] = rn(B, T, H, V).to(dtype)
+        out["dht"] = (rn(N, H, K, V) * 0.01).float()
+    if device != "cpu" and not generate_on_device:
         out = {n: (t.to(device) if t is not None else None) for n, t in out.items()}
     return out
 
 
-def make_workload(name: str, seed: int = 0, device="cpu", scale_down: int = 1):
+def make_workload(name: str, seed: int = 0, device="cpu", scale_down: int = 1, generate_on_device=False):
     """Inputs of a named workload.  `scale_down` divides B (or the number of packed sequences) to
-    make a smaller case with the same per-sequence shape."""
+    make a smaller case with the same per-sequence shape.  The packed lengths always come from the CPU generator."""
     w = WORKLOADS[name]
     if w.n_seqs:
         lengths = varlen_lengths(max(1, w.n_seqs // scale_down), w.min_len, w.max_len, seed)
         cu = cu_seqlens_from_lengths(lengths)
         d = make_inputs(1, int(cu[-1]), w.H, w.K, w.V, w.dtype, seed, w.h0_std, n_states=len(lengths),
-                        backward=w.backward, device=device)
+                        backward=w.backward, device=device, generate_on_device=generate_on_device)
         d["cu_seqlens"] = cu.to(device) if device != "cpu" else cu
         return d
     d = make_inputs(max(1, w.B // scale_down), w.T, w.H, w.K, w.V, w.dtype, seed, w.h0_std,
-                    backward=w.backward, device=device)
+                    backward=w.backward, device=device, generate_on_device=generate_on_device)
     d["cu_seqlens"] = None
     return d
 

@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import ctypes as C
 import math
+import os
 
 import torch
 
@@ -17,6 +18,14 @@ from . import _lib
 
 _DT = {torch.bfloat16: _lib.KDA_BF16, torch.float32: _lib.KDA_FP32}
 CHUNK = 64
+
+
+def _checked() -> bool:
+    """KDA_B200_CHECK=1: after every operator call read the kernels' device status words (bounded waits that gave
+    up, an inconsistent cu_seqlens) and raise if one is set.  Each read waits for the device, so this is a
+    debugging / validation mode; without it a serving loop reads `_lib.chunk_status` / `_lib.recurrent_status`
+    itself at a point where it synchronises anyway."""
+    return os.environ.get("KDA_B200_CHECK", "0") not in ("", "0")
 
 
 def _ptr(t):
@@ -298,6 +307,10 @@ def fused_recurrent_kda_fwd(q, k, v, g, beta, A_log=None, dt_bias=None, initial_
         HQ=q.shape[2], **gate_kw)
     with torch.cuda.device(dev):
         _lib.check(_lib.load().kda_recurrent_fwd(C.byref(args), _stream(dev)), "kda_recurrent_fwd")
+        if _checked():
+            st = _lib.recurrent_status()
+            if st:
+                raise _lib.KdaError(f"kda_recurrent_fwd: device status 0x{st:x} (a bounded wait gave up); the outputs are incomplete")
     return o, ht
 
 
@@ -370,6 +383,8 @@ class ChunkKDAFunction(torch.autograd.Function):
         args = _chunk_args(q, k, v, g32, beta32, h0, cu, o, ht, ws, N, H, K, V, tokens, use_l2norm, save, scale)
         with torch.cuda.device(dev):
             _lib.check(lib.kda_chunk_fwd(C.byref(args), _stream(dev)), "kda_chunk_fwd")
+            if _checked():
+                _lib.check_chunk_status(ws.data_ptr(), "kda_chunk_fwd")
         if need_grad:
             ctx.save_for_backward(q, k, v, g32, beta32, h0, cu, ws)
             ctx.meta = (N, H, K, V, tokens, use_l2norm, scale, g.dtype, beta.dtype, initial_state is not None, HQ)
@@ -393,6 +408,8 @@ class ChunkKDAFunction(torch.autograd.Function):
                            d_o=do, d_ht=dht, dq=dq, dk=dk, dv=dv, dg=dg, dbeta=dbeta, dh0=dh0, bwd_ws=bws)
         with torch.cuda.device(dev):
             _lib.check(lib.kda_chunk_bwd(C.byref(args), _stream(dev)), "kda_chunk_bwd")
+            if _checked():
+                _lib.check_chunk_status(ws.data_ptr(), "kda_chunk_bwd")
         return dq, dk, dv, dg.to(g_dtype), dbeta.to(beta_dtype), None, dh0, None, None, None
 
 
@@ -423,6 +440,8 @@ def _chunk_fwd_with_states(q, k, v, g, beta, scale, initial_state, output_final_
     with torch.cuda.device(dev):
         _lib.check(lib.kda_chunk_fwd(C.byref(args), _stream(dev)), "kda_chunk_fwd")
         _lib.check(lib.kda_chunk_export_states(_ptr(ws), ws.numel(), tokens, N, H, _ptr(hbuf), _stream(dev)), "kda_chunk_export_states")
+        if _checked():
+            _lib.check_chunk_status(ws.data_ptr(), "kda_chunk_fwd")
     nt = nt_shape[0] * nt_shape[1]
     return o, ht, hbuf[:nt].view(nt_shape[0], nt_shape[1], H, K, V)
 

@@ -17,6 +17,21 @@ def batch_slice(B: int, rank: int, world: int) -> slice:
     return slice(start, start + base + (1 if rank < rem else 0))
 
 
+def batch_head_block(B: int, H: int, rank: int, world: int) -> tuple[int, int, int, int]:
+    """Contiguous block of the B*H flattened (batch, head) units for `rank`, as (b0, b1, h0, h1): whole batch rows
+    while there are at least as many rows as ranks, otherwise a head range of one row (world must then be a multiple
+    of B and H a multiple of world // B), so that every rank's slice stays a dense sub-tensor."""
+    if world <= B:
+        sl = batch_slice(B, rank, world)
+        return sl.start, sl.stop, 0, H
+    if world % B or H % (world // B):
+        raise ValueError(f"cannot cut {B} x {H} (batch, head) units into {world} dense blocks")
+    per = world // B
+    hs = H // per
+    b, j = divmod(rank, per)
+    return b, b + 1, j * hs, (j + 1) * hs
+
+
 def balance_sequences(lengths, world: int) -> list[list[int]]:
     """Longest-processing-time assignment of whole sequences to ranks; returns per-rank sequence ids
     (each list in ascending id order so that a rank's packed tensor keeps the original order)."""

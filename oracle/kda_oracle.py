@@ -133,6 +133,14 @@ def cosine(x: torch.Tensor, ref: torch.Tensor) -> float:
     return float((x @ ref).item() / (nx * nr))
 
 
+def assert_bf16_parity(x: torch.Tensor, ref: torch.Tensor, name: str = "", rel: float = 2e-2, cos: float = 0.9999) -> None:
+    """The bf16-mode bar, read both ways: max|x - ref| / max|ref| <= rel AND ||x - ref||_2 / ||ref||_2 <= rel, and
+    cosine >= cos; every value finite."""
+    assert torch.isfinite(x.detach().float()).all(), f"{name}: non-finite values"
+    e_max, e_l2, c = max_norm_err(x, ref), rel_l2_err(x, ref), cosine(x, ref)
+    assert e_max <= rel and e_l2 <= rel and c >= cos, f"{name}: max-normalised {e_max:.3e}, relative L2 {e_l2:.3e}, cosine {c:.6f}"
+
+
 # ---- gate front end -------------------------------------------------------------------------------------
 def kda_gate(g_raw, A_log, dt_bias=None, lower_bound=None, dtype=torch.float64):
     """Decay activation in front of the operator, differentiable, in `dtype`.

@@ -24,6 +24,16 @@ def test_exports_every_declared_symbol(lib):
         assert hasattr(lib, n), n
 
 
+def test_exports_nothing_but_the_declared_symbols(lib):
+    """The header says its entries are the library's only exports: development checks live in libkda_b200_debug.so."""
+    import subprocess
+    import __graft_entry__ as ge
+    from kda_b200 import _lib
+    out = subprocess.run(["nm", "-D", "--defined-only", _lib.LIB_PATH], capture_output=True, text=True, check=True).stdout
+    exported = {ln.split()[-1] for ln in out.splitlines() if " T " in ln}
+    assert exported == set(ge.declared_symbols()) == set(_lib.EXPORTS)
+
+
 def test_version_and_error_text(lib):
     import re
     from kda_b200 import _lib
@@ -32,6 +42,8 @@ def test_version_and_error_text(lib):
     assert lib.kda_b200_strerror(0) == b"ok"
     assert b"NULL" in lib.kda_b200_strerror(-1)
     assert b"workspace" in lib.kda_b200_strerror(-5)
+    assert b"tensor map" in lib.kda_b200_strerror(-8)
+    assert lib.kda_chunk_status(None, None) == -1
 
 
 def test_workspace_sizes_are_monotone(lib):

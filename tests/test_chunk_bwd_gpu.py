@@ -1,11 +1,11 @@
 """GPU parity of the bf16 chunked backward against float64 autograd through the token-by-token oracle
-(bf16 mode: max-normalised error <= 2e-2 and cosine >= 0.9999 for every gradient)."""
+(bf16 mode: max-normalised error and relative L2 error <= 2e-2 and cosine >= 0.9999 for every gradient)."""
 import numpy as np
 import pytest
 import torch
 
 from kda_b200.inputs import make_inputs
-from oracle.kda_oracle import cosine, max_norm_err, recurrent_kda_grads
+from oracle.kda_oracle import assert_bf16_parity, recurrent_kda_grads
 
 pytestmark = pytest.mark.gpu
 REL, COS = 2e-2, 0.9999
@@ -25,15 +25,9 @@ def run_gpu(d, cu=None, scale=None, l2=False, with_h0=True):
 
 
 def check(got, ref, names=NAMES):
-    bad = []
     for n in names:
-        if ref[n] is None:
-            continue
-        assert torch.isfinite(got[n].float()).all(), n
-        e, c = max_norm_err(got[n], ref[n]), cosine(got[n], ref[n])
-        if e > REL or c < COS:
-            bad.append((n, e, c))
-    assert not bad, bad
+        if ref[n] is not None:
+            assert_bf16_parity(got[n], ref[n], n, REL, COS)      # max-normalised AND relative L2 <= 2e-2, cosine >= 0.9999
 
 
 @pytest.mark.parametrize("T", [1, 63, 64, 65, 130, 256])
@@ -88,3 +82,26 @@ def test_chunk_bwd_deterministic():
     a, b = run_gpu(d), run_gpu(d)
     for n in NAMES:
         assert torch.equal(a[n], b[n]), n
+
+
+@pytest.mark.parametrize("l2", [False, True])
+def test_chunk_bwd_persistent_tile_walk(l2):
+    """B=48 T=130 H=4: 576 (chunk, head) tiles with ragged tails, more than three per SM, so every persistent CTA of the
+    per-chunk backward walks several tiles (next-tile prefetch, the alternating chunk-info slots, barrier phase flips,
+    re-use of the dq / dk staging tiles).  Every batch row must equal, bit for bit, the same row run alone (fewer tiles
+    than SMs: no CTA takes a second tile there), and one row must match float64 autograd; with and without the fused
+    L2-normalisation epilogue."""
+    B, T, H = 48, 130, 4
+    d = make_inputs(B, T, H, 128, 128, torch.bfloat16, seed=36, h0_std=0.02, backward=True)
+    if l2:
+        d["q"], d["k"] = (d["q"].float() * 1.7).bfloat16(), (d["k"].float() * 0.6).bfloat16()
+    got = run_gpu(d, l2=l2)
+    for b in (0, 17, 47):
+        di = {n: d[n][b:b + 1] for n in d}
+        gi = run_gpu(di, l2=l2)
+        for n in NAMES:
+            assert torch.equal(gi[n], got[n][b:b + 1]), (n, b)
+    b = 31
+    ref = recurrent_kda_grads(*(d[n][b:b + 1] for n in ("q", "k", "v", "g", "beta", "do", "dht")), initial_state=d["h0"][b:b + 1],
+                              use_qk_l2norm=l2)
+    check({n: got[n][b:b + 1] for n in NAMES}, ref)

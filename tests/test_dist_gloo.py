@@ -72,3 +72,51 @@ def test_balance_is_a_partition_and_deterministic():
     assert a == balance_sequences(lengths, 8)
     loads = [sum(lengths[i] for i in o) for o in a]
     assert max(loads) - min(loads) <= max(lengths)
+
+
+def test_batch_head_blocks_partition_the_units():
+    from kda_b200.shard import batch_head_block
+    for B, H in ((8, 32), (4, 32), (1, 32)):
+        for world in (1, 2, 4, 8):
+            if world > B and (world % B or H % (world // B)):
+                continue
+            seen = set()
+            for r in range(world):
+                b0, b1, h0, h1 = batch_head_block(B, H, r, world)
+                block = {(b, h) for b in range(b0, b1) for h in range(h0, h1)}
+                assert block and not (block & seen)
+                seen |= block
+            assert len(seen) == B * H
+    assert batch_head_block(4, 32, 5, 8) == (2, 3, 16, 32)          # two ranks per batch row: the second takes heads 16..31
+
+
+def _bench_shard_worker(rank, world, port, ret):
+    """The benchmark's own sharding of the headline workload (bench.shard_inputs), shrunk: the union of the ranks' batch
+    rows is the batch a single rank would generate, row for row."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import argparse
+    import dataclasses
+    import bench
+    from kda_b200.inputs import WORKLOADS
+    w = dataclasses.replace(WORKLOADS["train_bf16"], B=4, T=16, H=2)
+    args = argparse.Namespace(workload="train_bf16", weak=False, scale_down=1)
+    mine, cu, job_tokens = bench.shard_inputs(args, w, rank, world, None)
+    whole, _, _ = bench.shard_inputs(args, w, 0, 1, None)
+    sl = batch_slice(4, rank, world)
+    ok = all(torch.equal(mine[n], whole[n][sl]) for n in mine) and cu is None and job_tokens == 4 * 16
+    flags = [torch.zeros(1) for _ in range(world)]
+    dist.all_gather(flags, torch.tensor([1.0 if ok else 0.0]))
+    if rank == 0:
+        ret["ok"] = [bool(f.item()) for f in flags]
+        ret["rows"] = mine["q"].shape[0]
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_bench_shards_the_headline_batch_over_two_ranks():
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_bench_shard_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
+    assert ret["ok"] == [True, True] and ret["rows"] == 2

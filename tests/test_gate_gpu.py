@@ -7,7 +7,7 @@ import pytest
 import torch
 
 from kda_b200.inputs import make_inputs
-from oracle.kda_oracle import beta_sigmoid, cosine, kda_gate, max_norm_err, recurrent_kda
+from oracle.kda_oracle import beta_sigmoid, cosine, kda_gate, max_norm_err, recurrent_kda, rel_l2_err
 
 pytestmark = pytest.mark.gpu
 
@@ -115,10 +115,10 @@ def test_chunk_kda_with_gate_in_kernel(lb, raw_dtype):
         got = {"o": o.detach(), "ht": ht.detach()}.get(n)
         if got is None:
             got = lc[n[1:]].grad
-        e, c = max_norm_err(got, r), cosine(got, r)
+        e, e2, c = max_norm_err(got, r), rel_l2_err(got, r), cosine(got, r)
         rel, cos = (5e-2, 0.999) if n in ("dA_log", "ddt_bias") else (2e-2, 0.9999)
-        if e > rel or c < cos:
-            bad.append((n, e, c))
+        if e > rel or e2 > rel or c < cos:
+            bad.append((n, e, e2, c))
     assert not bad, bad
 
 

@@ -5,7 +5,7 @@ import pytest
 import torch
 
 from kda_b200.inputs import make_inputs
-from oracle.kda_oracle import cosine, max_norm_err, recurrent_kda
+from oracle.kda_oracle import assert_bf16_parity, max_norm_err, recurrent_kda
 
 pytestmark = pytest.mark.gpu
 NAMES = ("q", "k", "v", "g", "beta", "h0")
@@ -35,13 +35,9 @@ def _gpu(d, cu=None, l2=False):
 
 
 def _check(got, ref):
-    bad = []
     for n, r in ref.items():
         assert got[n].shape == r.shape, (n, got[n].shape, r.shape)
-        e, c = max_norm_err(got[n], r), cosine(got[n], r)
-        if e > 2e-2 or c < 0.9999:
-            bad.append((n, e, c))
-    assert not bad, bad
+        assert_bf16_parity(got[n], r, n)      # max-normalised AND relative L2 <= 2e-2, cosine >= 0.9999
 
 
 @pytest.mark.parametrize("H,HV,l2", [(2, 4, False), (1, 4, True), (2, 6, False)])

@@ -123,6 +123,7 @@ def test_large_decode_batch_bulk_copy_kernel(case):
     assert max_norm_err(ht, h_ref) <= 1e-4
 
 
+@pytest.mark.captures_graph
 @pytest.mark.parametrize("N", [4, 40])
 def test_decode_step_replays_from_a_cuda_graph(N):
     """Serving loops capture the decode step in a CUDA graph: the C entry point makes no synchronising call and takes the

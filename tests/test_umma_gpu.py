@@ -15,13 +15,14 @@ CASES = [  # M, N, NB (rows of B in shared memory), n_off, a_mn, b_mn, neg_b
     (64, 64, 64, 0, 0, 0, 0), (64, 64, 64, 0, 1, 1, 0), (64, 128, 128, 0, 1, 0, 0),
     (128, 16, 64, 16, 1, 0, 0), (128, 16, 64, 48, 1, 0, 0), (128, 16, 64, 32, 1, 1, 0), (128, 16, 64, 0, 0, 1, 0),
     (64, 16, 64, 16, 0, 0, 0),
+    (128, 32, 64, 0, 0, 1, 0), (128, 32, 64, 32, 1, 1, 0), (64, 32, 64, 0, 0, 1, 0), (128, 32, 64, 16, 1, 0, 0),
 ]
 
 
 @pytest.mark.parametrize("M,N,NB,n_off,a_mn,b_mn,neg_b", CASES)
 def test_umma_gemm(M, N, NB, n_off, a_mn, b_mn, neg_b):
-    from kda_b200 import _lib
-    lib = _lib.load()
+    from kda_b200 import build
+    lib = C.CDLL(build.DEBUG_LIB)          # development checks live in their own library, not in libkda_b200.so
     fn = lib.kda_b200_debug_umma_gemm
     fn.restype = C.c_int
     fn.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p,

@@ -50,6 +50,7 @@ def test_noalloc_matches_regular_entry_point_twice():
         assert torch.isfinite(o2.float()).all() and torch.isfinite(h2).all()
         assert torch.equal(o1, o2), call
         assert torch.equal(h1, h2), call
+        assert _lib.chunk_status(None) == 0 and _lib.chunk_status(ws.data_ptr()) == 0      # no bounded wait gave up
         del o1, h1, o2, h2, ws, d      # so that the next round's allocator bookkeeping starts clean
 
 
