@@ -40,7 +40,7 @@ class ChunkArgs(C.Structure):
         ("bwd_workspace", C.c_void_p), ("bwd_workspace_bytes", C.c_size_t),
         ("tokens", C.c_int64), ("N", C.c_int32), ("H", C.c_int32), ("K", C.c_int32), ("V", C.c_int32),
         ("io_dtype", C.c_int32), ("use_qk_l2norm", C.c_int32), ("save_for_backward", C.c_int32),
-        ("scale", C.c_float), ("HQ", C.c_int32),
+        ("scale", C.c_float), ("HQ", C.c_int32), ("scan_slices", C.c_int32),
     ]
 
 

@@ -20,6 +20,7 @@
 //   dg = reverse cumsum of dG inside the chunk.
 #include "kda_chunk.cuh"
 #include "kda_chunk_bwd.cuh"
+#include "kda_scan.cuh"
 
 namespace kda {
 
@@ -154,10 +155,11 @@ extern "C" int kda_chunk_bwd(const kda_chunk_args* args, void* stream) {
   rp.cu = a.cu_seqlens; rp.seq_chunk_off = w.seq_chunk_off; rp.chunk_seq = w.chunk_seq;
   rp.W = w.W; rp.KG = w.KG; rp.QG = w.QG; rp.AQK = w.AQK; rp.GL = w.GL;
   rp.DH = w.DH; rp.DVNEWT = w.DVNEWT;
-  rp.d_o = static_cast<const __nv_bfloat16*>(a.d_o); rp.d_ht = a.d_ht; rp.dh0 = a.dh0; rp.status = w.status;
+  rp.d_o = static_cast<const __nv_bfloat16*>(a.d_o); rp.d_ht = a.d_ht; rp.dh0 = a.dh0; rp.status = w.status; rp.dbg = g_dbg_clocks;
   rp.N = a.N; rp.H = a.H;
   if (make_rows_tmap(&rp.tm_do, a.d_o, false, a.tokens, a.H, VD, 64, C, true)) return KDA_E_TMAP;
-  if ((rc = launch_bwd_scan_tc(rp, a.N * a.H, st)) != KDA_OK) return rc;
+  const int slices = scan_slices_for(a.N * a.H, a.scan_slices);
+  if ((rc = slices > 1 ? launch_bwd_scan_vs(rp, a.N * a.H, slices, st) : launch_bwd_scan_tc(rp, a.N * a.H, st)) != KDA_OK) return rc;
   prof_mark(prof, KDA_STAGE_BWD_SCAN, st);
 
   MainParams mp{};

@@ -35,11 +35,14 @@ struct RScanParams {
   const float* d_ht;
   float* dh0;
   unsigned* status;
+  long long* dbg;       // development aid: phase clocks
   int N, H;
   alignas(64) CUtensorMap tm_do;   // 64-column boxes of dO in the 128-byte-swizzled operand layout
 };
 
 int launch_bwd_scan_tc(const RScanParams& p, int blocks, cudaStream_t st);
+// several CTAs per (sequence, head) unit, one per slice of the value columns (kda_chunk_bwd_scan_vs.cu)
+int launch_bwd_scan_vs(const RScanParams& p, int units, int slices, cudaStream_t st);
 
 // both return KDA_OK, a negative KDA_E_* or a positive cudaError_t
 // tcgen05 / TMEM version of the per-chunk backward kernel (kda_chunk_bwd_tc.cu)

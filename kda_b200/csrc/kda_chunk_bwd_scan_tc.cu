@@ -114,6 +114,8 @@ __global__ void __launch_bounds__(RNT, 1) kda_chunk_bwd_scan_tc_kernel(const __g
     TcRScanStage& d = s.st[i & 1];
     const int c = c_end - 1 - i;
     const size_t tile = static_cast<size_t>(c) * p.H + h;
+    long long* const dbg = (i == 8) ? p.dbg : nullptr;      // development aid: clocks of a steady-state chunk
+    KDA_DBG_CLOCK(dbg, 40);
 
     if (!mbar_wait(&s.full[i & 1], (i >> 1) & 1)) alive = false;
     if (tid == 0) bulk_wait_read<0>();      // the previous chunk's tile stores have read DHb / DVNT
@@ -122,6 +124,7 @@ __global__ void __launch_bounds__(RNT, 1) kda_chunk_bwd_scan_tc_kernel(const __g
       if (tid == 0) atomicOr(p.status, 4u);
       break;
     }
+    KDA_DBG_CLOCK(dbg, 41);
 
     // ---- state pass ------------------------------------------------------------------------------------------------------
 #pragma unroll
@@ -137,9 +140,11 @@ __global__ void __launch_bounds__(RNT, 1) kda_chunk_bwd_scan_tc_kernel(const __g
     }
     umma::tmem_st_wait();
     fence_proxy_async();
+    KDA_DBG_CLOCK(dbg, 42);
     umma::fence_before_sync();
     __syncthreads();
     umma::fence_after_sync();
+    KDA_DBG_CLOCK(dbg, 43);
 
     // ---- products 1: dv_new^T = dO^T Aqk + dhT kg^T ---------------------------------------------------------------------
     if (tid == 0) {
@@ -164,6 +169,7 @@ __global__ void __launch_bounds__(RNT, 1) kda_chunk_bwd_scan_tc_kernel(const __g
     if (!mbar_wait(&s.barM, mph & 1)) alive = false;
     ++mph;
     umma::fence_after_sync();
+    KDA_DBG_CLOCK(dbg, 44);
 
     // ---- epilogue 1: dv_new^T -> bf16 tile -----------------------------------------------------------------------------------
     if (alive) {
@@ -184,6 +190,7 @@ __global__ void __launch_bounds__(RNT, 1) kda_chunk_bwd_scan_tc_kernel(const __g
       break;
     }
     umma::fence_after_sync();
+    KDA_DBG_CLOCK(dbg, 45);
 
     // ---- products 2: dhT += dO^T qg - dv_new^T w ------------------------------------------------------------------------------
     if (tid == 0) {
@@ -192,11 +199,12 @@ __global__ void __launch_bounds__(RNT, 1) kda_chunk_bwd_scan_tc_kernel(const __g
       constexpr uint32_t idW = umma::instr_desc(128, 128, false, true, false, true);     // A = dv_new^T (K-major), B = -w rows j
       const uint64_t dDO = umma::smem_desc(aDO, 8192, umma::ATOM_BYTES), dQ = umma::smem_desc(aQG, 8192, umma::ATOM_BYTES);
       const uint64_t dDV = umma::desc_kmajor(aDV, 0), dW = umma::smem_desc(aW, 8192, umma::ATOM_BYTES);
+      // first every dO^T qg term, then every dv_new^T w term: the order in which the sliced kernel (kda_chunk_bwd_scan_vs.cu)
+      // has to add them, so that both layouts give the same bits
 #pragma unroll
-      for (int sK = 0; sK < 4; ++sK) {
-        umma::mma_ss(tb + C_H, dDO + static_cast<uint64_t>(sK) * 128u, dQ + static_cast<uint64_t>(sK) * 128u, idQ, 1);
-        umma::mma_ss(tb + C_H, dDV + static_cast<uint64_t>(sK) * 2u, dW + static_cast<uint64_t>(sK) * 128u, idW, 1);
-      }
+      for (int sK = 0; sK < 4; ++sK) umma::mma_ss(tb + C_H, dDO + static_cast<uint64_t>(sK) * 128u, dQ + static_cast<uint64_t>(sK) * 128u, idQ, 1);
+#pragma unroll
+      for (int sK = 0; sK < 4; ++sK) umma::mma_ss(tb + C_H, dDV + static_cast<uint64_t>(sK) * 2u, dW + static_cast<uint64_t>(sK) * 128u, idW, 1);
       umma::commit(&s.barM);
       bulk_s2g(p.DVNEWT + tile * TILE_VT, s.DVNT, TILE_VT);
       bulk_commit();
@@ -204,6 +212,7 @@ __global__ void __launch_bounds__(RNT, 1) kda_chunk_bwd_scan_tc_kernel(const __g
     if (!mbar_wait(&s.barM, mph & 1)) alive = false;
     ++mph;
     umma::fence_after_sync();
+    KDA_DBG_CLOCK(dbg, 46);
     if (tid == 0 && alive && i + 2 < nchunks) issue_load(i + 2);      // this stage's tiles are free again
   }
 

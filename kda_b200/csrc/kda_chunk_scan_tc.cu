@@ -124,6 +124,8 @@ __global__ void __launch_bounds__(SNT, 1) kda_chunk_scan_tc_kernel(const ScanPar
     ci.len = static_cast<int>(seq_tok1 - ci.tok0 < C ? seq_tok1 - ci.tok0 : C);
     const size_t tile = static_cast<size_t>(c) * p.H + h;
     const uint32_t to = C_O + 64 * (i & 1);
+    long long* const dbg = (i == 8) ? p.dbg : nullptr;      // development aid: clocks of a steady-state chunk
+    KDA_DBG_CLOCK(dbg, 32);
 
     if (!mbar_wait(&s.full[i & 1], (i >> 1) & 1)) alive = false;
     // the previous chunk's bulk stores must have read Hb / VNT before they are rewritten
@@ -133,6 +135,7 @@ __global__ void __launch_bounds__(SNT, 1) kda_chunk_scan_tc_kernel(const ScanPar
       if (tid == 0) atomicOr(p.status, 1u);
       break;
     }
+    KDA_DBG_CLOCK(dbg, 33);
 
     // ---- state pass: bf16 copy of hT for the products, hT *= Gam_last in TMEM ----------------------------------
     if (!issuer) {
@@ -150,9 +153,11 @@ __global__ void __launch_bounds__(SNT, 1) kda_chunk_scan_tc_kernel(const ScanPar
       umma::tmem_st_wait();
       fence_proxy_async();
     }
+    KDA_DBG_CLOCK(dbg, 34);
     umma::fence_before_sync();
     __syncthreads();
     umma::fence_after_sync();
+    KDA_DBG_CLOCK(dbg, 35);
 
     // ---- products 1: the chain from chunk to chunk runs through v_part only; it goes first with its own commit, the
     // products for o execute behind it while the compute warps already turn v_part into v_new
@@ -184,6 +189,7 @@ __global__ void __launch_bounds__(SNT, 1) kda_chunk_scan_tc_kernel(const ScanPar
     if (!issuer) {
       if (!mbar_wait(&s.barM, mph & 1)) alive = false;
       umma::fence_after_sync();
+      KDA_DBG_CLOCK(dbg, 36);
       if (alive) {
         float x[16], y[16];
         umma::tmem_ld16(tq + C_VN + 32 * half, x);
@@ -214,6 +220,7 @@ __global__ void __launch_bounds__(SNT, 1) kda_chunk_scan_tc_kernel(const ScanPar
       break;
     }
     umma::fence_after_sync();
+    KDA_DBG_CLOCK(dbg, 37);
 
     // ---- products 2 ---------------------------------------------------------------------------------------------------
     if (lead) {
@@ -236,6 +243,7 @@ __global__ void __launch_bounds__(SNT, 1) kda_chunk_scan_tc_kernel(const ScanPar
     if (!mbar_wait(&s.barM, mph & 1)) alive = false;
     ++mph;
     umma::fence_after_sync();
+    KDA_DBG_CLOCK(dbg, 38);
     if (issuer) {
       // this stage's operand tiles are free: fetch chunk i + 2 into it (the compute warps do not wait for this)
       if (lead && alive && i + 2 < nchunks) issue_load(i + 2);
@@ -264,6 +272,7 @@ __global__ void __launch_bounds__(SNT, 1) kda_chunk_scan_tc_kernel(const ScanPar
             *reinterpret_cast<const uint4*>(&s.oS[r * VD + pc * 8]);
     }
     // (the next iteration's first barrier orders these reads of oS before it is rewritten)
+    KDA_DBG_CLOCK(dbg, 39);
   }
   alive = __syncthreads_and(alive);
 

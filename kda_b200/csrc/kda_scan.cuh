@@ -14,10 +14,24 @@ struct ScanParams {
   float* ht;
   __nv_bfloat16* o;
   unsigned* status;
+  long long* dbg;       // development aid: phase clocks (NULL unless built with the clock marks and a buffer is registered)
   int N, H;
 };
 
 // tcgen05 / TMEM version (kda_chunk_scan_tc.cu); returns KDA_OK, a negative KDA_E_* or a positive cudaError_t
 int launch_scan_tc(const ScanParams& p, int blocks, cudaStream_t st);
+
+// The same scan with `slices` (2 or 4) CTAs per (sequence, head) unit, one per slice of the value columns
+// (kda_chunk_scan_vs.cu): for calls with fewer units than SMs, where one CTA's chunk-to-chunk chain sets the time.
+int launch_scan_vs(const ScanParams& p, int units, int slices, cudaStream_t st);
+
+// How many CTAs per unit the two state scans use: `requested` (1, 2 or 4) if the caller chose, otherwise as many
+// slices as keep the grid within one CTA per SM of the current device.
+inline int scan_slices_for(int units, int requested) {
+  if (requested == 1 || requested == 2 || requested == 4) return requested;
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return units * 4 <= sms ? 4 : (units * 2 <= sms ? 2 : 1);
+}
 
 }  // namespace kda

@@ -93,6 +93,36 @@ __device__ __forceinline__ void mma_ss_lead(uint32_t tmem_d, uint64_t adesc, uin
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(leader)
       : "memory");
 }
+// Four products of one accumulation chain in ONE asm block: D (+)= A_s B_s for k-steps s = 0..3, the descriptors of step s
+// being a + s * A_INC and b + s * B_INC (in descriptor units of 16 bytes: 2 per k-step of a K-major tile, 128 per k-step
+// of an MN-major tile).  The first product accumulates iff acc_first != 0, the others always.  Keeping the descriptor
+// arithmetic and the predicates inside the block lets consecutive products issue about 56 cycles apart; issued as four
+// separate asm statements with their operands prepared in between, the same thread needs about 90 cycles per product.
+template <int A_INC, int B_INC>
+__device__ __forceinline__ void mma4(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc_first) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p0, p1;\n\t"
+      ".reg .b64 a1, b1;\n\t"
+      "setp.ne.b32 p0, %4, 0;\n\t"
+      "setp.eq.b32 p1, %4, %4;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p0;\n\t"
+      "add.u64 a1, %1, %5;\n\t"
+      "add.u64 b1, %2, %8;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a1, b1, %3, p1;\n\t"
+      "add.u64 a1, %1, %6;\n\t"
+      "add.u64 b1, %2, %9;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a1, b1, %3, p1;\n\t"
+      "add.u64 a1, %1, %7;\n\t"
+      "add.u64 b1, %2, %10;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a1, b1, %3, p1;\n\t"
+      "}\n" ::"r"(tmem_d),
+      "l"(a), "l"(b), "r"(idesc), "r"(acc_first), "n"(A_INC), "n"(2 * A_INC), "n"(3 * A_INC), "n"(B_INC), "n"(2 * B_INC), "n"(3 * B_INC)
+      : "memory");
+}
+constexpr int KSTEP_KMAJOR = 2;      // descriptor units per k-step (16 columns = 32 bytes) inside a K-major SW128 tile
+constexpr int KSTEP_MNMAJOR = 128;   // descriptor units per k-step (16 rows = two atoms = 2048 bytes) of an MN-major SW128 tile
+
 // Makes the mbarrier receive one arrival when every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");

@@ -18,6 +18,7 @@ from . import _lib
 
 _DT = {torch.bfloat16: _lib.KDA_BF16, torch.float32: _lib.KDA_FP32}
 CHUNK = 64
+SCAN_SLICES = 0      # CTAs per (sequence, head) of the state scans: 0 = automatic; 1, 2, 4 force a layout (tests, measurements)
 
 
 def _checked() -> bool:
@@ -344,7 +345,7 @@ def _chunk_args(q, k, v, g, beta, h0, cu, o, ht, ws, N, H, K, V, tokens, l2, sav
         q=_ptr(q), k=_ptr(k), v=_ptr(v), g=_ptr(g), beta=_ptr(beta), h0=_ptr(h0), cu_seqlens=_ptr(cu),
         o=_ptr(o), ht=_ptr(ht), workspace=_ptr(ws), workspace_bytes=ws.numel() if ws is not None else 0,
         tokens=tokens, N=N, H=H, K=K, V=V, io_dtype=_lib.KDA_BF16, use_qk_l2norm=int(l2),
-        save_for_backward=int(save), scale=float(scale), HQ=q.shape[-2])
+        save_for_backward=int(save), scale=float(scale), HQ=q.shape[-2], scan_slices=int(SCAN_SLICES))
     for name, t in extra.items():
         if name == "bwd_ws":
             a.bwd_workspace = _ptr(t)
