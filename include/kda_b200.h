@@ -158,9 +158,9 @@ typedef struct kda_chunk_args {
   int32_t HQ;                  /* grouped value heads (GVA, fla/ops/kda/chunk.py:194-196,379-386): q, k, dq, dk have HQ heads
                                   ([tokens, HQ, K]) while v, g, beta, o, the states and their gradients have H; value head h reads
                                   q/k head h / (H / HQ), and dq, dk are summed over each group.  0 or H: no grouping. */
-  int32_t scan_slices;         /* CTAs per (sequence, head) of the two state scans: 0 = chosen from N * H and the SM count (calls
-                                  with fewer units than SMs cut every unit into 2 or 4 slices of value columns, which shortens the
-                                  chunk-to-chunk chain); 1, 2 or 4 force a layout.  The results do not depend on it. */
+  int32_t scan_slices;         /* CTAs per (sequence, head) of the two state scans: 0 = chosen from N * H and the SM count (a call with
+                                  at most a quarter as many units as SMs cuts every unit into 4 slices of 32 value columns, which
+                                  shortens the chunk-to-chunk chain); 1 or 4 force a layout.  The results do not depend on it. */
 } kda_chunk_args;
 
 /* Upper bound on the number of chunks: every sequence adds at most one partial chunk. */

@@ -159,7 +159,7 @@ extern "C" int kda_chunk_bwd(const kda_chunk_args* args, void* stream) {
   rp.N = a.N; rp.H = a.H;
   if (make_rows_tmap(&rp.tm_do, a.d_o, false, a.tokens, a.H, VD, 64, C, true)) return KDA_E_TMAP;
   const int slices = scan_slices_for(a.N * a.H, a.scan_slices);
-  if ((rc = slices > 1 ? launch_bwd_scan_vs(rp, a.N * a.H, slices, st) : launch_bwd_scan_tc(rp, a.N * a.H, st)) != KDA_OK) return rc;
+  if ((rc = slices > 1 ? launch_bwd_scan_vs(rp, a.N * a.H, st) : launch_bwd_scan_tc(rp, a.N * a.H, st)) != KDA_OK) return rc;
   prof_mark(prof, KDA_STAGE_BWD_SCAN, st);
 
   MainParams mp{};

@@ -41,8 +41,8 @@ struct RScanParams {
 };
 
 int launch_bwd_scan_tc(const RScanParams& p, int blocks, cudaStream_t st);
-// several CTAs per (sequence, head) unit, one per slice of the value columns (kda_chunk_bwd_scan_vs.cu)
-int launch_bwd_scan_vs(const RScanParams& p, int units, int slices, cudaStream_t st);
+// four CTAs per (sequence, head) unit, one per slice of 32 value columns (kda_chunk_bwd_scan_vs.cu)
+int launch_bwd_scan_vs(const RScanParams& p, int units, cudaStream_t st);
 
 // both return KDA_OK, a negative KDA_E_* or a positive cudaError_t
 // tcgen05 / TMEM version of the per-chunk backward kernel (kda_chunk_bwd_tc.cu)

@@ -1,7 +1,7 @@
 // Reverse state scan of chunked KDA for FEW (sequence, head) units: several CTAs per unit, one per slice of the value
 // columns (sm_100a, tcgen05 + TMEM).  The counterpart of kda_chunk_scan_vs.cu for the backward.
 //
-// A unit is cut into 128 / VS slices of VS value columns (VS = 64 or 32); each CTA walks the unit's chunks from the last
+// A unit is cut into 128 / VS slices of VS value columns (VS = 32: four slices); each CTA walks the unit's chunks from the last
 // to the first with its slice of the state gradient in tensor memory, TMEM lane = KEY row k: dh[k][v].  Per chunk:
 //   state pass   thread k writes its VS/2 columns of dh as bf16 into row k of DHb ([128 k][VS v], MN-major B operand;
 //                transposed into the chunk's DH tile rows beside the products) and scales the fp32 copy by Gam_last[k];
@@ -324,8 +324,6 @@ static int launch_rvs(const RScanParams& p, int units, cudaStream_t st) {
   return static_cast<int>(cudaGetLastError());
 }
 
-int launch_bwd_scan_vs(const RScanParams& p, int units, int slices, cudaStream_t st) {
-  return slices == 4 ? launch_rvs<32>(p, units, st) : launch_rvs<64>(p, units, st);
-}
+int launch_bwd_scan_vs(const RScanParams& p, int units, cudaStream_t st) { return launch_rvs<32>(p, units, st); }
 
 }  // namespace kda

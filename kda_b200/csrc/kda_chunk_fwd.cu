@@ -649,7 +649,7 @@ int validate_chunk_args(const kda_chunk_args& a, bool backward) {
   if (a.tokens < 0 || a.N < 0 || a.H <= 0) return KDA_E_SHAPE;
   if (a.HQ < 0 || (a.HQ > 0 && (a.HQ > a.H || a.H % a.HQ != 0))) return KDA_E_SHAPE;
   if (a.K != KD || a.V != VD) return KDA_E_SHAPE;
-  if (a.scan_slices != 0 && a.scan_slices != 1 && a.scan_slices != 2 && a.scan_slices != 4) return KDA_E_SHAPE;
+  if (a.scan_slices != 0 && a.scan_slices != 1 && a.scan_slices != 4) return KDA_E_SHAPE;
   if (a.io_dtype != KDA_BF16) return KDA_E_DTYPE;
   if (a.tokens / C + a.N > 0x3fffffffLL) return KDA_E_SHAPE;
   if (a.tokens == 0 || a.N == 0) return KDA_OK;
@@ -732,7 +732,7 @@ extern "C" int kda_chunk_fwd(const kda_chunk_args* args, void* stream) {
   sp.h0 = a.h0; sp.ht = a.ht; sp.o = static_cast<__nv_bfloat16*>(a.o); sp.status = w.status; sp.dbg = g_dbg_clocks;
   sp.N = a.N; sp.H = a.H;
   const int slices = scan_slices_for(a.N * a.H, a.scan_slices);
-  if ((rc = slices > 1 ? launch_scan_vs(sp, a.N * a.H, slices, st) : launch_scan_tc(sp, a.N * a.H, st)) != KDA_OK) return rc;
+  if ((rc = slices > 1 ? launch_scan_vs(sp, a.N * a.H, st) : launch_scan_tc(sp, a.N * a.H, st)) != KDA_OK) return rc;
   prof_mark(prof, KDA_STAGE_SCAN, st);
   return KDA_OK;
 }

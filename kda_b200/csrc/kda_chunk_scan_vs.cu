@@ -2,7 +2,7 @@
 // columns (sm_100a, tcgen05 + TMEM).
 //
 // The recurrence is independent per value column, and the time of a scan with fewer units than SMs is set by the
-// chunk-to-chunk chain of one CTA.  Here a unit is cut into 128 / VS slices of VS value columns (VS = 64 or 32), each
+// chunk-to-chunk chain of one CTA.  Here a unit is cut into 128 / VS slices of VS value columns (VS = 32: four slices), each
 // walked by its own CTA, and the state is held the other way round than in the one-CTA-per-unit kernel: TMEM lane =
 // KEY row k, columns = the slice's value columns, h[k][v].  That makes every product's N dimension the slice width, so
 // the state pass and the epilogue of a chunk shrink with the slice.  Per chunk:
@@ -384,8 +384,6 @@ static int launch_vs(const ScanParams& p, int units, cudaStream_t st) {
   return static_cast<int>(cudaGetLastError());
 }
 
-int launch_scan_vs(const ScanParams& p, int units, int slices, cudaStream_t st) {
-  return slices == 4 ? launch_vs<32>(p, units, st) : launch_vs<64>(p, units, st);
-}
+int launch_scan_vs(const ScanParams& p, int units, cudaStream_t st) { return launch_vs<32>(p, units, st); }
 
 }  // namespace kda

@@ -21,17 +21,18 @@ struct ScanParams {
 // tcgen05 / TMEM version (kda_chunk_scan_tc.cu); returns KDA_OK, a negative KDA_E_* or a positive cudaError_t
 int launch_scan_tc(const ScanParams& p, int blocks, cudaStream_t st);
 
-// The same scan with `slices` (2 or 4) CTAs per (sequence, head) unit, one per slice of the value columns
-// (kda_chunk_scan_vs.cu): for calls with fewer units than SMs, where one CTA's chunk-to-chunk chain sets the time.
-int launch_scan_vs(const ScanParams& p, int units, int slices, cudaStream_t st);
+// The same scan with four CTAs per (sequence, head) unit, one per slice of 32 value columns (kda_chunk_scan_vs.cu): for
+// calls with so few units that one CTA's chunk-to-chunk chain sets the time.
+int launch_scan_vs(const ScanParams& p, int units, cudaStream_t st);
 
-// How many CTAs per unit the two state scans use: `requested` (1, 2 or 4) if the caller chose, otherwise as many
-// slices as keep the grid within one CTA per SM of the current device.
+// How many CTAs per unit the two state scans use: `requested` (1 or 4) if the caller chose, otherwise four while the
+// grid stays within one CTA per SM of the current device.  (Two slices of 64 columns were built and measured: slower
+// than one CTA per unit at every size, because the chain's cost is latency, not the width of its products.)
 inline int scan_slices_for(int units, int requested) {
-  if (requested == 1 || requested == 2 || requested == 4) return requested;
+  if (requested == 1 || requested == 4) return requested;
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  return units * 4 <= sms ? 4 : (units * 2 <= sms ? 2 : 1);
+  return units * 4 <= sms ? 4 : 1;
 }
 
 }  // namespace kda

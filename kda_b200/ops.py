@@ -18,7 +18,7 @@ from . import _lib
 
 _DT = {torch.bfloat16: _lib.KDA_BF16, torch.float32: _lib.KDA_FP32}
 CHUNK = 64
-SCAN_SLICES = 0      # CTAs per (sequence, head) of the state scans: 0 = automatic; 1, 2, 4 force a layout (tests, measurements)
+SCAN_SLICES = 0      # CTAs per (sequence, head) of the state scans: 0 = automatic; 1 or 4 force a layout (tests, measurements)
 
 
 def _checked() -> bool:
@@ -414,9 +414,12 @@ class ChunkKDAFunction(torch.autograd.Function):
         return dq, dk, dv, dg.to(g_dtype), dbeta.to(beta_dtype), None, dh0, None, None, None
 
 
-def _chunk_fwd_with_states(q, k, v, g, beta, scale, initial_state, output_final_state, use_l2norm, cu_seqlens):
+def _chunk_fwd_with_states(q, k, v, g, beta, scale, initial_state, output_final_state, use_l2norm, cu_seqlens, chunk_size=CHUNK):
     """Forward for inference engines (fla/ops/kda/chunk.py:95-98): also returns h, the state at the start of every
-    chunk, [B, NT, H, K, V] bf16 (NT chunks per sequence; with cu_seqlens B = 1 and NT counts all chunks)."""
+    chunk of `chunk_size` tokens, [B, NT, H, K, V] bf16 (NT chunks per sequence; with cu_seqlens B = 1 and NT counts all
+    chunks).  The kernels tile by 64 tokens and keep the state at the start of every 64-token chunk; for chunk_size = 32
+    the state in the middle of a chunk is that chunk's start state advanced over its first 32 tokens by the
+    token-recurrent kernel (one short sequence per chunk)."""
     B, T, _, K = q.shape
     H, V = v.shape[-2], v.shape[-1]
     dev = q.device
@@ -425,12 +428,12 @@ def _chunk_fwd_with_states(q, k, v, g, beta, scale, initial_state, output_final_
     h0 = initial_state.contiguous() if initial_state is not None else None
     if cu_seqlens is None:
         N, cu = B, _fixed_cu_seqlens(B, T, dev)
-        nt_shape = (B, (T + CHUNK - 1) // CHUNK)
+        starts, lens = [b * T for b in range(B)], [T] * B
     else:
         cu = _as_i32(cu_seqlens, dev)
         N = cu.numel() - 1
-        lens = (cu[1:] - cu[:-1]).cpu()                       # the output shape depends on the lengths: one host read
-        nt_shape = (1, int(((lens + CHUNK - 1) // CHUNK).sum()))
+        cul = cu.cpu().tolist()                               # the output shape depends on the lengths: one host read
+        starts, lens = cul[:-1], [cul[i + 1] - cul[i] for i in range(N)]
     tokens = B * T
     lib = _lib.load()
     ws = torch.empty(lib.kda_chunk_workspace_bytes(tokens, N, H, K, V, 1), dtype=torch.uint8, device=dev)
@@ -443,8 +446,40 @@ def _chunk_fwd_with_states(q, k, v, g, beta, scale, initial_state, output_final_
         _lib.check(lib.kda_chunk_export_states(_ptr(ws), ws.numel(), tokens, N, H, _ptr(hbuf), _stream(dev)), "kda_chunk_export_states")
         if _checked():
             _lib.check_chunk_status(ws.data_ptr(), "kda_chunk_fwd")
-    nt = nt_shape[0] * nt_shape[1]
-    return o, ht, hbuf[:nt].view(nt_shape[0], nt_shape[1], H, K, V)
+    nt64 = [(n + CHUNK - 1) // CHUNK for n in lens]
+    h64 = hbuf[:sum(nt64)]
+    if chunk_size == CHUNK:
+        h = h64
+        nt = nt64
+    else:
+        # states every 32 tokens: even positions are the 64-token chunks' start states; an odd position exists where the
+        # chunk has more than 32 tokens and is that chunk's state after its first 32 tokens
+        half = CHUNK // 2
+        nt = [(n + half - 1) // half for n in lens]
+        h = torch.empty(sum(nt), H, K, V, dtype=torch.bfloat16, device=dev)
+        even_dst, odd_dst, odd_src, tok = [], [], [], []
+        base32 = base64 = 0
+        for s0, n, c64, c32 in zip(starts, lens, nt64, nt):
+            for c in range(c64):
+                even_dst.append(base32 + 2 * c)
+                if n - c * CHUNK > half:
+                    odd_dst.append(base32 + 2 * c + 1)
+                    odd_src.append(base64 + c)
+                    tok.append(s0 + c * CHUNK)
+            base32, base64 = base32 + c32, base64 + c64
+        h[torch.tensor(even_dst, device=dev, dtype=torch.long)] = h64
+        if odd_dst:
+            idx = (torch.tensor(tok, device=dev, dtype=torch.long).unsqueeze(1) + torch.arange(half, device=dev)).reshape(-1)
+            flat = lambda t: t.reshape(tokens, *t.shape[2:]).index_select(0, idx).unsqueeze(0)      # noqa: E731
+            seg_cu = torch.arange(0, len(tok) * half + 1, half, dtype=torch.int32, device=dev)
+            start_state = h64.index_select(0, torch.tensor(odd_src, device=dev, dtype=torch.long)).float()
+            _, mid = fused_recurrent_kda_fwd(flat(q), flat(k), flat(v), flat(g32), flat(beta32), initial_state=start_state, scale=scale,
+                                             output_final_state=True, inplace_final_state=False, cu_seqlens=seg_cu,
+                                             use_qk_l2norm_in_kernel=use_l2norm)
+            h[torch.tensor(odd_dst, device=dev, dtype=torch.long)] = mid.to(torch.bfloat16)
+    if cu_seqlens is None:
+        return o, ht, h.view(B, nt[0], H, K, V)
+    return o, ht, h.view(1, sum(nt), H, K, V)
 
 
 @torch.compiler.disable
@@ -465,9 +500,10 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
     tensor is [.., V, K] instead of [.., K, V].
 
     bf16 inputs with K = V = 128 take the chunked tensor-core kernels.  float32 inputs take the exact
-    token-recurrent fp32 kernel (forward only).  `safe_gate`, `disable_recompute` and `chunk_size` (32 or 64) only
-    select variants of the same computation upstream and are accepted as no-ops (the kernels here are range-safe
-    for any gate and always tile by 64 tokens); options that change results and are not built raise.
+    token-recurrent fp32 kernel (forward only).  `safe_gate` and `disable_recompute` only select variants of the same
+    computation upstream and are accepted as no-ops (the kernels here are range-safe for any gate); `chunk_size` (32 or
+    64) changes nothing but the spacing of the intermediate states (the kernels always tile by 64 tokens); options
+    that change results and are not built raise.
     """
     _unsupported("cp_context", cp_context, None)
     if "use_qk_l2norm" in kwargs:
@@ -477,9 +513,7 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
         raise ValueError(f"`chunk_size` must be either 32 or 64 for KDA, got {chunk_size}.")
     # chunk_size only selects how the same recurrence is tiled: o, the final state and every gradient are the same
     # function of the inputs for 32 and 64, so both run on the 64-token tiles.  Only the intermediate states depend on
-    # it (one state per chunk).
-    if chunk_size != CHUNK and return_intermediate_states:
-        raise NotImplementedError("kda_b200: return_intermediate_states gives one state per 64 tokens; chunk_size=32 is not built for it")
+    # it (one state per chunk of that size, see _chunk_fwd_with_states).
     B, T, H, K, V = _check_common(q, k, v, g, beta, initial_state, cu_seqlens)
     if scale is None:
         scale = K ** -0.5
@@ -502,7 +536,7 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
         assert torch.is_inference_mode_enabled(), "return_intermediate_states is only allowed in inference mode"
         assert disable_recompute is False, "return_intermediate_states must be used with disable_recompute=False"
         o, ht, h = _chunk_fwd_with_states(q, k, v, g, beta, float(scale), initial_state, bool(output_final_state),
-                                          bool(use_qk_l2norm_in_kernel), cu_seqlens)
+                                          bool(use_qk_l2norm_in_kernel), cu_seqlens, chunk_size)
         if transpose_state_layout:
             ht, h = (tr(ht).contiguous() if ht is not None else None), tr(h).contiguous()
         return o, ht, h

@@ -155,8 +155,46 @@ def test_chunk_size_32_is_the_same_function():
     assert max_norm_err(outs[0][0], o_ref) <= 2e-2 and max_norm_err(outs[0][1], ht_ref) <= 2e-2
     with pytest.raises(ValueError, match="32 or 64"):
         chunk_kda(*(d[n].cuda() for n in ("q", "k", "v", "g", "beta")), chunk_size=16)
-    with torch.inference_mode(), pytest.raises(NotImplementedError, match="chunk_size=32"):
-        chunk_kda(*(d[n].cuda() for n in ("q", "k", "v", "g", "beta")), chunk_size=32, return_intermediate_states=True)
+
+
+def test_intermediate_states_every_32_tokens():
+    """chunk_size=32 with return_intermediate_states: one state per 32 tokens (fla/ops/kda/chunk.py:95-98 with
+    chunk_size=32), each against the fp64 oracle run on the prefix; equal-length batch with a ragged tail and packed varlen."""
+    from kda_b200 import chunk_kda
+    from oracle.kda_oracle import recurrent_kda
+    d = make_inputs(2, 150, 2, 128, 128, torch.bfloat16, seed=81, h0_std=0.02)
+    c = {n: (t.cuda() if t is not None else None) for n, t in d.items()}
+    with torch.inference_mode():
+        o, ht, h = chunk_kda(c["q"], c["k"], c["v"], c["g"], c["beta"], initial_state=c["h0"], output_final_state=True,
+                             return_intermediate_states=True, chunk_size=32, use_qk_l2norm_in_kernel=True)
+        o64, ht64, h64 = chunk_kda(c["q"], c["k"], c["v"], c["g"], c["beta"], initial_state=c["h0"], output_final_state=True,
+                                   return_intermediate_states=True, use_qk_l2norm_in_kernel=True)
+    assert h.shape == (2, 5, 2, 128, 128) and h.dtype == torch.bfloat16          # ceil(150 / 32) = 5
+    assert torch.equal(o, o64) and torch.equal(ht, ht64) and torch.equal(h[:, 0::2], h64)
+    for i in range(5):
+        if i == 0:
+            ref = d["h0"].double()
+        else:
+            _, ref = recurrent_kda(d["q"][:, :32 * i], d["k"][:, :32 * i], d["v"][:, :32 * i], d["g"][:, :32 * i], d["beta"][:, :32 * i],
+                                   initial_state=d["h0"], output_final_state=True, use_qk_l2norm=True)
+        assert max_norm_err(h[:, i], ref) <= 2e-2, i
+    # packed: 70 + 20 + 130 tokens -> 3 + 1 + 5 states
+    cu = torch.tensor([0, 70, 90, 220], dtype=torch.int32)
+    dv = make_inputs(1, 220, 2, 128, 128, torch.bfloat16, seed=82, h0_std=0.02, n_states=3)
+    cv = {n: (t.cuda() if t is not None else None) for n, t in dv.items()}
+    with torch.inference_mode():
+        _, _, hv = chunk_kda(cv["q"], cv["k"], cv["v"], cv["g"], cv["beta"], initial_state=cv["h0"], cu_seqlens=cu.cuda(),
+                             return_intermediate_states=True, chunk_size=32)
+    assert hv.shape == (1, 9, 2, 128, 128)
+    for pos, (seq, ntok) in {1: (0, 32), 2: (0, 64), 3: (1, 0), 5: (2, 32), 8: (2, 128)}.items():
+        s0 = int(cu[seq])
+        if ntok == 0:
+            ref = dv["h0"][seq].double()
+        else:
+            _, ref = recurrent_kda(*(dv[n][:, s0:s0 + ntok] for n in ("q", "k", "v", "g", "beta")), initial_state=dv["h0"][seq:seq + 1],
+                                   output_final_state=True)
+            ref = ref[0]
+        assert max_norm_err(hv[0, pos], ref) <= 2e-2, pos
 
 
 @pytest.mark.captures_graph

@@ -1,5 +1,5 @@
-"""The two state scans run with one CTA per (sequence, head) unit or, for calls with fewer units than SMs, with 2 or 4
-CTAs per unit (one per slice of the value columns).  Every layout computes the same sums in the same order, so o, the
+"""The two state scans run with one CTA per (sequence, head) unit or, for calls with few units, with four CTAs per unit
+(one per slice of 32 value columns).  Every layout computes the same sums in the same order, so o, the
 final state and every gradient are the same bits whichever is used -- which is what lets a packed sequence equal the
 same sequence run alone even when the two calls pick different layouts -- and each layout matches the float64 oracle."""
 import numpy as np
@@ -43,7 +43,7 @@ def test_every_scan_layout_gives_the_same_bits_and_matches_the_oracle(lens, l2):
                               use_qk_l2norm=l2)
     for n in NAMES:
         assert_bf16_parity(one[n], ref[n], n)
-    for slices in (2, 4):
+    for slices in (4,):
         got = _run(d, cu, slices, l2=l2)
         for n in NAMES:
             assert torch.equal(got[n], one[n]), (n, slices)
@@ -53,18 +53,18 @@ def test_forward_only_layouts_agree():
     """Inference (no tiles kept for a backward): the sliced scans skip their staging stores; same bits again."""
     d = make_inputs(2, 333, 2, 128, 128, torch.bfloat16, seed=950, h0_std=0.02, backward=True)
     one = _run(d, None, 1, backward=False)
-    for slices in (2, 4):
+    for slices in (4,):
         got = _run(d, None, slices, backward=False)
         assert torch.equal(got["o"], one["o"]) and torch.equal(got["ht"], one["ht"]), slices
 
 
 def test_automatic_choice_and_argument_check():
-    """Few units pick a sliced layout on their own; a slice count other than 0, 1, 2, 4 is an argument error."""
+    """Few units pick the sliced layout on their own; a slice count other than 0, 1, 4 is an argument error."""
     import ctypes as C
     from kda_b200 import _lib
     d = make_inputs(1, 100, 2, 128, 128, torch.bfloat16, seed=951, h0_std=0.02, backward=True)
     auto, one = _run(d, None, 0), _run(d, None, 1)
     for n in NAMES:
         assert torch.equal(auto[n], one[n]), n
-    a = _lib.ChunkArgs(tokens=64, N=1, H=2, K=128, V=128, io_dtype=0, scan_slices=3)
+    a = _lib.ChunkArgs(tokens=64, N=1, H=2, K=128, V=128, io_dtype=0, scan_slices=2)
     assert _lib.load().kda_chunk_fwd(C.byref(a), None) == -2
