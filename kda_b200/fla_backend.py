@@ -22,8 +22,8 @@ def _accepts(q, k, v, g, beta, initial_state=None, cp_context=None, **kwargs):
         return False, "kda_b200 needs an sm_100 CUDA device"
     if cp_context is not None:
         return False, "kda_b200 does not implement context parallelism"
-    if kwargs.get("chunk_size", 64) != 64 and kwargs.get("return_intermediate_states", False):
-        return False, "kda_b200 returns intermediate states per 64 tokens only (chunk_size=32 asked)"
+    if kwargs.get("chunk_size", 64) not in (32, 64):
+        return False, "kda_b200 takes chunk_size 32 or 64"
     if v.shape[2] % q.shape[2]:
         return False, f"HV={v.shape[2]} is not a multiple of H={q.shape[2]}"
     if q.dtype == torch.bfloat16:

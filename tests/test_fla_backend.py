@@ -42,8 +42,9 @@ def test_fla_chunk_kda_routes_to_kda_b200():
         assert "kda:chunk_kda:kda_b200" in kda_registry._logged
         assert torch.equal(o1, o2) and torch.equal(h1, h2)
         # what the kernels do not cover is handed back
-        ok, why = shim._accepts(c["q"], c["k"], c["v"], c["g"], c["beta"], chunk_size=32, return_intermediate_states=True)
+        ok, why = shim._accepts(c["q"], c["k"], c["v"], c["g"], c["beta"], chunk_size=16)
         assert not ok and "chunk_size" in why
+        assert shim._accepts(c["q"], c["k"], c["v"], c["g"], c["beta"], chunk_size=32, return_intermediate_states=True)[0]
         ok, why = shim._accepts(c["q"], c["k"], c["v"], c["g"], c["beta"], cp_context=object())
         assert not ok and "context parallelism" in why
         assert shim._accepts(c["q"], c["k"], c["v"], c["g"], c["beta"], chunk_size=32)[0]
