@@ -77,9 +77,9 @@ KERNEL_WORK = {
     "gate_bwd": (20 * K_, 4 * K_ + 2 * K_ + 2 * K_ + 4 + 2 + 2, 4 * K_ + 2 * K_ + 2 * K_ + 4 + 2 + 2),
 }
 # DRAM bytes per (token, head) that ncu measured (dram__bytes_read.sum + dram__bytes_write.sum of one launch) on a
-# small case of each kernel (B=1 T=8192, 262,144 (token, head) units; summaries under profiles/).  Traffic grows in
-# proportion to the units, so a launch's traffic is this figure times its units.
-KERNEL_TRAFFIC = {"prepare": 2533.0, "scan": 2043.0, "bwd_scan": 1814.0, "bwd_main": 4577.0, "decode": 125600.0}
+# small case of each kernel (B=1 T=8192, 262,144 (token, head) units; the one-CTA-per-unit scans at B=2; summaries under
+# profiles/).  Traffic grows in proportion to the units, so a launch's traffic is this figure times its units.
+KERNEL_TRAFFIC = {"prepare": 2524.0, "scan": 2112.0, "bwd_scan": 1870.0, "bwd_main": 4572.0, "decode": 125600.0}
 
 
 def load_peaks():
