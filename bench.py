@@ -96,13 +96,13 @@ class ClockSampler:
     Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index: int):
-        self.index, self.proc, self.lines = index, None, []
+    def __init__(self, index: int, interval_ms: int = 20):
+        self.index, self.proc, self.lines, self.interval_ms = index, None, [], interval_ms
 
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "20"],
+                                          "--format=csv,noheader,nounits", "-lms", str(self.interval_ms)],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -398,6 +398,7 @@ def main():
                          "(use_gate_in_kernel, use_beta_sigmoid_in_kernel); training workloads and decode")
     ap.add_argument("--l2norm", action="store_true", help="use_qk_l2norm_in_kernel=True (chunked workloads)")
     ap.add_argument("--gpu-bar-deadline", type=float, default=240.0, help="seconds the Triton comparison may take (0: skip it)")
+    ap.add_argument("--clock-interval-ms", type=int, default=20, help="nvidia-smi sampling interval during the timed region")
     ap.add_argument("--gpu-bar-child", action="store_true", help=argparse.SUPPRESS)
     args = ap.parse_args()
 
@@ -456,7 +457,7 @@ def main():
 
     # ---------------- kernel-resident timing ----------------
     sampler = ClockSampler(local_rank if os.environ.get("CUDA_VISIBLE_DEVICES") is None else
-                           int(os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local_rank]))
+                           int(os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local_rank]), args.clock_interval_ms)
     if rank == 0:
         sampler.start()          # started before the warm-up: nvidia-smi needs a moment to deliver samples
     for _ in range(args.warmup):
