@@ -147,3 +147,72 @@ extern "C" __attribute__((visibility("default"))) int kda_b200_debug_umma_issue_
   kda::umma_issue_bench_kernel<<<1, 128, smem, static_cast<cudaStream_t>(stream)>>>(out, M, N, count, naccum, converged, status);
   return static_cast<int>(cudaGetLastError());
 }
+
+// Round trip of one hand-over: a "compute" warp arrives on an mbarrier, the issuing thread (lane 0 of another warp) wakes,
+// issues `nmma` products (0, 4 or 8; M=64 N=32) and commits, the compute warp waits for the commit.  out[0] = average
+// cycles per round trip over `rounds` rounds, measured by the compute warp.
+namespace kda {
+
+__global__ void __launch_bounds__(64, 1) umma_roundtrip_kernel(long long* __restrict__ out, int nmma, int rounds, unsigned* __restrict__ status) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* barX = reinterpret_cast<uint64_t*>(base + 65536);
+  uint64_t* barY = barX + 1;
+  uint32_t* slot = reinterpret_cast<uint32_t*>(base + 65536 + 32);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  for (int i = tid; i < 65536 / 16; i += 64) reinterpret_cast<uint4*>(base)[i] = make_uint4(0u, 0u, 0u, 0u);
+  fence_proxy_async();
+  if (warp == 0) umma::tmem_alloc(slot, 64);
+  if (tid == 0) {
+    mbar_init(barX, 1);
+    mbar_init(barY, 1);
+    fence_mbar_init();
+  }
+  umma::fence_before_sync();
+  __syncthreads();
+  umma::fence_after_sync();
+  const uint32_t taddr = *slot;
+  const uint32_t idesc = umma::instr_desc(64, 32, false, true);
+  const uint64_t dA = umma::desc_kmajor(smem_u32(base), 0), dB = umma::desc_mnmajor(smem_u32(base + 32768), 0, 16384u);
+  bool ok = true;
+  if (warp == 0) {
+    const long long t0 = clock64();
+    for (int r = 0; r < rounds && ok; ++r) {
+      umma::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(barX);
+      ok = __all_sync(0xffffffffu, mbar_wait(barY, r & 1));
+      umma::fence_after_sync();
+    }
+    const long long t1 = clock64();
+    if (lane == 0) {
+      out[0] = (t1 - t0) / (rounds > 0 ? rounds : 1);
+      if (!ok) atomicOr(status, 1u);
+    }
+  } else if (lane == 0) {
+    for (int r = 0; r < rounds && ok; ++r) {
+      ok = mbar_wait(barX, r & 1);
+      umma::fence_after_sync();
+      if (nmma >= 4) umma::mma4<umma::KSTEP_KMAJOR, umma::KSTEP_MNMAJOR>(taddr, dA, dB, idesc, 0);
+      if (nmma >= 8) umma::mma4<umma::KSTEP_KMAJOR, umma::KSTEP_MNMAJOR>(taddr, dA + 8u, dB + 4u * umma::KSTEP_MNMAJOR, idesc, 1);
+      umma::commit(barY);
+    }
+    if (!ok) atomicOr(status, 2u);
+  }
+  umma::fence_before_sync();
+  __syncthreads();
+  if (warp == 0) umma::tmem_dealloc(taddr, 64);
+}
+
+}  // namespace kda
+
+extern "C" __attribute__((visibility("default"))) int kda_b200_debug_umma_roundtrip(long long* out, int nmma, int rounds, unsigned* status,
+                                                                                    void* stream) {
+  if (!out || !status) return KDA_E_NULL;
+  if ((nmma != 0 && nmma != 4 && nmma != 8) || rounds < 1 || rounds > 4096) return KDA_E_SHAPE;
+  const int smem = 65536 + 64 + 1024;
+  cudaError_t e = cudaFuncSetAttribute(kda::umma_roundtrip_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  kda::umma_roundtrip_kernel<<<1, 64, smem, static_cast<cudaStream_t>(stream)>>>(out, nmma, rounds, status);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -164,19 +164,17 @@ __global__ void __launch_bounds__(VS_THREADS, 1) kda_chunk_scan_vs_kernel(const 
   // gave up raises s.dead and leaves, and the others follow at their next look (or when their own wait runs out).
   if (warp < 8) {
     // ================= compute warps: the chain =================
-    bool ok = true;
+    bool ok = nchunks == 0 || warp_wait(&s.full[0], 0);      // the first chunk's GL and UT rows are there
+    float gl = (ok && nchunks > 0) ? s.st[0].GL[k] : 0.f;    // Gam_last[k] of the current chunk (read one chunk ahead, see below)
     for (int i = 0; i < nchunks && ok; ++i) {
       VsStage<VS>& d = s.st[i & 1];
       long long* const dbg = (i == 8) ? p.dbg : nullptr;      // development aid: clocks of a steady-state chunk
       KDA_DBG_CLOCK(dbg, 48);
-      if (__any_sync(0xffffffffu, s.dead != 0)) break;
-      if (!warp_wait(&s.full[i & 1], (i >> 1) & 1)) { ok = false; break; }      // GL and the UT rows are there
       KDA_DBG_CLOCK(dbg, 49);
 
       // ---- state pass ---------------------------------------------------------------------------------------------------
       uint4 hp[HC / 8];                                  // this thread's bf16 state values (kept for the HS tile)
       {
-        const float gl = d.GL[k];
 #pragma unroll
         for (int g = 0; g < HC / 16; ++g) {
           float x[16];
@@ -261,6 +259,13 @@ __global__ void __launch_bounds__(VS_THREADS, 1) kda_chunk_scan_vs_kernel(const 
         if (lane == 0) mbar_arrive(&s.sgReady);
       }
       KDA_DBG_CLOCK(dbg, 54);
+      // beside products 2 (nothing else to do until they complete): make sure the next chunk's operand stage has landed
+      // and fetch its Gam_last, so that the next state pass starts without a look at a barrier or a shared-memory read;
+      // a raised s.dead is noticed here as well
+      if (i + 1 < nchunks) {
+        if (__any_sync(0xffffffffu, s.dead != 0) || !warp_wait(&s.full[(i + 1) & 1], ((i + 1) >> 1) & 1)) { ok = false; break; }
+        gl = s.st[(i + 1) & 1].GL[k];
+      }
       if (!warp_wait(&s.barM, 1)) { ok = false; break; }      // products 2 complete: the state is that of the next chunk's start
       umma::fence_after_sync();
       KDA_DBG_CLOCK(dbg, 55);
@@ -286,14 +291,13 @@ __global__ void __launch_bounds__(VS_THREADS, 1) kda_chunk_scan_vs_kernel(const 
       constexpr uint32_t id1 = umma::instr_desc(64, VS, false, true);      // A = w / qg / Aqk rows t (K-major), B = h rows k / v_new rows j (MN-major)
       constexpr uint32_t idH = umma::instr_desc(128, VS, true, true);      // A = kg rows t, two spans of 64 k (MN-major); B = v_new rows t
       const uint64_t dHb = umma::desc_mnmajor(smem_u32(s.Hb), 0, 16384u), dVN = umma::desc_mnmajor(smem_u32(s.VN), 0, 16384u);
-      bool ok = true;
-      for (int i = 0; i < nchunks; ++i) {
+      bool ok = nchunks == 0 || mbar_wait(&s.full[0], 0);
+      for (int i = 0; i < nchunks && ok; ++i) {
         VsStage<VS>& d = s.st[i & 1];
         const uint32_t to = tb + C_O + VS * (i & 1);
         const uint64_t dW = umma::desc_kmajor(smem_u32(d.W), 0), dQ = umma::desc_kmajor(smem_u32(d.QG), 0);
         const uint64_t dKG = umma::desc_mnmajor(smem_u32(d.KG), 0, 8192u), dAQ = umma::desc_kmajor(smem_u32(d.AQK), 0);
-        if (s.dead) break;
-        if (!mbar_wait(&s.full[i & 1], (i >> 1) & 1) || !mbar_wait(&s.stReady, i & 1)) { ok = false; break; }
+        if (!mbar_wait(&s.stReady, i & 1)) { ok = false; break; }      // (the stage itself was waited for one chunk ahead)
         umma::fence_after_sync();
         // products 1: v_part = w h (k-steps 0..3 in the first sub-tile of W, 4..7 in the second)
         umma::mma4<umma::KSTEP_KMAJOR, umma::KSTEP_MNMAJOR>(tb + C_VN, dW, dHb, id1, 0);
@@ -310,6 +314,8 @@ __global__ void __launch_bounds__(VS_THREADS, 1) kda_chunk_scan_vs_kernel(const 
         umma::commit(&s.barM);
         umma::mma4<umma::KSTEP_KMAJOR, umma::KSTEP_MNMAJOR>(to, dAQ, dVN, id1, 1);
         umma::commit(&s.barO[i & 1]);      // every product of this chunk is complete when this fires: o is final, the stage is free
+        // off the chain: the next chunk's operand stage has landed; somebody gave up?
+        if (s.dead || (i + 1 < nchunks && !mbar_wait(&s.full[(i + 1) & 1], ((i + 1) >> 1) & 1))) { ok = s.dead == 0 ? false : ok; break; }
       }
       if (!ok) {
         s.dead = 1;
