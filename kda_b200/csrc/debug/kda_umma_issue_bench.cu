@@ -153,7 +153,8 @@ extern "C" __attribute__((visibility("default"))) int kda_b200_debug_umma_issue_
 // cycles per round trip over `rounds` rounds, measured by the compute warp.
 namespace kda {
 
-__global__ void __launch_bounds__(64, 1) umma_roundtrip_kernel(long long* __restrict__ out, int nmma, int rounds, unsigned* __restrict__ status) {
+__global__ void __launch_bounds__(64, 1) umma_roundtrip_kernel(long long* __restrict__ out, int nmma, int rounds, unsigned* __restrict__ status,
+                                                               int variant, int extra) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* barX = reinterpret_cast<uint64_t*>(base + 65536);
@@ -172,8 +173,12 @@ __global__ void __launch_bounds__(64, 1) umma_roundtrip_kernel(long long* __rest
   __syncthreads();
   umma::fence_after_sync();
   const uint32_t taddr = *slot;
-  const uint32_t idesc = umma::instr_desc(64, 32, false, true);
-  const uint64_t dA = umma::desc_kmajor(smem_u32(base), 0), dB = umma::desc_mnmajor(smem_u32(base + 32768), 0, 16384u);
+  // variant 0: M=64, A K-major (the shape of the sliced scans' products 1); variant 1: M=128, A MN-major in two spans of 64
+  // (their products 2: kg^T read from a [64 t][128 k] tile)
+  const uint32_t idesc = variant ? umma::instr_desc(128, 32, true, true) : umma::instr_desc(64, 32, false, true);
+  const uint64_t dA = variant ? umma::desc_mnmajor(smem_u32(base), 0, 8192u) : umma::desc_kmajor(smem_u32(base), 0);
+  const uint64_t dB = umma::desc_mnmajor(smem_u32(base + 32768), 0, 16384u);
+  const uint64_t dB0k = umma::desc_kmajor(smem_u32(base + 16384), 0);
   bool ok = true;
   if (warp == 0) {
     const long long t0 = clock64();
@@ -193,9 +198,17 @@ __global__ void __launch_bounds__(64, 1) umma_roundtrip_kernel(long long* __rest
     for (int r = 0; r < rounds && ok; ++r) {
       ok = mbar_wait(barX, r & 1);
       umma::fence_after_sync();
-      if (nmma >= 4) umma::mma4<umma::KSTEP_KMAJOR, umma::KSTEP_MNMAJOR>(taddr, dA, dB, idesc, 0);
-      if (nmma >= 8) umma::mma4<umma::KSTEP_KMAJOR, umma::KSTEP_MNMAJOR>(taddr, dA + 8u, dB + 4u * umma::KSTEP_MNMAJOR, idesc, 1);
+      if (variant) {
+        if (nmma >= 4) umma::mma4<umma::KSTEP_MNMAJOR, umma::KSTEP_MNMAJOR>(taddr, dA, dB, idesc, 0);
+      } else {
+        if (nmma >= 4) umma::mma4<umma::KSTEP_KMAJOR, umma::KSTEP_MNMAJOR>(taddr, dA, dB, idesc, 0);
+        if (nmma >= 8) umma::mma4<umma::KSTEP_KMAJOR, umma::KSTEP_MNMAJOR>(taddr, dA + 8u, dB + 4u * umma::KSTEP_MNMAJOR, idesc, 1);
+      }
       umma::commit(barY);
+      // `extra` products into another accumulator behind the commit (the way the scans issue their o products behind the
+      // chain's): does the next round's hand-over find the issuing thread late?
+      if (extra >= 4) umma::mma4<umma::KSTEP_KMAJOR, umma::KSTEP_MNMAJOR>(taddr + 32, dB0k, dB, umma::instr_desc(64, 32, false, true), 0);
+      if (extra >= 8) umma::mma4<umma::KSTEP_KMAJOR, umma::KSTEP_MNMAJOR>(taddr + 32, dB0k + 8u, dB + 4u * umma::KSTEP_MNMAJOR, umma::instr_desc(64, 32, false, true), 1);
     }
     if (!ok) atomicOr(status, 2u);
   }
@@ -207,12 +220,14 @@ __global__ void __launch_bounds__(64, 1) umma_roundtrip_kernel(long long* __rest
 }  // namespace kda
 
 extern "C" __attribute__((visibility("default"))) int kda_b200_debug_umma_roundtrip(long long* out, int nmma, int rounds, unsigned* status,
-                                                                                    void* stream) {
+                                                                                    void* stream, int variant, int extra) {
   if (!out || !status) return KDA_E_NULL;
-  if ((nmma != 0 && nmma != 4 && nmma != 8) || rounds < 1 || rounds > 4096) return KDA_E_SHAPE;
+  if ((nmma != 0 && nmma != 4 && nmma != 8) || rounds < 1 || rounds > 4096 || (variant != 0 && variant != 1) || (variant == 1 && nmma == 8) ||
+      (extra != 0 && extra != 4 && extra != 8))
+    return KDA_E_SHAPE;
   const int smem = 65536 + 64 + 1024;
   cudaError_t e = cudaFuncSetAttribute(kda::umma_roundtrip_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return static_cast<int>(e);
-  kda::umma_roundtrip_kernel<<<1, 64, smem, static_cast<cudaStream_t>(stream)>>>(out, nmma, rounds, status);
+  kda::umma_roundtrip_kernel<<<1, 64, smem, static_cast<cudaStream_t>(stream)>>>(out, nmma, rounds, status, variant, extra);
   return static_cast<int>(cudaGetLastError());
 }
