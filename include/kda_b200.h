@@ -31,7 +31,7 @@ extern "C" {
 #pragma GCC visibility push(default) /* the entry points below are the library's only exports */
 #endif
 
-#define KDA_B200_ABI_VERSION 7
+#define KDA_B200_ABI_VERSION 8
 #define KDA_CHUNK 64 /* tokens per chunk of the chunked kernels */
 
 /* io_dtype of q, k, v, o and of their gradients */
@@ -161,6 +161,11 @@ typedef struct kda_chunk_args {
   int32_t scan_slices;         /* CTAs per (sequence, head) of the two state scans: 0 = chosen from N * H and the SM count (a call with
                                   at most a quarter as many units as SMs cuts every unit into 4 slices of 32 value columns, which
                                   shortens the chunk-to-chunk chain); 1 or 4 force a layout.  The results do not depend on it. */
+  int32_t safe_gate;           /* nonzero: the caller promises g >= -5 for every token and channel (fla's safe_gate,
+                                  fla/ops/kda/chunk.py:235-246, chunk_intra.py:659-761).  The forward then computes the diagonal 16 x 16
+                                  blocks of the intra-chunk products on tensor cores too, factored around each block's middle row,
+                                  instead of pairwise on CUDA cores.  With gates outside the bound the result may overflow; 0 is safe
+                                  for any gate. */
 } kda_chunk_args;
 
 /* Upper bound on the number of chunks: every sequence adds at most one partial chunk. */

@@ -11,7 +11,7 @@ LIB_PATH = os.path.join(PKG, "libkda_b200.so")
 
 KDA_BF16, KDA_FP32 = 0, 1
 NOALLOC_SCRATCH_BYTES = 32 << 20
-ABI_VERSION = 7
+ABI_VERSION = 8
 
 
 class RecurrentArgs(C.Structure):
@@ -40,7 +40,7 @@ class ChunkArgs(C.Structure):
         ("bwd_workspace", C.c_void_p), ("bwd_workspace_bytes", C.c_size_t),
         ("tokens", C.c_int64), ("N", C.c_int32), ("H", C.c_int32), ("K", C.c_int32), ("V", C.c_int32),
         ("io_dtype", C.c_int32), ("use_qk_l2norm", C.c_int32), ("save_for_backward", C.c_int32),
-        ("scale", C.c_float), ("HQ", C.c_int32), ("scan_slices", C.c_int32),
+        ("scale", C.c_float), ("HQ", C.c_int32), ("scan_slices", C.c_int32), ("safe_gate", C.c_int32),
     ]
 
 

@@ -176,8 +176,75 @@ __device__ __forceinline__ void diag_decode(const int g, const int L, int& row, 
   col = 8 * u + (is_kk ? off - t - 1 : off);
 }
 
+// One 16 x 16 block of Aqk / Akk on tensor cores: rows row0 .. row0 + 15, columns col0 .. col0 + 15, the decay factored
+// around row `ref`:  2^(G_t - G_ref) on the row side, 2^(G_ref - G_j) on the column side.  Off-diagonal blocks take ref = row0
+// (both factors <= 1: safe for any gate).  DIAG: a diagonal block (col0 == row0) with ref = its middle row -- only valid when
+// the caller has promised bounded gates (safe_gate: at least -5 per token), which keeps both factors within 2^58.
+template <bool DIAG>
+__device__ __forceinline__ void prep_block16(PrepSmem& s, const float scale, const int row0, const int col0, const int ref, const int lane) {
+const int gid = lane >> 2, tig = lane & 3;
+const int ta = row0 + gid, tb = ta + 8;
+const int ja = col0 + gid, jb = ja + 8;
+const int r0 = ref;
+  float cq[2][4], ck[2][4];
+#pragma unroll
+  for (int n = 0; n < 2; ++n) cq[n][0] = cq[n][1] = cq[n][2] = cq[n][3] = ck[n][0] = ck[n][1] = ck[n][2] = ck[n][3] = 0.f;
+#pragma unroll 2
+  for (int ks = 0; ks < 8; ++ks) {
+    const int k0 = ks * 16 + tig * 2, k1 = k0 + 8;
+    const float2 R0 = *reinterpret_cast<const float2*>(&s.G[r0 * GS + k0]);
+    const float2 R1 = *reinterpret_cast<const float2*>(&s.G[r0 * GS + k1]);
+    const float2 Ga0 = *reinterpret_cast<const float2*>(&s.G[ta * GS + k0]);
+    const float2 Ga1 = *reinterpret_cast<const float2*>(&s.G[ta * GS + k1]);
+    const float2 Gb0 = *reinterpret_cast<const float2*>(&s.G[tb * GS + k0]);
+    const float2 Gb1 = *reinterpret_cast<const float2*>(&s.G[tb * GS + k1]);
+    const float ea0x = ex2(Ga0.x - R0.x), ea0y = ex2(Ga0.y - R0.y), ea1x = ex2(Ga1.x - R1.x), ea1y = ex2(Ga1.y - R1.y);
+    const float eb0x = ex2(Gb0.x - R0.x), eb0y = ex2(Gb0.y - R0.y), eb1x = ex2(Gb1.x - R1.x), eb1y = ex2(Gb1.y - R1.y);
+    const float2 qa0 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.q[ta * QS + k0]));
+    const float2 qa1 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.q[ta * QS + k1]));
+    const float2 qb0 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.q[tb * QS + k0]));
+    const float2 qb1 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.q[tb * QS + k1]));
+    const float2 ka0 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.k[ta * QS + k0]));
+    const float2 ka1 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.k[ta * QS + k1]));
+    const float2 kb0 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.k[tb * QS + k0]));
+    const float2 kb1 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.k[tb * QS + k1]));
+    uint32_t aq[4], ak[4];
+    aq[0] = pack_bf16(qa0.x * ea0x, qa0.y * ea0y); aq[1] = pack_bf16(qb0.x * eb0x, qb0.y * eb0y);
+    aq[2] = pack_bf16(qa1.x * ea1x, qa1.y * ea1y); aq[3] = pack_bf16(qb1.x * eb1x, qb1.y * eb1y);
+    ak[0] = pack_bf16(ka0.x * ea0x, ka0.y * ea0y); ak[1] = pack_bf16(kb0.x * eb0x, kb0.y * eb0y);
+    ak[2] = pack_bf16(ka1.x * ea1x, ka1.y * ea1y); ak[3] = pack_bf16(kb1.x * eb1x, kb1.y * eb1y);
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {
+      const int j = n ? jb : ja;
+      const float2 Gj0 = *reinterpret_cast<const float2*>(&s.G[j * GS + k0]);
+      const float2 Gj1 = *reinterpret_cast<const float2*>(&s.G[j * GS + k1]);
+      const float2 kj0 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.k[j * QS + k0]));
+      const float2 kj1 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.k[j * QS + k1]));
+      const uint32_t b0 = pack_bf16(kj0.x * ex2(R0.x - Gj0.x), kj0.y * ex2(R0.y - Gj0.y));
+      const uint32_t b1 = pack_bf16(kj1.x * ex2(R1.x - Gj1.x), kj1.y * ex2(R1.y - Gj1.y));
+      mma16816(cq[n], aq, b0, b1);
+      mma16816(ck[n], ak, b0, b1);
+    }
+  }
+#pragma unroll
+  for (int n = 0; n < 2; ++n) {
+    const int col = col0 + n * 8 + tig * 2;
+    if (DIAG) {      // a diagonal block: Aqk keeps j <= t, the raw k-k products j < t, the rest is zero
+      cq[n][0] = (col <= ta) ? cq[n][0] : 0.f; cq[n][1] = (col + 1 <= ta) ? cq[n][1] : 0.f;
+      cq[n][2] = (col <= tb) ? cq[n][2] : 0.f; cq[n][3] = (col + 1 <= tb) ? cq[n][3] : 0.f;
+      ck[n][0] = (col < ta) ? ck[n][0] : 0.f; ck[n][1] = (col + 1 < ta) ? ck[n][1] : 0.f;
+      ck[n][2] = (col < tb) ? ck[n][2] : 0.f; ck[n][3] = (col + 1 < tb) ? ck[n][3] : 0.f;
+    }
+    *reinterpret_cast<uint32_t*>(&s.Aqk[ta * TS + col]) = pack_bf16(scale * cq[n][0], scale * cq[n][1]);
+    *reinterpret_cast<uint32_t*>(&s.Aqk[tb * TS + col]) = pack_bf16(scale * cq[n][2], scale * cq[n][3]);
+    *reinterpret_cast<float2*>(&s.Akk[ta * AS + col]) = make_float2(ck[n][0], ck[n][1]);
+    *reinterpret_cast<float2*>(&s.Akk[tb * AS + col]) = make_float2(ck[n][2], ck[n][3]);
+  }
+}
+
 // KEEP_QN: also leave the L2-normalised q, k and their reciprocal norms in the workspace (training with use_l2norm).
-template <bool KEEP_QN>
+// SAFE: the caller promises bounded gates (safe_gate); the diagonal 16 x 16 blocks then go to the tensor cores as well.
+template <bool KEEP_QN, bool SAFE>
 __global__ void __launch_bounds__(256, 2) kda_chunk_prepare_kernel(const PrepParams p) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   PrepSmem& s = *reinterpret_cast<PrepSmem*>(smem_raw);
@@ -265,6 +332,7 @@ __global__ void __launch_bounds__(256, 2) kda_chunk_prepare_kernel(const PrepPar
   // ---- P3a: diagonal 8x8 blocks, pairwise decay as running products (never a factorisation there: range-safe).
   // Warp = (block, key half).  The halves meet in the v buffer, whose load is issued only afterwards.
   {
+    if constexpr (!SAFE) {
     const int b = warp & 3, hh = warp >> 2, r0 = 16 * b;
     float res[DIAG_GROUPS];
     prep_diag_half(s, b, hh, lane, res);
@@ -288,6 +356,7 @@ __global__ void __launch_bounds__(256, 2) kda_chunk_prepare_kernel(const PrepPar
       }
     }
     __syncthreads();
+    }      // !SAFE
     for (int i = tid; i < C * 16; i += 256) {       // v: needed by the last phase only
       const int r = i >> 4, pc = i & 15;
       const bool ok = r < len;
@@ -305,55 +374,13 @@ __global__ void __launch_bounds__(256, 2) kda_chunk_prepare_kernel(const PrepPar
   if (warp < 6) {
     const int I = (warp < 1) ? 1 : (warp < 3 ? 2 : 3);
     const int np = (warp < 1) ? 0 : (warp < 3 ? warp - 1 : warp - 3);
-    const int r0 = 16 * I, ta = r0 + gid, tb = ta + 8;
-    const int ja = np * 16 + gid, jb = ja + 8;
-    float cq[2][4], ck[2][4];
-#pragma unroll
-    for (int n = 0; n < 2; ++n) cq[n][0] = cq[n][1] = cq[n][2] = cq[n][3] = ck[n][0] = ck[n][1] = ck[n][2] = ck[n][3] = 0.f;
-#pragma unroll 2
-    for (int ks = 0; ks < 8; ++ks) {
-      const int k0 = ks * 16 + tig * 2, k1 = k0 + 8;
-      const float2 R0 = *reinterpret_cast<const float2*>(&s.G[r0 * GS + k0]);
-      const float2 R1 = *reinterpret_cast<const float2*>(&s.G[r0 * GS + k1]);
-      const float2 Ga0 = *reinterpret_cast<const float2*>(&s.G[ta * GS + k0]);
-      const float2 Ga1 = *reinterpret_cast<const float2*>(&s.G[ta * GS + k1]);
-      const float2 Gb0 = *reinterpret_cast<const float2*>(&s.G[tb * GS + k0]);
-      const float2 Gb1 = *reinterpret_cast<const float2*>(&s.G[tb * GS + k1]);
-      const float ea0x = ex2(Ga0.x - R0.x), ea0y = ex2(Ga0.y - R0.y), ea1x = ex2(Ga1.x - R1.x), ea1y = ex2(Ga1.y - R1.y);
-      const float eb0x = ex2(Gb0.x - R0.x), eb0y = ex2(Gb0.y - R0.y), eb1x = ex2(Gb1.x - R1.x), eb1y = ex2(Gb1.y - R1.y);
-      const float2 qa0 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.q[ta * QS + k0]));
-      const float2 qa1 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.q[ta * QS + k1]));
-      const float2 qb0 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.q[tb * QS + k0]));
-      const float2 qb1 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.q[tb * QS + k1]));
-      const float2 ka0 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.k[ta * QS + k0]));
-      const float2 ka1 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.k[ta * QS + k1]));
-      const float2 kb0 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.k[tb * QS + k0]));
-      const float2 kb1 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.k[tb * QS + k1]));
-      uint32_t aq[4], ak[4];
-      aq[0] = pack_bf16(qa0.x * ea0x, qa0.y * ea0y); aq[1] = pack_bf16(qb0.x * eb0x, qb0.y * eb0y);
-      aq[2] = pack_bf16(qa1.x * ea1x, qa1.y * ea1y); aq[3] = pack_bf16(qb1.x * eb1x, qb1.y * eb1y);
-      ak[0] = pack_bf16(ka0.x * ea0x, ka0.y * ea0y); ak[1] = pack_bf16(kb0.x * eb0x, kb0.y * eb0y);
-      ak[2] = pack_bf16(ka1.x * ea1x, ka1.y * ea1y); ak[3] = pack_bf16(kb1.x * eb1x, kb1.y * eb1y);
-#pragma unroll
-      for (int n = 0; n < 2; ++n) {
-        const int j = n ? jb : ja;
-        const float2 Gj0 = *reinterpret_cast<const float2*>(&s.G[j * GS + k0]);
-        const float2 Gj1 = *reinterpret_cast<const float2*>(&s.G[j * GS + k1]);
-        const float2 kj0 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.k[j * QS + k0]));
-        const float2 kj1 = unpack_bf16(*reinterpret_cast<const uint32_t*>(&s.k[j * QS + k1]));
-        const uint32_t b0 = pack_bf16(kj0.x * ex2(R0.x - Gj0.x), kj0.y * ex2(R0.y - Gj0.y));
-        const uint32_t b1 = pack_bf16(kj1.x * ex2(R1.x - Gj1.x), kj1.y * ex2(R1.y - Gj1.y));
-        mma16816(cq[n], aq, b0, b1);
-        mma16816(ck[n], ak, b0, b1);
-      }
-    }
-#pragma unroll
-    for (int n = 0; n < 2; ++n) {
-      const int col = np * 16 + n * 8 + tig * 2;
-      *reinterpret_cast<uint32_t*>(&s.Aqk[ta * TS + col]) = pack_bf16(p.scale * cq[n][0], p.scale * cq[n][1]);
-      *reinterpret_cast<uint32_t*>(&s.Aqk[tb * TS + col]) = pack_bf16(p.scale * cq[n][2], p.scale * cq[n][3]);
-      *reinterpret_cast<float2*>(&s.Akk[ta * AS + col]) = make_float2(ck[n][0], ck[n][1]);
-      *reinterpret_cast<float2*>(&s.Akk[tb * AS + col]) = make_float2(ck[n][2], ck[n][3]);
+    prep_block16<false>(s, p.scale, 16 * I, 16 * np, 16 * I, lane);
+  } else if constexpr (SAFE) {
+    // bounded gates: the four diagonal blocks whole, factored around their middle row (no pairwise phase at all)
+#pragma unroll 1
+    for (int bb = 0; bb < 2; ++bb) {
+      const int b = 2 * (warp - 6) + bb;
+      prep_block16<true>(s, p.scale, 16 * b, 16 * b, 16 * b + 8, lane);
     }
   } else {
 #pragma unroll 1
@@ -636,7 +663,8 @@ static DeviceOnce g_prepare_once;
 static int set_attrs() {      // KDA_OK, a negative KDA_E_* or a positive cudaError_t
   return g_prepare_once.run([] {
     cudaError_t e = cudaSuccess;
-    for (auto fn : {kda_chunk_prepare_kernel<false>, kda_chunk_prepare_kernel<true>}) {
+    for (auto fn : {kda_chunk_prepare_kernel<false, false>, kda_chunk_prepare_kernel<true, false>, kda_chunk_prepare_kernel<false, true>,
+                    kda_chunk_prepare_kernel<true, true>}) {
       if (e == cudaSuccess) e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(PrepSmem)));
       if (e == cudaSuccess) e = cudaFuncSetAttribute(fn, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     }
@@ -720,8 +748,14 @@ extern "C" int kda_chunk_fwd(const kda_chunk_args* args, void* stream) {
   pp.HQ = a.HQ > 0 ? a.HQ : a.H; pp.grp = a.H / pp.HQ;
   pp.QN = keep_qn ? w.QN : nullptr; pp.KN = keep_qn ? w.KN : nullptr; pp.RSTD = keep_qn ? w.RSTD : nullptr;
   pp.qrows = static_cast<long long>(a.tokens) * pp.HQ;
-  if (keep_qn) kda_chunk_prepare_kernel<true><<<dim3(NTmax, a.H), 256, sizeof(PrepSmem), st>>>(pp);
-  else kda_chunk_prepare_kernel<false><<<dim3(NTmax, a.H), 256, sizeof(PrepSmem), st>>>(pp);
+  const dim3 pgrid(NTmax, a.H);
+  if (a.safe_gate) {
+    if (keep_qn) kda_chunk_prepare_kernel<true, true><<<pgrid, 256, sizeof(PrepSmem), st>>>(pp);
+    else kda_chunk_prepare_kernel<false, true><<<pgrid, 256, sizeof(PrepSmem), st>>>(pp);
+  } else {
+    if (keep_qn) kda_chunk_prepare_kernel<true, false><<<pgrid, 256, sizeof(PrepSmem), st>>>(pp);
+    else kda_chunk_prepare_kernel<false, false><<<pgrid, 256, sizeof(PrepSmem), st>>>(pp);
+  }
   if ((e = cudaGetLastError()) != cudaSuccess) return static_cast<int>(e);
   prof_mark(prof, KDA_STAGE_PREPARE, st);
 

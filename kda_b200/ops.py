@@ -345,7 +345,8 @@ def _chunk_args(q, k, v, g, beta, h0, cu, o, ht, ws, N, H, K, V, tokens, l2, sav
         q=_ptr(q), k=_ptr(k), v=_ptr(v), g=_ptr(g), beta=_ptr(beta), h0=_ptr(h0), cu_seqlens=_ptr(cu),
         o=_ptr(o), ht=_ptr(ht), workspace=_ptr(ws), workspace_bytes=ws.numel() if ws is not None else 0,
         tokens=tokens, N=N, H=H, K=K, V=V, io_dtype=_lib.KDA_BF16, use_qk_l2norm=int(l2),
-        save_for_backward=int(save), scale=float(scale), HQ=q.shape[-2], scan_slices=int(SCAN_SLICES))
+        save_for_backward=int(save), scale=float(scale), HQ=q.shape[-2], scan_slices=int(SCAN_SLICES),
+        safe_gate=int(bool(extra.pop("safe_gate", False))))
     for name, t in extra.items():
         if name == "bwd_ws":
             a.bwd_workspace = _ptr(t)
@@ -361,7 +362,7 @@ class ChunkKDAFunction(torch.autograd.Function):
     inputs and recomputes; with 180 GB of HBM the tiles are kept instead)."""
 
     @staticmethod
-    def forward(ctx, q, k, v, g, beta, scale, initial_state, output_final_state, use_l2norm, cu_seqlens):
+    def forward(ctx, q, k, v, g, beta, scale, initial_state, output_final_state, use_l2norm, cu_seqlens, safe_gate=False):
         B, T, HQ, K = q.shape
         H, V = v.shape[-2], v.shape[-1]          # H counts value heads; q and k may have fewer (grouped value heads)
         dev = q.device
@@ -381,7 +382,7 @@ class ChunkKDAFunction(torch.autograd.Function):
         ws = torch.empty(lib.kda_chunk_workspace_bytes(tokens, N, H, K, V, save), dtype=torch.uint8, device=dev)
         o = torch.empty_like(v)
         ht = torch.empty(N, H, K, V, dtype=torch.float32, device=dev) if output_final_state else None
-        args = _chunk_args(q, k, v, g32, beta32, h0, cu, o, ht, ws, N, H, K, V, tokens, use_l2norm, save, scale)
+        args = _chunk_args(q, k, v, g32, beta32, h0, cu, o, ht, ws, N, H, K, V, tokens, use_l2norm, save, scale, safe_gate=safe_gate)
         with torch.cuda.device(dev):
             _lib.check(lib.kda_chunk_fwd(C.byref(args), _stream(dev)), "kda_chunk_fwd")
             if _checked():
@@ -411,10 +412,11 @@ class ChunkKDAFunction(torch.autograd.Function):
             _lib.check(lib.kda_chunk_bwd(C.byref(args), _stream(dev)), "kda_chunk_bwd")
             if _checked():
                 _lib.check_chunk_status(ws.data_ptr(), "kda_chunk_bwd")
-        return dq, dk, dv, dg.to(g_dtype), dbeta.to(beta_dtype), None, dh0, None, None, None
+        return dq, dk, dv, dg.to(g_dtype), dbeta.to(beta_dtype), None, dh0, None, None, None, None
 
 
-def _chunk_fwd_with_states(q, k, v, g, beta, scale, initial_state, output_final_state, use_l2norm, cu_seqlens, chunk_size=CHUNK):
+def _chunk_fwd_with_states(q, k, v, g, beta, scale, initial_state, output_final_state, use_l2norm, cu_seqlens, chunk_size=CHUNK,
+                           safe_gate=False):
     """Forward for inference engines (fla/ops/kda/chunk.py:95-98): also returns h, the state at the start of every
     chunk of `chunk_size` tokens, [B, NT, H, K, V] bf16 (NT chunks per sequence; with cu_seqlens B = 1 and NT counts all
     chunks).  The kernels tile by 64 tokens and keep the state at the start of every 64-token chunk; for chunk_size = 32
@@ -440,7 +442,7 @@ def _chunk_fwd_with_states(q, k, v, g, beta, scale, initial_state, output_final_
     o = torch.empty_like(v)
     ht = torch.empty(N, H, K, V, dtype=torch.float32, device=dev) if output_final_state else None
     hbuf = torch.empty(lib.kda_chunk_max_chunks(tokens, N), H, K, V, dtype=torch.bfloat16, device=dev)
-    args = _chunk_args(q, k, v, g32, beta32, h0, cu, o, ht, ws, N, H, K, V, tokens, use_l2norm, True, scale)
+    args = _chunk_args(q, k, v, g32, beta32, h0, cu, o, ht, ws, N, H, K, V, tokens, use_l2norm, True, scale, safe_gate=safe_gate)
     with torch.cuda.device(dev):
         _lib.check(lib.kda_chunk_fwd(C.byref(args), _stream(dev)), "kda_chunk_fwd")
         _lib.check(lib.kda_chunk_export_states(_ptr(ws), ws.numel(), tokens, N, H, _ptr(hbuf), _stream(dev)), "kda_chunk_export_states")
@@ -500,8 +502,11 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
     tensor is [.., V, K] instead of [.., K, V].
 
     bf16 inputs with K = V = 128 take the chunked tensor-core kernels.  float32 inputs take the exact
-    token-recurrent fp32 kernel (forward only).  `safe_gate` and `disable_recompute` only select variants of the same
-    computation upstream and are accepted as no-ops (the kernels here are range-safe for any gate); `chunk_size` (32 or
+    token-recurrent fp32 kernel (forward only).  `safe_gate=True` is the caller's promise that every gate value is at least
+    -5 (fla/ops/kda/chunk.py:235-246); the forward then computes the diagonal 16 x 16 blocks of the intra-chunk products on
+    tensor cores as well (factored around each block's middle row) instead of pairwise, which is faster and only safe under
+    that bound; without it the kernels are range-safe for any gate.  `disable_recompute` only selects a variant of the
+    same computation upstream and is accepted as a no-op; `chunk_size` (32 or
     64) changes nothing but the spacing of the intermediate states (the kernels always tile by 64 tokens); options
     that change results and are not built raise.
     """
@@ -536,12 +541,12 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
         assert torch.is_inference_mode_enabled(), "return_intermediate_states is only allowed in inference mode"
         assert disable_recompute is False, "return_intermediate_states must be used with disable_recompute=False"
         o, ht, h = _chunk_fwd_with_states(q, k, v, g, beta, float(scale), initial_state, bool(output_final_state),
-                                          bool(use_qk_l2norm_in_kernel), cu_seqlens, chunk_size)
+                                          bool(use_qk_l2norm_in_kernel), cu_seqlens, chunk_size, bool(safe_gate))
         if transpose_state_layout:
             ht, h = (tr(ht).contiguous() if ht is not None else None), tr(h).contiguous()
         return o, ht, h
     o, ht = ChunkKDAFunction.apply(q, k, v, g, beta, float(scale), initial_state, bool(output_final_state),
-                                   bool(use_qk_l2norm_in_kernel), cu_seqlens)
+                                   bool(use_qk_l2norm_in_kernel), cu_seqlens, bool(safe_gate))
     if transpose_state_layout and ht is not None:
         ht = tr(ht).contiguous()
     return o, ht
