@@ -28,7 +28,9 @@ def _accepts(q, k, v, g, beta, initial_state=None, cp_context=None, **kwargs):
         return False, f"HV={v.shape[2]} is not a multiple of H={q.shape[2]}"
     if q.dtype == torch.bfloat16:
         if q.shape[-1] != 128 or v.shape[-1] != 128:
-            return False, f"kda_b200 bf16 kernels need K = V = 128, got K={q.shape[-1]}, V={v.shape[-1]}"
+            # kda_b200.chunk_kda itself also serves smaller heads (zero-padded to 128 channels); as a registered backend
+            # it only takes over the shape it is faster on
+            return False, f"kda_b200 bf16 kernels are built for K = V = 128, got K={q.shape[-1]}, V={v.shape[-1]}"
         return True, None
     if q.dtype == torch.float32:
         needs_grad = torch.is_grad_enabled() and any(

@@ -501,7 +501,8 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
     [B, NT, H, K, V] bf16 holds the state at the start of every chunk.  `transpose_state_layout`: every state
     tensor is [.., V, K] instead of [.., K, V].
 
-    bf16 inputs with K = V = 128 take the chunked tensor-core kernels.  float32 inputs take the exact
+    bf16 inputs with K, V <= 128 take the chunked tensor-core kernels (built for K = V = 128; smaller heads are
+    zero-padded to 128 channels, which leaves every result unchanged).  float32 inputs take the exact
     token-recurrent fp32 kernel (forward only).  `safe_gate=True` is the caller's promise that every gate value is at least
     -5 (fla/ops/kda/chunk.py:235-246); the forward then computes the diagonal 16 x 16 blocks of the intra-chunk products on
     tensor cores as well (factored around each block's middle row) instead of pairwise, which is faster and only safe under
@@ -530,23 +531,37 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
                                        output_final_state=output_final_state, inplace_final_state=False,
                                        use_qk_l2norm_in_kernel=use_qk_l2norm_in_kernel, cu_seqlens=cu_seqlens,
                                        transpose_state_layout=transpose_state_layout)
-    if K != 128 or V != 128:
-        raise NotImplementedError(f"kda_b200: the bf16 chunked kernels are built for K = V = 128, got K={K}, V={V}")
+    if K > 128 or V > 128:
+        raise NotImplementedError(f"kda_b200: the bf16 chunked kernels are built for head sizes up to 128, got K={K}, V={V}")
     # transposed state layout ([N, H, V, K]): the chunk kernels keep [N, H, K, V]; states cross the boundary once per
     # sequence, so they are transposed there (differentiably)
     tr = (lambda t: t.transpose(-1, -2)) if transpose_state_layout else (lambda t: t)
     if initial_state is not None:
         initial_state = tr(initial_state)
+    # Smaller heads ride on the 128-wide kernels: key channels padded with k = q = 0 and g = 0 (decay 1) and value
+    # channels padded with v = 0 never touch the real ones -- the padded state rows and columns stay zero, the row norms
+    # of q and k are unchanged -- so o, the states and (through autograd of the padding) every gradient are those of
+    # the unpadded problem.  `scale` was fixed from the real K above.
+    pad_k, pad_v = 128 - K, 128 - V
+    if pad_k or pad_v:
+        padk = lambda t: torch.nn.functional.pad(t, (0, pad_k))      # noqa: E731
+        q, k, g, v = padk(q), padk(k), padk(g), torch.nn.functional.pad(v, (0, pad_v))
+        if initial_state is not None:
+            initial_state = torch.nn.functional.pad(initial_state, (0, pad_v, 0, pad_k))
     if return_intermediate_states:
         assert torch.is_inference_mode_enabled(), "return_intermediate_states is only allowed in inference mode"
         assert disable_recompute is False, "return_intermediate_states must be used with disable_recompute=False"
         o, ht, h = _chunk_fwd_with_states(q, k, v, g, beta, float(scale), initial_state, bool(output_final_state),
                                           bool(use_qk_l2norm_in_kernel), cu_seqlens, chunk_size, bool(safe_gate))
+        if pad_k or pad_v:
+            o, ht, h = o[..., :V], (ht[..., :K, :V] if ht is not None else None), h[..., :K, :V]
         if transpose_state_layout:
             ht, h = (tr(ht).contiguous() if ht is not None else None), tr(h).contiguous()
         return o, ht, h
     o, ht = ChunkKDAFunction.apply(q, k, v, g, beta, float(scale), initial_state, bool(output_final_state),
                                    bool(use_qk_l2norm_in_kernel), cu_seqlens, bool(safe_gate))
+    if pad_k or pad_v:
+        o, ht = o[..., :V], (ht[..., :K, :V] if ht is not None else None)
     if transpose_state_layout and ht is not None:
         ht = tr(ht).contiguous()
     return o, ht
