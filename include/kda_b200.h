@@ -31,7 +31,7 @@ extern "C" {
 #pragma GCC visibility push(default) /* the entry points below are the library's only exports */
 #endif
 
-#define KDA_B200_ABI_VERSION 8
+#define KDA_B200_ABI_VERSION 9
 #define KDA_CHUNK 64 /* tokens per chunk of the chunked kernels */
 
 /* io_dtype of q, k, v, o and of their gradients */
@@ -108,6 +108,45 @@ int kda_recurrent_fwd(const kda_recurrent_args* args, void* stream);
  * the device: a diagnostic, not part of the step).  0: every wait completed; bit 0: a wait gave up and the outputs
  * of that step are incomplete. */
 int kda_recurrent_status(uint32_t* host_out);
+
+/* ------------------------------------------------------------------------------------------------
+ * Token-recurrent backward in fp32: the exact gradients of the recurrence kda_recurrent_fwd computes
+ * (fla/ops/kda/naive.py:12-66 differentiated), for training with float32 tensors.  Stands behind chunk_kda's
+ * autograd function when the inputs are float32.  Whole sequences from their initial states (no slots, no gate
+ * front end: g and beta are the activated fp32 values).  Deterministic: every sum has a fixed order.
+ * ------------------------------------------------------------------------------------------------ */
+typedef struct kda_recurrent_bwd_args {
+  const void* q;               /* [tokens, HQ, K] fp32 */
+  const void* k;               /* [tokens, HQ, K] fp32 */
+  const void* v;               /* [tokens, H, V]  fp32 */
+  const float* g;              /* [tokens, H, K] fp32 log-decay */
+  const float* beta;           /* [tokens, H]    fp32 */
+  const float* h0;             /* [N, H, K, V] fp32 or NULL */
+  const int32_t* cu_seqlens;   /* device [N+1] or NULL (then every sequence has T tokens) */
+  const void* d_o;             /* [tokens, H, V] fp32 */
+  const float* d_ht;           /* [N, H, K, V] fp32 or NULL */
+  void* dq;                    /* [tokens, HQ, K] fp32 (summed over each group of value heads) */
+  void* dk;                    /* [tokens, HQ, K] fp32 */
+  void* dv;                    /* [tokens, H, V]  fp32 */
+  float* dg;                   /* [tokens, H, K] fp32 */
+  float* dbeta;                /* [tokens, H]    fp32 */
+  float* dh0;                  /* [N, H, K, V] fp32 or NULL */
+  void* workspace;             /* >= kda_recurrent_bwd_workspace_bytes(..), 256-byte aligned */
+  size_t workspace_bytes;
+  int64_t tokens;
+  int32_t N;
+  int32_t T;                   /* tokens per sequence when cu_seqlens is NULL */
+  int32_t H, K, V;             /* K, V in {32, 64, 128} */
+  int32_t HQ;                  /* grouped value heads: heads of q and k; 0 or H: no grouping */
+  int32_t io_dtype;            /* KDA_FP32 */
+  int32_t use_qk_l2norm;       /* the forward normalised the rows of q and k; dq, dk go through that too */
+  float scale;
+} kda_recurrent_bwd_args;
+
+/* Scratch for kda_recurrent_bwd: per-value-head dq, dk, the state at the start of every 64-token chunk
+ * ((tokens / 64 + N + 1) x H x K x V x 4 bytes) and the per-token states of the chunks in flight. */
+size_t kda_recurrent_bwd_workspace_bytes(int64_t tokens, int32_t N, int32_t H, int32_t K, int32_t V);
+int kda_recurrent_bwd(const kda_recurrent_bwd_args* args, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Chunked forward / backward (chunk = 64 tokens), bf16 tensor-core path, K = V = 128.

@@ -11,7 +11,7 @@ LIB_PATH = os.path.join(PKG, "libkda_b200.so")
 
 KDA_BF16, KDA_FP32 = 0, 1
 NOALLOC_SCRATCH_BYTES = 32 << 20
-ABI_VERSION = 8
+ABI_VERSION = 9
 
 
 class RecurrentArgs(C.Structure):
@@ -44,6 +44,17 @@ class ChunkArgs(C.Structure):
     ]
 
 
+class RecurrentBwdArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("g", C.c_void_p), ("beta", C.c_void_p),
+        ("h0", C.c_void_p), ("cu_seqlens", C.c_void_p), ("d_o", C.c_void_p), ("d_ht", C.c_void_p),
+        ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p), ("dg", C.c_void_p), ("dbeta", C.c_void_p),
+        ("dh0", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("tokens", C.c_int64), ("N", C.c_int32), ("T", C.c_int32), ("H", C.c_int32), ("K", C.c_int32), ("V", C.c_int32),
+        ("HQ", C.c_int32), ("io_dtype", C.c_int32), ("use_qk_l2norm", C.c_int32), ("scale", C.c_float),
+    ]
+
+
 class GateArgs(C.Structure):
     _fields_ = [
         ("g_raw", C.c_void_p), ("A_log", C.c_void_p), ("dt_bias", C.c_void_p), ("beta_raw", C.c_void_p),
@@ -57,6 +68,7 @@ class GateArgs(C.Structure):
 
 EXPORTS = (
     "kda_b200_abi_version", "kda_b200_strerror", "kda_recurrent_fwd", "kda_recurrent_status",
+    "kda_recurrent_bwd_workspace_bytes", "kda_recurrent_bwd",
     "kda_chunk_max_chunks", "kda_chunk_workspace_bytes", "kda_chunk_bwd_workspace_bytes",
     "kda_chunk_fwd", "kda_chunk_bwd", "kda_chunk_status", "kda_chunk_fwd_noalloc", "kda_chunk_export_states",
     "kda_gate_bwd_workspace_bytes", "kda_gate_fwd", "kda_gate_bwd",
@@ -83,6 +95,10 @@ def load() -> C.CDLL:
     lib.kda_recurrent_fwd.argtypes = [C.POINTER(RecurrentArgs), C.c_void_p]
     lib.kda_recurrent_status.restype = C.c_int
     lib.kda_recurrent_status.argtypes = [C.POINTER(C.c_uint32)]
+    lib.kda_recurrent_bwd_workspace_bytes.restype = C.c_size_t
+    lib.kda_recurrent_bwd_workspace_bytes.argtypes = [C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32]
+    lib.kda_recurrent_bwd.restype = C.c_int
+    lib.kda_recurrent_bwd.argtypes = [C.POINTER(RecurrentBwdArgs), C.c_void_p]
     lib.kda_chunk_max_chunks.restype = C.c_int64
     lib.kda_chunk_max_chunks.argtypes = [C.c_int64, C.c_int32]
     lib.kda_chunk_workspace_bytes.restype = C.c_size_t

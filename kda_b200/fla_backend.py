@@ -36,7 +36,7 @@ def _accepts(q, k, v, g, beta, initial_state=None, cp_context=None, **kwargs):
         needs_grad = torch.is_grad_enabled() and any(
             t is not None and t.requires_grad for t in (q, k, v, g, beta, initial_state))
         if needs_grad:
-            return False, "kda_b200 float32 path is forward-only"
+            return False, "kda_b200 trains float32 tensors token by token (exact, slow); left to fla as a backend"
         if q.shape[-1] not in (32, 64, 128, 256) or v.shape[-1] % 32:
             return False, "kda_b200 float32 path needs K in {32,64,128,256} and V a multiple of 32"
         return True, None

@@ -336,6 +336,48 @@ def fused_recurrent_kda(q, k, v, g, beta, A_log=None, dt_bias=None, scale=None, 
                                    transpose_state_layout=transpose_state_layout)
 
 
+class RecurrentKDAFunction(torch.autograd.Function):
+    """float32 path of chunk_kda with gradients: forward by the token-recurrent fp32 kernel, backward by its exact
+    reverse-mode counterpart (`kda_recurrent_bwd`, fla/ops/kda/naive.py:12-66 differentiated).  K, V in {32, 64, 128}."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, g, beta, scale, initial_state, output_final_state, use_l2norm, cu_seqlens):
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        g32, beta32 = g.contiguous().float(), beta.contiguous().float()
+        h0 = initial_state.contiguous().float() if initial_state is not None else None
+        o, ht = fused_recurrent_kda_fwd(q, k, v, g32, beta32, initial_state=h0, scale=scale,
+                                        output_final_state=output_final_state, inplace_final_state=False,
+                                        use_qk_l2norm_in_kernel=use_l2norm, cu_seqlens=cu_seqlens)
+        cu = _as_i32(cu_seqlens, q.device) if cu_seqlens is not None else None
+        ctx.save_for_backward(q, k, v, g32, beta32, h0, cu)
+        ctx.meta = (float(scale), bool(use_l2norm), g.dtype, beta.dtype)
+        return o, ht
+
+    @staticmethod
+    def backward(ctx, do, dht):
+        q, k, v, g32, beta32, h0, cu = ctx.saved_tensors
+        scale, use_l2norm, g_dtype, beta_dtype = ctx.meta
+        B, T, HQ, K = q.shape
+        H, V = v.shape[-2], v.shape[-1]
+        N = B if cu is None else cu.numel() - 1
+        dev = q.device
+        lib = _lib.load()
+        do = do.contiguous().float()
+        dht = dht.contiguous().float() if dht is not None else None
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        dg, dbeta = torch.empty_like(g32), torch.empty_like(beta32)
+        dh0 = torch.empty(N, H, K, V, dtype=torch.float32, device=dev) if h0 is not None else None
+        ws = torch.empty(lib.kda_recurrent_bwd_workspace_bytes(B * T, N, H, K, V), dtype=torch.uint8, device=dev)
+        args = _lib.RecurrentBwdArgs(
+            q=_ptr(q), k=_ptr(k), v=_ptr(v), g=_ptr(g32), beta=_ptr(beta32), h0=_ptr(h0), cu_seqlens=_ptr(cu),
+            d_o=_ptr(do), d_ht=_ptr(dht), dq=_ptr(dq), dk=_ptr(dk), dv=_ptr(dv), dg=_ptr(dg), dbeta=_ptr(dbeta), dh0=_ptr(dh0),
+            workspace=_ptr(ws), workspace_bytes=ws.numel(), tokens=B * T, N=N, T=T, H=H, K=K, V=V, HQ=HQ,
+            io_dtype=_lib.KDA_FP32, use_qk_l2norm=int(use_l2norm), scale=scale)
+        with torch.cuda.device(dev):
+            _lib.check(lib.kda_recurrent_bwd(C.byref(args), _stream(dev)), "kda_recurrent_bwd")
+        return dq, dk, dv, dg.to(g_dtype), dbeta.to(beta_dtype), None, dh0, None, None, None
+
+
 # =================================================================================================
 # chunked forward / backward
 # =================================================================================================
@@ -503,7 +545,7 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
 
     bf16 inputs with K, V <= 128 take the chunked tensor-core kernels (built for K = V = 128; smaller heads are
     zero-padded to 128 channels, which leaves every result unchanged).  float32 inputs take the exact
-    token-recurrent fp32 kernel (forward only).  `safe_gate=True` is the caller's promise that every gate value is at least
+    token-recurrent fp32 kernels: forward for K in {32, 64, 128, 256}, with gradients for K, V in {32, 64, 128}.  `safe_gate=True` is the caller's promise that every gate value is at least
     -5 (fla/ops/kda/chunk.py:235-246); the forward then computes the diagonal 16 x 16 blocks of the intra-chunk products on
     tensor cores as well (factored around each block's middle row) instead of pairwise, which is faster and only safe under
     that bound; without it the kernels are range-safe for any gate.  `disable_recompute` only selects a variant of the
@@ -526,7 +568,12 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
     g, beta = _gate_front_end(g, beta, use_gate_in_kernel, use_beta_sigmoid_in_kernel, safe_gate, lower_bound, kwargs)
     if q.dtype == torch.float32:
         if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (q, k, v, g, beta, initial_state)):
-            raise NotImplementedError("kda_b200: the float32 path is forward-only; use bfloat16 inputs for training")
+            if K not in (32, 64, 128) or V not in (32, 64, 128) or return_intermediate_states:
+                raise NotImplementedError(f"kda_b200: float32 gradients need K, V in {{32, 64, 128}}, got K={K}, V={V}")
+            tr = (lambda t: t.transpose(-1, -2)) if transpose_state_layout else (lambda t: t)
+            o, ht = RecurrentKDAFunction.apply(q, k, v, g, beta, float(scale), tr(initial_state) if initial_state is not None else None,
+                                               bool(output_final_state), bool(use_qk_l2norm_in_kernel), cu_seqlens)
+            return o, (tr(ht).contiguous() if (transpose_state_layout and ht is not None) else ht)
         return fused_recurrent_kda_fwd(q, k, v, g, beta, initial_state=initial_state, scale=scale,
                                        output_final_state=output_final_state, inplace_final_state=False,
                                        use_qk_l2norm_in_kernel=use_qk_l2norm_in_kernel, cu_seqlens=cu_seqlens,

@@ -83,3 +83,43 @@ def test_decode_stays_inside_its_buffers(N, H, slots):
     if slots:
         rest = sorted(set(range(N + extra)) - set(idx.tolist()))
         assert all(bool((pool[i] == 3.0).all()) for i in rest)
+
+
+@pytest.mark.parametrize("lens,K,V", [([1], 128, 128), ([65], 64, 32), ([70, 0, 3, 129], 128, 128)])
+def test_fp32_recurrent_backward_stays_inside_its_buffers(lens, K, V):
+    """kda_recurrent_bwd through the C ABI with every output and its workspace between sentinel margins; the results
+    equal those of the operator's float32 autograd path."""
+    import ctypes as C
+    from kda_b200 import _lib, chunk_kda
+    from _abi import guarded_like
+    lib = _lib.load()
+    tokens, N, H = sum(lens), len(lens), 2
+    d = make_inputs(1, tokens, H, K, V, torch.float32, seed=800 + tokens, h0_std=0.1, n_states=N, backward=True)
+    d = {n: t.cuda().contiguous() for n, t in d.items()}
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32, device="cuda")
+    guards, out = [], {}
+    for name, ref in (("dq", d["q"]), ("dk", d["k"]), ("dv", d["v"]), ("dg", d["g"]), ("dbeta", d["beta"]), ("dh0", d["h0"])):
+        g, t = guarded_like(tuple(ref.shape), torch.float32)
+        guards.append((name, g))
+        out[name] = t
+    wsg, ws = guarded_like((lib.kda_recurrent_bwd_workspace_bytes(tokens, N, H, K, V),), torch.uint8)
+    guards.append(("workspace", wsg))
+    p = lambda t: C.c_void_p(t.data_ptr())      # noqa: E731
+    a = _lib.RecurrentBwdArgs(q=p(d["q"]), k=p(d["k"]), v=p(d["v"]), g=p(d["g"]), beta=p(d["beta"]), h0=p(d["h0"]), cu_seqlens=p(cu),
+                              d_o=p(d["do"]), d_ht=p(d["dht"]), dq=p(out["dq"]), dk=p(out["dk"]), dv=p(out["dv"]), dg=p(out["dg"]),
+                              dbeta=p(out["dbeta"]), dh0=p(out["dh0"]), workspace=p(ws), workspace_bytes=ws.numel(), tokens=tokens,
+                              N=N, T=0, H=H, K=K, V=V, HQ=H, io_dtype=_lib.KDA_FP32, use_qk_l2norm=0, scale=K ** -0.5)
+    _lib.check(lib.kda_recurrent_bwd(C.byref(a), C.c_void_p(torch.cuda.current_stream().cuda_stream)), "kda_recurrent_bwd")
+    torch.cuda.synchronize()
+    for name, g in guards:
+        assert g.margins_intact(), name
+    lv = {n: d[n].detach().clone().requires_grad_(True) for n in ("q", "k", "v", "g", "beta", "h0")}
+    o, ht = chunk_kda(lv["q"], lv["k"], lv["v"], lv["g"], lv["beta"], initial_state=lv["h0"], output_final_state=True, cu_seqlens=cu)
+    torch.autograd.backward([o, ht], [d["do"], d["dht"]])
+    for name, src in (("dq", "q"), ("dk", "k"), ("dv", "v"), ("dg", "g"), ("dbeta", "beta"), ("dh0", "h0")):
+        assert torch.equal(out[name], lv[src].grad), name
+    # argument errors launch nothing
+    a.K = 48
+    assert lib.kda_recurrent_bwd(C.byref(a), None) == -2
+    a.K, a.workspace_bytes = K, 16
+    assert lib.kda_recurrent_bwd(C.byref(a), None) == -5
