@@ -77,8 +77,11 @@ def _fixed_cu_seqlens(B: int, T: int, device) -> torch.Tensor:
     key = (B, T, str(device))
     cu = _cu_cache.get(key)
     if cu is None:
-        cu = torch.arange(0, (B + 1) * T, T, dtype=torch.int32, device=device) if T > 0 else \
-            torch.zeros(B + 1, dtype=torch.int32, device=device)
+        # a tensor made inside torch.inference_mode() cannot be saved for a later backward: the cached table must be an
+        # ordinary tensor whichever mode the first caller was in
+        with torch.inference_mode(False):
+            cu = torch.arange(0, (B + 1) * T, T, dtype=torch.int32, device=device) if T > 0 else \
+                torch.zeros(B + 1, dtype=torch.int32, device=device)
         if len(_cu_cache) > 64:
             _cu_cache.clear()
         _cu_cache[key] = cu

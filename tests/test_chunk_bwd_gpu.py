@@ -105,3 +105,16 @@ def test_chunk_bwd_persistent_tile_walk(l2):
     ref = recurrent_kda_grads(*(d[n][b:b + 1] for n in ("q", "k", "v", "g", "beta", "do", "dht")), initial_state=d["h0"][b:b + 1],
                               use_qk_l2norm=l2)
     check({n: got[n][b:b + 1] for n in NAMES}, ref)
+
+
+def test_training_after_an_inference_mode_call_of_the_same_shape():
+    """The per-shape table of sequence starts is cached; the copy made by a call under torch.inference_mode() must
+    still be usable by a later training call of the same shape (inference tensors cannot be saved for backward)."""
+    from kda_b200 import chunk_kda
+    d = make_inputs(2, 70, 1, 128, 128, torch.bfloat16, seed=35, h0_std=0.02, backward=True)
+    c = {n: t.cuda() for n, t in d.items()}
+    with torch.inference_mode():
+        o_inf, _ = chunk_kda(c["q"], c["k"], c["v"], c["g"], c["beta"], initial_state=c["h0"], output_final_state=True)
+    got = run_gpu(d)
+    assert torch.equal(got["o"], o_inf)
+    assert all(torch.isfinite(got[n]).all() for n in NAMES)
