@@ -467,19 +467,38 @@ def main():
                            int(os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local_rank]), args.clock_interval_ms)
     if rank == 0:
         sampler.start()          # returns once nvidia-smi delivers samples
+    # the warm-up keeps each step's results alive until the next step has produced its own, exactly as the timed loop
+    # does: otherwise the caching allocator meets the second set of output and workspace blocks only inside the timed
+    # region, and its cudaMalloc calls (milliseconds, longer when several ranks of a box allocate at once) stall the host
+    # while the GPU runs dry
+    outs = None
     for _ in range(args.warmup):
-        step()
+        outs = step()
     barrier()
-    _lib.profile_enable(True)
+    _lib.profile_enable(True)      # the library's event pair around every kernel: per-kernel times over the timed region itself
     _lib.profile_read(reset=True)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    t_host = time.perf_counter()
     e0.record()
+    host_marks = []
     for _ in range(args.steps):
         outs = step()
+        host_marks.append(time.perf_counter())
     e1.record()
+    host_issue_ms = (time.perf_counter() - t_host) * 1e3 / args.steps      # what the host needs to queue one step
+    if os.environ.get("KDA_BENCH_HOST_MARKS"):
+        print("host ms per step:", [round((b - a) * 1e3, 3) for a, b in zip([t_host] + host_marks[:-1], host_marks)], file=sys.stderr, flush=True)
     barrier()
-    ms_total = maxms(e0.elapsed_time(e1))
+    ms_rank = e0.elapsed_time(e1)
+    ms_total = maxms(ms_rank)
+    if world > 1:
+        per_rank = torch.zeros(world, 2, device=dev, dtype=torch.float64)
+        per_rank[rank, 0], per_rank[rank, 1] = ms_rank / args.steps, host_issue_ms
+        dist.all_reduce(per_rank)
+        ranks_ms, ranks_host = [round(x, 4) for x in per_rank[:, 0].tolist()], [round(x, 4) for x in per_rank[:, 1].tolist()]
+    else:
+        ranks_ms, ranks_host = [round(ms_rank / args.steps, 4)], [round(host_issue_ms, 4)]
     stages = _lib.profile_read(reset=True)
     _lib.profile_enable(False)
     # what was timed is checked: every output finite, no bounded wait gave up, cu_seqlens accepted
@@ -641,6 +660,7 @@ def main():
                    "l2": "inputs of a step far exceed the 126 MB L2; no flush needed",
                    "seed": "one per batch row" if host_resident else "0 (drawn on the device)"},
         "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks, "checks": checks,
+        "ms_per_step_by_rank": ranks_ms, "host_issue_ms_per_step_by_rank": ranks_host,
         "roofline": roof, "step_roofline": whole, "kernels": kernels, "cpu_baseline": cpu,
     }
     if workloads is not None:
