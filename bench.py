@@ -193,7 +193,7 @@ def run_reference(args, rank):
 # steps of the workloads on device-resident inputs
 # =====================================================================================================================
 
-def make_step(workload: str, x: dict, cu, gate: bool = False, l2: bool = False):
+def make_step(workload: str, x: dict, cu, gate: bool = False, l2: bool = False, safe: bool = False):
     """Returns (step function over a dict of device tensors, kernel launches per step, names that get gradients)."""
     from kda_b200 import chunk_kda, fused_recurrent_kda_fwd
     w = WORKLOADS[workload]
@@ -215,16 +215,18 @@ def make_step(workload: str, x: dict, cu, gate: bool = False, l2: bool = False):
             leaves = [x[n].requires_grad_(True) for n in grad_names]
             kw = dict(gate_kw, A_log=x["A_log"], dt_bias=x["dt_bias"]) if gate else {}
             o, ht = chunk_kda(x["q"], x["k"], x["v"], x["g"], x["beta"], initial_state=x.get("h0"),
-                              output_final_state=True, cu_seqlens=cu, use_qk_l2norm_in_kernel=l2, **kw)
+                              output_final_state=True, cu_seqlens=cu, use_qk_l2norm_in_kernel=l2, safe_gate=safe, **kw)
             grads = torch.autograd.grad([o, ht], leaves, [x["do"], x["dht"]])
             return (o, ht) + tuple(grads)
+        if x["q"].dtype == torch.float32:
+            return step, 3, grad_names                    # token-recurrent forward, backward, its finishing kernel
         return step, (10 if gate else 5), grad_names      # gate: + activation, beta sigmoid; + their backward and the reduction
 
     def step(x=x):
         with torch.no_grad():
             return chunk_kda(x["q"], x["k"], x["v"], x["g"], x["beta"], initial_state=x.get("h0"),
-                             output_final_state=True, cu_seqlens=cu, use_qk_l2norm_in_kernel=l2)
-    return step, 3, []
+                             output_final_state=True, cu_seqlens=cu, use_qk_l2norm_in_kernel=l2, safe_gate=safe)
+    return step, (1 if x["q"].dtype == torch.float32 else 3), []
 
 
 def time_steps(step, steps: int, warmup: int) -> float:
@@ -404,6 +406,8 @@ def main():
                     help="call the operator as the layer does: raw bf16 gate input + A_log + dt_bias and beta logits "
                          "(use_gate_in_kernel, use_beta_sigmoid_in_kernel); training workloads and decode")
     ap.add_argument("--l2norm", action="store_true", help="use_qk_l2norm_in_kernel=True (chunked workloads)")
+    ap.add_argument("--safe-gate", action="store_true",
+                    help="bounded gates g = -5 sigmoid(x) and safe_gate=True: the forward's tensor-core diagonal blocks (chunked workloads)")
     ap.add_argument("--gpu-bar-deadline", type=float, default=240.0, help="seconds the Triton comparison may take (0: skip it)")
     ap.add_argument("--clock-interval-ms", type=int, default=20, help="nvidia-smi sampling interval during the timed region")
     ap.add_argument("--gpu-bar-child", action="store_true", help=argparse.SUPPRESS)
@@ -439,6 +443,11 @@ def main():
         mine["beta"] = torch.randn(mine["beta"].shape, generator=gen).bfloat16().to(mine["beta"].device)   # beta logits
         mine["A_log"] = torch.log(torch.empty(w.H).uniform_(1, 16, generator=gen))
         mine["dt_bias"] = torch.randn(w.H * w.K, generator=gen)
+    if args.safe_gate:
+        if args.gate or args.workload == "decode" or w.dtype != torch.bfloat16:
+            raise SystemExit("--safe-gate goes with the bf16 chunked workloads, without --gate")
+        gen = torch.Generator().manual_seed(2000 + rank)
+        mine["g"] = (-5.0 * torch.sigmoid(2.0 * torch.randn(mine["g"].shape, generator=gen))).to(mine["g"].device)      # g >= -5
     names = list(mine)
     host_resident = not mine["q"].is_cuda
     pinned = {n: mine[n].pin_memory() for n in names} if host_resident else None
@@ -460,7 +469,7 @@ def main():
             return float(t.item())
         return ms
 
-    step, launches_per_step, grad_names = make_step(args.workload, devt, cu, args.gate, args.l2norm)
+    step, launches_per_step, grad_names = make_step(args.workload, devt, cu, args.gate, args.l2norm, args.safe_gate)
 
     # ---------------- kernel-resident timing ----------------
     sampler = ClockSampler(local_rank if os.environ.get("CUDA_VISIBLE_DEVICES") is None else
@@ -526,7 +535,7 @@ def main():
     e2e = None
     if not args.no_e2e and host_resident:
         out_host = None
-        pipelined = w.backward and cu is None and args.workload != "decode" and not args.gate and not args.l2norm
+        pipelined = w.backward and cu is None and args.workload != "decode" and not args.gate and not args.l2norm and not args.safe_gate
         head_groups = 4 if (pipelined and B < 4) else None      # few batch rows: cut the pieces along the heads as well
 
         def e2e_step():
@@ -578,6 +587,7 @@ def main():
 
     # ---------------- roofline of the dominant kernel ----------------
     th = tokens * H                                      # (token, head) units one launch of this rank processes
+    roof = None
     if args.workload == "decode":
         byt = B * H * decode_bytes_per_seq_head()
         ach = byt / (ms_step * 1e-3) / 1e9
@@ -593,7 +603,18 @@ def main():
                 kv["hbm_frac"] = KERNEL_WORK[s_][1] * th / sec_ / 1e9 / peaks["hbm"]          # algorithmic bytes, "of measured"
                 kv["dram_efficiency"] = KERNEL_WORK[s_][2] * th / sec_ / 1e9 / peaks["hbm"]   # design bytes (boundary + tiles)
                 kv["tensor_frac_sustained"] = KERNEL_WORK[s_][0] * th / sec_ / 1e12 / peaks["tf_sust"]
-        dom = max((s for s in kernels if s in KERNEL_WORK), key=lambda s: kernels[s]["ms_per_launch"] * kernels[s]["launches"])
+        staged = [s for s in kernels if s in KERNEL_WORK]
+        dom = max(staged, key=lambda s: kernels[s]["ms_per_launch"] * kernels[s]["launches"]) if staged else None
+        if dom is None:
+            # float32 tensors: the token-recurrent pair of kernels, which the library does not time one by one; the whole
+            # step against the operator-boundary bytes (all tensors float32)
+            io = 4 * (3 * 128 + 2 * 128 + 1) + (4 * (4 * 128 + 2 * 128 + 1) if w.backward else 0)
+            ach = io * th / (ms_step * 1e-3) / 1e9
+            roof = {"kernel": "kda_recurrent_kernel" + (" + kda_recurrent_bwd_kernel" if w.backward else ""), "bound": "hbm",
+                    "achieved": ach, "peak": peaks["hbm"], "unit": "GB/s", "frac": ach / peaks["hbm"], "traffic": None,
+                    "peak_source": peaks["src"], "algorithmic_bytes_per_launch": io * th,
+                    "note": "exact fp32 path: one warp (forward) or CTA (backward) per (sequence, head), token-serial; not HBM-bound"}
+    if roof is None:
         fl, by, design = KERNEL_WORK[dom]
         sec = kernels[dom]["ms_per_launch"] * 1e-3
         ridge = peaks["tf_sust"] * 1e12 / (peaks["hbm"] * 1e9)
@@ -632,7 +653,7 @@ def main():
                          f"{reps} x (B=1 T=512 H=32 K=V=128), {spent:.1f} s"}
 
     workloads = None
-    default_run = args.workload == "train_bf16" and not args.gate and not args.l2norm and args.scale_down == 1
+    default_run = args.workload == "train_bf16" and not args.gate and not args.l2norm and not args.safe_gate and args.scale_down == 1
     if default_run and world == 1 and not args.no_workloads:
         del devt, step
         torch.cuda.empty_cache()
@@ -647,14 +668,15 @@ def main():
 
     strong = world > 1 and not args.weak
     line = {
-        "metric": METRIC if (args.workload == "train_bf16" and not args.gate and not args.l2norm) else
+        "metric": METRIC if (args.workload == "train_bf16" and not args.gate and not args.l2norm and not args.safe_gate) else
                   f"KDA {args.workload}{' +gate' if args.gate else ''}{' +l2norm' if args.l2norm else ''} tokens/s",
         "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak" if (args.weak and world > 1) else "strong",
-        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "vs_baseline": None, "dtype": "f32" if w.dtype == torch.float32 else "bf16", "data": "synthetic",
         "config": {"workload": f"{args.workload} (B={B * (world if strong else 1)} T={T} H={H} K=V=128, chunk 64"
                                f"{', fwd+bwd' if w.backward else ''}{', packed varlen' if cu is not None else ''}"
-                               f"{', gate + beta sigmoid in kernel' if args.gate else ''}{', q/k l2norm in kernel' if args.l2norm else ''})",
+                               f"{', gate + beta sigmoid in kernel' if args.gate else ''}{', q/k l2norm in kernel' if args.l2norm else ''}"
+                               f"{', bounded gates + safe_gate' if args.safe_gate else ''})",
                    "per_gpu_batch": B, "sharding": ("batch rows over ranks, no collective on the data path" if strong else
                                                     ("replicas" if world > 1 else "one GPU")),
                    "l2": "inputs of a step far exceed the 126 MB L2; no flush needed",

@@ -40,6 +40,8 @@ WORKLOADS = {
     # variable-length packed forward+backward
     "varlen_bf16": Workload("varlen_bf16", 1, 0, 32, 128, 128, torch.bfloat16, True, 0.02,
                             n_seqs=64, min_len=128, max_len=16384),
+    # float32 training (the exact token-recurrent kernels); not one of the five stated workloads: a measurement case
+    "train_fp32": Workload("train_fp32", 8, 2048, 32, 128, 128, torch.float32, True, 0.02),
     # decode: 1024 sequences, one token each, 256 consecutive steps
     "decode": Workload("decode", 1024, 1, 32, 128, 128, torch.bfloat16, False, 0.02, steps=256),
 }
