@@ -21,6 +21,15 @@ def _step(d, dev):
     e = {n: t.to(dev) for n, t in make_inputs(40, 1, 16, 128, 128, torch.bfloat16, seed=9, h0_std=0.05).items() if t is not None}
     state = e["h0"].clone()
     od, _ = fused_recurrent_kda_fwd(e["q"], e["k"], e["v"], e["g"], e["beta"], scale=0.1, initial_state=state, inplace_final_state=True)
+    # the bounded-gate variant of the forward and the float32 training path have kernels (and attributes) of their own
+    with torch.no_grad():
+        gs = -5.0 * torch.sigmoid(c["g"])
+        o_safe, _ = chunk_kda(c["q"], c["k"], c["v"], gs, c["beta"], initial_state=c["h0"], output_final_state=True, safe_gate=True)
+    f = {n: t.to(dev) for n, t in make_inputs(1, 70, 2, 128, 128, torch.float32, seed=10, h0_std=0.1, backward=True).items()}
+    lf = {n: f[n].requires_grad_(True) for n in ("q", "k", "v", "g", "beta", "h0")}
+    o32, ht32 = chunk_kda(lf["q"], lf["k"], lf["v"], lf["g"], lf["beta"], initial_state=lf["h0"], output_final_state=True)
+    torch.autograd.backward([o32, ht32], [f["do"], f["dht"]])
+    outs += [o_safe, o32.detach(), lf["q"].grad, lf["g"].grad, lf["h0"].grad]
     torch.cuda.synchronize(dev)
     return [t.cpu() for t in outs + [od, state]]
 
