@@ -547,7 +547,8 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
     tensor is [.., V, K] instead of [.., K, V].
 
     bf16 inputs with K, V <= 128 take the chunked tensor-core kernels (built for K = V = 128; smaller heads are
-    zero-padded to 128 channels, which leaves every result unchanged).  float32 inputs take the exact
+    zero-padded to 128 channels, which leaves every result unchanged; K = 256 runs forward-only through the
+    token-recurrent kernel).  float32 inputs take the exact
     token-recurrent fp32 kernels: forward for K in {32, 64, 128, 256}, with gradients for K, V in {32, 64, 128}.  `safe_gate=True` is the caller's promise that every gate value is at least
     -5 (fla/ops/kda/chunk.py:235-246); the forward then computes the diagonal 16 x 16 blocks of the intra-chunk products on
     tensor cores as well (factored around each block's middle row) instead of pairwise, which is faster and only safe under
@@ -582,7 +583,15 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
                                        use_qk_l2norm_in_kernel=use_qk_l2norm_in_kernel, cu_seqlens=cu_seqlens,
                                        transpose_state_layout=transpose_state_layout)
     if K > 128 or V > 128:
-        raise NotImplementedError(f"kda_b200: the bf16 chunked kernels are built for head sizes up to 128, got K={K}, V={V}")
+        # larger heads (fla allows K <= 256): forward through the token-recurrent kernel (bf16 in and out, fp32 state),
+        # which serves K = 256; there is no backward for them
+        needs_grad = torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (q, k, v, g, beta, initial_state))
+        if needs_grad or return_intermediate_states or K != 256 or V % 32 != 0 or (transpose_state_layout and K not in (64, 128)):
+            raise NotImplementedError(f"kda_b200: the bf16 chunked kernels are built for head sizes up to 128, got K={K}, V={V} "
+                                      "(K = 256 runs forward-only)")
+        return fused_recurrent_kda_fwd(q, k, v, g, beta, initial_state=initial_state, scale=scale,
+                                       output_final_state=output_final_state, inplace_final_state=False,
+                                       use_qk_l2norm_in_kernel=use_qk_l2norm_in_kernel, cu_seqlens=cu_seqlens)
     # transposed state layout ([N, H, V, K]): the chunk kernels keep [N, H, K, V]; states cross the boundary once per
     # sequence, so they are transposed there (differentiably)
     tr = (lambda t: t.transpose(-1, -2)) if transpose_state_layout else (lambda t: t)

@@ -62,8 +62,21 @@ def test_small_heads_intermediate_states():
     assert_bf16_parity(h[:, 0], d["h0"], "h[0]")
 
 
-def test_heads_above_128_rejected():
+def test_key_size_256_runs_forward_only():
+    """K = 256 (fla's upper limit): forward through the token-recurrent kernel, bf16 in and out; training raises."""
     from kda_b200 import chunk_kda
-    d = make_inputs(1, 64, 1, 256, 128, torch.bfloat16, seed=913)
+    from oracle.kda_oracle import recurrent_kda
+    d = make_inputs(2, 100, 2, 256, 128, torch.bfloat16, seed=913, h0_std=0.02)
+    c = {n: d[n].cuda() for n in ("q", "k", "v", "g", "beta", "h0")}
+    with torch.no_grad():
+        o, ht = chunk_kda(c["q"], c["k"], c["v"], c["g"], c["beta"], initial_state=c["h0"], output_final_state=True)
+    ro, rh = recurrent_kda(d["q"], d["k"], d["v"], d["g"], d["beta"], initial_state=d["h0"], output_final_state=True)
+    assert o.dtype == torch.bfloat16 and ht.shape == (2, 2, 256, 128)
+    assert_bf16_parity(o, ro, "o")
+    assert_bf16_parity(ht, rh, "ht")
     with pytest.raises(NotImplementedError):
-        chunk_kda(*(d[n].cuda() for n in ("q", "k", "v", "g", "beta")))
+        chunk_kda(c["q"].requires_grad_(True), c["k"], c["v"], c["g"], c["beta"])
+    e = make_inputs(1, 64, 1, 192, 128, torch.bfloat16, seed=914)
+    with pytest.raises(NotImplementedError):
+        with torch.no_grad():
+            chunk_kda(*(e[n].cuda() for n in ("q", "k", "v", "g", "beta")))
